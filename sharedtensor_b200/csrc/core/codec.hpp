@@ -1,0 +1,114 @@
+// Sign-bit delta codec (host side).
+//
+// Two wire formats live here:
+//
+//  * tensor-scale frames: one fp32 scale followed by ceil(N/8) sign bytes, element i in byte i/8
+//    bit i%8, bit 0 => +scale, bit 1 => -scale.  This is the format the reference speaks on its TCP
+//    edges (reference src/sharedtensor.c:156-177 encoder, 106-111 decoder) and is reproduced
+//    bit for bit, including "zero counts as negative" (168-172) and scale==0 no-op frames.
+//
+//  * block-scale frames: one E8M0-style exponent byte per block of B elements (B a power of two,
+//    32..4096) plus one 32-bit sign word per 32 elements (bit j of word w = element 32*w+j, so the
+//    little-endian byte stream has the same bit order as the tensor-scale frame).  This is the
+//    format the GPU kernels produce and consume; the functions here are their bit-exact CPU oracle.
+//
+// State model ("mirror form").  A replica keeps its values V and, per edge e, a mirror K_e = the
+// part of V that the neighbour on e is already known to hold (everything sent to it plus everything
+// received from it).  The quantity the reference calls the edge residual (`Connection.delta`,
+// src/sharedtensor.c:27) is V - K_e, so encoding is "quantise V - K_e, add the quantised step to
+// K_e", and decoding a frame from e is "add the step to V and to K_e".  Updates received on another
+// edge change V but not K_e, which forwards them, exactly like src/sharedtensor.c:124-127.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+
+namespace st {
+
+// ---------------------------------------------------------------------------------------------
+// Exponent helpers shared (by construction, not by include) with the CUDA kernels.
+// ---------------------------------------------------------------------------------------------
+
+// Code 0 means "silent block": nothing is applied for that block in this frame.
+constexpr int kSilent = 0;
+// Smallest / largest exponent a code can carry: code = exponent + 127, codes 1..254.
+constexpr int kMinExp = -126;
+constexpr int kMaxExp = 127;
+
+inline uint32_t f32_bits(float x) {
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  return u;
+}
+inline float bits_f32(uint32_t u) {
+  float x;
+  std::memcpy(&x, &u, 4);
+  return x;
+}
+
+// floor(log2(x)) for a finite positive normal fp32 x, taken from the exponent field; for zero and
+// denormals returns -127 (callers treat anything that small as silent).
+inline int floor_log2_f32(float x) { return int((f32_bits(x) >> 23) & 0xff) - 127; }
+
+// Exponent k of the power-of-two floor of sqrt(sumsq / B): floor((floor_log2(sumsq) - log2 B) / 2).
+inline int rms_exponent(float sumsq, int log2_block) {
+  int e = floor_log2_f32(sumsq) - log2_block;
+  return e >> 1;  // arithmetic shift = floor division by two
+}
+
+// 2^k as fp32 for k in [-126, 127].
+inline float exp2i(int k) { return bits_f32(uint32_t(k + 127) << 23); }
+
+struct BlockGate {
+  int min_exp = -100;  // blocks whose scale exponent is below this stay silent
+  int rel_bits = 22;   // ... or below (exponent of the block's value RMS) - rel_bits
+};
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-scale (reference wire format)
+// ---------------------------------------------------------------------------------------------
+
+size_t sign_bytes(size_t n);  // ceil(n/8)
+
+// Power-of-two floor of the RMS of r[0..n), summed left to right in fp32 like the reference
+// (src/sharedtensor.c:156-159).  Returns 0 for an all-zero (or underflowing) input.
+float ref_scale_of(const float* r, size_t n);
+
+// Reference encoder on an explicit residual array (src/sharedtensor.c:166-174): chooses the scale,
+// writes the sign bytes, moves every residual element by -/+ scale.  Returns the scale.
+float encode_residual_ref(float* r, size_t n, uint8_t* bits);
+
+// Mirror-form encoder: quantises v - k with one scale for the whole tensor, adds the step to k.
+// `min_scale`: if the chosen scale is below it the frame is a no-op (scale 0, k untouched).
+// Returns the scale written on the wire.
+float encode_tensor(const float* v, float* k, size_t n, uint8_t* bits, float min_scale);
+
+// Decoder: dst[i] += (bit ? -scale : +scale).  `dst2` may be null; if not it gets the same step.
+void decode_tensor_add(const uint8_t* bits, float scale, size_t n, float* dst, float* dst2);
+
+// ---------------------------------------------------------------------------------------------
+// Block-scale (GPU format; CPU oracle)
+// ---------------------------------------------------------------------------------------------
+
+size_t block_words(size_t n);              // ceil(n/32)
+size_t block_scales(size_t n, int block);  // ceil(n/block)
+
+// Sum of squares of one 32-element group in the canonical order used by the kernels:
+// per 4 consecutive elements ((x0^2 + x1^2) + (x2^2 + x3^2)), then a pairwise tree over the 8 partial sums.
+float group32_sumsq(const float* x);
+
+// Encodes n elements (n need not be a multiple of anything; missing elements count as zero residual
+// and their bits are 1).  v: values, k: mirror (updated), words/scales: outputs.
+// Returns the sum of squared residual (before the update), a cheap convergence statistic.
+double encode_block(const float* v, float* k, size_t n, int block, const BlockGate& gate,
+                    uint32_t* words, uint8_t* scales);
+
+// Applies one block-scale frame to dst (and dst2 if non-null).
+void decode_block_add(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst,
+                      float* dst2);
+
+// Per-segment sum of squares over a flat arena (table sync; README.md:41 of the reference lists
+// per-tensor magnitudes as a TODO).  offsets has n_seg+1 entries.
+void segment_sumsq(const float* x, const int64_t* offsets, int n_seg, double* out);
+
+}  // namespace st

@@ -1,0 +1,115 @@
+"""Configuration of a shared tensor.
+
+The reference has no configuration beyond the three arguments of ``createOrFetch`` and a handful of
+hard-coded constants (listen backlog 5 at src/sharedtensor.c:323, a one-second idle sleep at 163,
+fan-out 2 in the struct at 31-33, the scale rule at 158-159).  Here every such constant is a field
+of one dataclass, validated once, overridable per call (keyword arguments of ``createOrFetch``) and
+per process (``SHAREDTENSOR_<FIELD>`` environment variables), and echoed back by ``stats()``.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+from dataclasses import dataclass
+from typing import Any
+
+_TRUE = {"1", "true", "yes", "on"}
+
+
+@dataclass
+class Config:
+    # --- where the replica lives and how edges are carried -------------------------------------
+    transport: str = "auto"          # auto | gpu | tcp   (auto: gpu for CUDA tensors, tcp for CPU tensors)
+    topology: str = "tree"           # tree (reference semantics, dynamic join) | mesh (fixed group over NVSwitch)
+    # --- quantiser ------------------------------------------------------------------------------
+    scale_mode: str = "block32"      # GPU edges: block32 .. block4096
+    tcp_scale_mode: str = "tensor"   # TCP edges: tensor (reference wire format) | block32 .. block4096
+    min_exp: int = -60               # blocks whose scale exponent is below this stay silent
+    rel_bits: int = 22               # ... or this many bits below the block's own value RMS
+    min_scale_abs: float = 0.0       # tensor mode cut-offs
+    min_scale_rel: float = 2.0 ** -22
+    # --- GPU engine -----------------------------------------------------------------------------
+    ring_slots: int = 4              # frames in flight per edge direction
+    engine: str = "thread"           # thread: free-running rounds on a comm stream | manual: caller drives step()
+    comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
+    rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
+    idle_sleep_us: int = 200         # engine pause when a round moved nothing
+    poll_deadline_us: int = 1000     # upper bound of every device-side wait
+    use_multimem: bool = False       # NVLS store fan-out for mesh groups when the host exposes it
+    # --- TCP edges ------------------------------------------------------------------------------
+    max_frames_per_s: float = 0.0    # rate cap per edge (README.md:31 of the reference lists this as a TODO)
+    idle_keepalive_ms: int = 0
+    listen_backlog: int = 5
+    # --- membership -----------------------------------------------------------------------------
+    ready_mode: str = "converged"    # first_frame (reference) | converged
+    ready_bits: int = 12
+    ready_timeout_s: float = 30.0
+    rejoin: bool = True              # re-run the join walk when the up edge is lost
+    rejoin_backoff_ms: int = 200
+
+    def __post_init__(self) -> None:
+        self.validate()
+
+    # ------------------------------------------------------------------------------------------
+    @staticmethod
+    def _block_of(mode: str) -> int:
+        if mode == "tensor":
+            return 0
+        if not mode.startswith("block"):
+            raise ValueError(f"unknown scale mode {mode!r}")
+        b = int(mode[5:])
+        if b < 32 or b > 4096 or b & (b - 1):
+            raise ValueError(f"block size must be a power of two in 32..4096, got {b}")
+        return b
+
+    @property
+    def block(self) -> int:
+        return self._block_of(self.scale_mode)
+
+    @property
+    def tcp_block(self) -> int:
+        return self._block_of(self.tcp_scale_mode)
+
+    def validate(self) -> None:
+        if self.transport not in ("auto", "gpu", "tcp"):
+            raise ValueError(f"transport must be auto, gpu or tcp, got {self.transport!r}")
+        if self.topology not in ("tree", "mesh"):
+            raise ValueError(f"topology must be tree or mesh, got {self.topology!r}")
+        if self.block == 0:
+            raise ValueError("GPU edges need a block scale mode (block32..block4096)")
+        self.tcp_block  # validates
+        if self.engine not in ("thread", "manual"):
+            raise ValueError(f"engine must be thread or manual, got {self.engine!r}")
+        if self.ready_mode not in ("first_frame", "converged"):
+            raise ValueError(f"ready_mode must be first_frame or converged, got {self.ready_mode!r}")
+        if not 2 <= self.ring_slots <= 64:
+            raise ValueError("ring_slots must be in 2..64")
+        if self.rel_bits < 1 or self.rel_bits > 60:
+            raise ValueError("rel_bits must be in 1..60")
+        if self.rounds_in_flight < 1:
+            raise ValueError("rounds_in_flight must be >= 1")
+
+    # ------------------------------------------------------------------------------------------
+    @classmethod
+    def from_env_and_kwargs(cls, **kwargs: Any) -> "Config":
+        values: dict[str, Any] = {}
+        for f in dataclasses.fields(cls):
+            env = os.environ.get("SHAREDTENSOR_" + f.name.upper())
+            if env is None:
+                continue
+            if f.type in ("bool", bool):
+                values[f.name] = env.strip().lower() in _TRUE
+            elif f.type in ("int", int):
+                values[f.name] = int(env)
+            elif f.type in ("float", float):
+                values[f.name] = float(env)
+            else:
+                values[f.name] = env
+        unknown = set(kwargs) - {f.name for f in dataclasses.fields(cls)}
+        if unknown:
+            raise TypeError(f"unknown shared tensor option(s): {sorted(unknown)}")
+        values.update(kwargs)
+        return cls(**values)
+
+    def asdict(self) -> dict[str, Any]:
+        return dataclasses.asdict(self)

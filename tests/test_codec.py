@@ -1,0 +1,169 @@
+"""T0: the host codec against a numpy restatement of the reference's loops
+(encoder src/sharedtensor.c:156-174, decoder 106-111)."""
+import numpy as np
+import pytest
+import torch
+
+from sharedtensor_b200 import _native
+
+core = _native.core()
+
+
+def np_ref_encode(r: np.ndarray):
+    """Sequential fp32 model of the reference sender loop; returns (scale, bits, new residual)."""
+    r = r.astype(np.float32).copy()
+    acc = np.float32(0)
+    for x in r:
+        acc = np.float32(acc + np.float32(x * x))
+    mean = np.float32(acc / np.float32(len(r)))
+    s = np.float32(np.sqrt(np.float64(mean)))
+    if s > 0 and np.isfinite(s):
+        scale = np.float32(2.0 ** np.floor(np.log2(np.float64(s))))
+    else:
+        scale = np.float32(0)
+    bits = np.zeros((len(r) + 7) // 8, dtype=np.uint8)
+    for i in range(len(r)):
+        if r[i] > 0:
+            r[i] = np.float32(r[i] - scale)
+        else:
+            bits[i // 8] |= 1 << (i % 8)
+            r[i] = np.float32(r[i] + scale)
+    return scale, bits, r
+
+
+def np_ref_decode(bits, scale, n):
+    i = np.arange(n)
+    b = (bits[i // 8] >> (i % 8)) & 1
+    return (np.float32(scale) - b.astype(np.float32) * np.float32(scale) * 2).astype(np.float32)
+
+
+@pytest.mark.parametrize("n", [1, 2, 7, 8, 9, 31, 32, 33, 240, 1000])
+@pytest.mark.parametrize("kind", ["normal", "zeros", "tiny", "mixed"])
+def test_reference_encoder_bit_exact(n, kind):
+    rng = np.random.default_rng(n * 7 + len(kind))
+    if kind == "normal":
+        r = rng.standard_normal(n)
+    elif kind == "zeros":
+        r = np.zeros(n)
+    elif kind == "tiny":
+        r = rng.standard_normal(n) * 1e-30
+    else:
+        r = rng.standard_normal(n) * 10.0 ** rng.integers(-6, 3, n)
+        r[::3] = 0.0
+        r[1::5] = -0.0
+    r = r.astype(np.float32)
+    scale_np, bits_np, r_np = np_ref_encode(r)
+    t = torch.from_numpy(r.copy())
+    bits = torch.zeros(core.sign_bytes(n), dtype=torch.uint8)
+    scale = core.encode_residual_ref(t.data_ptr(), n, bits.data_ptr())
+    assert np.float32(scale) == scale_np
+    assert np.array_equal(bits.numpy(), bits_np)
+    assert np.array_equal(t.numpy(), r_np)
+    # scale is zero or an exact power of two
+    if scale:
+        m, _ = np.frexp(scale)
+        assert m == 0.5
+
+
+@pytest.mark.parametrize("n", [1, 5, 64, 240, 1001])
+def test_decoder_matches_reference(n):
+    rng = np.random.default_rng(n)
+    bits = rng.integers(0, 256, (n + 7) // 8, dtype=np.uint8)
+    dst = rng.standard_normal(n).astype(np.float32)
+    expect = dst + np_ref_decode(bits, 0.25, n)
+    t = torch.from_numpy(dst.copy())
+    t2 = torch.from_numpy(dst.copy())
+    b = torch.from_numpy(bits)
+    core.decode_tensor_add(b.data_ptr(), 0.25, n, t.data_ptr(), t2.data_ptr())
+    assert np.array_equal(t.numpy(), expect)
+    assert np.array_equal(t2.numpy(), expect)
+    # scale 0 is a no-op whatever the bits say
+    core.decode_tensor_add(b.data_ptr(), 0.0, n, t.data_ptr(), 0)
+    assert np.array_equal(t.numpy(), expect)
+
+
+def test_mirror_form_tracks_residual_form():
+    """Quantising v - k and stepping k produces the reference's residual stream.  The two forms
+    round differently in the last bit (the mirror form subtracts two exact numbers each frame, the
+    residual form accumulates roundings), so signs may differ for elements within an ulp of zero."""
+    n = 240
+    rng = np.random.default_rng(3)
+    v = torch.from_numpy(rng.standard_normal(n).astype(np.float32))
+    k = torch.zeros(n)
+    resid = v.clone()
+    bits_a = torch.zeros(core.sign_bytes(n), dtype=torch.uint8)
+    bits_b = torch.zeros_like(bits_a)
+    for it in range(40):
+        sa = core.encode_tensor(v.data_ptr(), k.data_ptr(), n, bits_a.data_ptr(), 0.0)
+        sb = core.encode_residual_ref(resid.data_ptr(), n, bits_b.data_ptr())
+        if it < 12:
+            assert sa == sb
+            assert torch.equal(bits_a, bits_b)
+        assert torch.allclose(v - k, resid, atol=1e-6)
+    assert (v - k).norm() / v.norm() < 2e-2  # the tensor-wide scale drains outliers slowly
+
+
+def test_tensor_stream_converges_to_fp32_floor():
+    n = 240
+    torch.manual_seed(0)
+    v = torch.randn(n)
+    k = torch.zeros(n)
+    peer = torch.zeros(n)
+    bits = torch.zeros(core.sign_bytes(n), dtype=torch.uint8)
+    for _ in range(400):
+        s = core.encode_tensor(v.data_ptr(), k.data_ptr(), n, bits.data_ptr(), 2.0 ** -24)
+        core.decode_tensor_add(bits.data_ptr(), s, n, peer.data_ptr(), 0)
+    assert torch.equal(peer, k)
+    assert ((peer - v).norm() / v.norm()) < 1e-5
+    assert (peer - v).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("block", [32, 64, 256, 4096])
+@pytest.mark.parametrize("n", [1, 31, 32, 33, 100, 4096, 5000])
+def test_block_roundtrip_and_convergence(block, n):
+    torch.manual_seed(n + block)
+    v = torch.randn(n) * torch.logspace(-3, 1, n)  # heterogeneous magnitudes
+    k = torch.zeros(n)
+    peer = torch.zeros(n)
+    words = torch.zeros(core.block_words(n), dtype=torch.int32)
+    scales = torch.zeros(core.block_scales(n, block), dtype=torch.uint8)
+    prev = None
+    for it in range(120):
+        ss = core.encode_block(v.data_ptr(), k.data_ptr(), n, block, -60, 22, words.data_ptr(), scales.data_ptr())
+        core.decode_block_add(words.data_ptr(), scales.data_ptr(), n, block, peer.data_ptr(), 0)
+        assert torch.equal(peer, k), "decoder and encoder-side mirror must agree bit for bit"
+        prev = ss
+    rel = ((peer - v).norm() / v.norm()).item()
+    # larger blocks share one scale among more heterogeneous elements and drain more slowly
+    assert rel < {32: 1e-5, 64: 1e-5, 256: 1e-3, 4096: 5e-2}[block], rel
+    assert prev is not None
+
+
+def test_block_silent_when_converged():
+    n = 256
+    v = torch.randn(n)
+    k = v.clone()
+    words = torch.zeros(core.block_words(n), dtype=torch.int32)
+    scales = torch.ones(core.block_scales(n, 32), dtype=torch.uint8)
+    ss = core.encode_block(v.data_ptr(), k.data_ptr(), n, 32, -60, 22, words.data_ptr(), scales.data_ptr())
+    assert ss == 0.0
+    assert int(scales.sum()) == 0
+    assert torch.equal(k, v)
+
+
+def test_block_scale_is_pow2_floor_of_rms():
+    n = 32
+    v = torch.full((n,), 3.0)
+    k = torch.zeros(n)
+    words = torch.zeros(1, dtype=torch.int32)
+    scales = torch.zeros(1, dtype=torch.uint8)
+    core.encode_block(v.data_ptr(), k.data_ptr(), n, 32, -60, 22, words.data_ptr(), scales.data_ptr())
+    assert int(scales[0]) - 127 == 1  # rms 3 -> 2^1
+    assert int(words[0]) == 0          # all positive -> bit 0
+    assert torch.equal(k, torch.full((n,), 2.0))
+
+
+def test_segment_sumsq():
+    x = torch.arange(10, dtype=torch.float32)
+    out = core.segment_sumsq(x.data_ptr(), [0, 3, 3, 10])
+    assert out == [5.0, 0.0, float((x[3:] ** 2).sum())]

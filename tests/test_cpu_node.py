@@ -1,0 +1,169 @@
+"""T1/T4: sum consistency of CPU replicas over localhost TCP, including the 2-process, 240-element,
+1000-adds-each configuration."""
+import multiprocessing as mp
+import time
+
+import pytest
+import torch
+
+import sharedtensor
+
+
+def _wait_equal(nodes, expect, tol_rel=1e-5, tol_inf=1e-4, timeout=30.0):
+    t0 = time.time()
+    out = torch.zeros_like(expect)
+    worst = None
+    while time.time() - t0 < timeout:
+        worst = 0.0
+        ok = True
+        for n in nodes:
+            n.copyToTensor(out)
+            rel = ((out - expect).norm() / expect.norm()).item()
+            inf = (out - expect).abs().max().item()
+            worst = max(worst, rel)
+            if rel > tol_rel or inf > tol_inf:
+                ok = False
+        if ok:
+            return worst
+        time.sleep(0.02)
+    raise AssertionError(f"replicas did not converge: worst rel-L2 {worst}")
+
+
+def _worker(port, seed, iters, q, ready):
+    torch.manual_seed(seed)
+    shape = (4, 5, 6, 2)
+    init = torch.randn(shape)
+    st = sharedtensor.createOrFetch("127.0.0.1", port, init)
+    ready.wait()
+    total = torch.zeros(shape)
+    for _ in range(iters):
+        d = torch.randn(shape) * 1e-2
+        st.addFromTensor(d)
+        total += d
+    q.put((seed, init if st.is_master else None, total))
+    # wait for the parent to tell us the expected sum
+    expect = q_in[seed].get()
+    out = torch.zeros(shape)
+    t0 = time.time()
+    ok = False
+    while time.time() - t0 < 30:
+        st.copyToTensor(out)
+        rel = ((out - expect).norm() / expect.norm()).item()
+        inf = (out - expect).abs().max().item()
+        if rel <= 1e-5 and inf <= 1e-4:
+            ok = True
+            break
+        time.sleep(0.02)
+    q.put((seed, ok, rel, inf))
+    done.wait()
+    st.close()
+
+
+q_in = {}
+done = None
+
+
+def test_config1_two_processes_1000_adds_each(free_port):
+    """2 processes on localhost TCP, fp32 tensor of shape 4x5x6x2 from N(0,1), 1000 addFromTensor calls
+    each with N(0,1e-2) deltas; both replicas must reach initial + sum of all deltas."""
+    global done
+    ctx = mp.get_context("fork")
+    q = ctx.Queue()
+    ready = ctx.Event()
+    done = ctx.Event()
+    q_in[1] = ctx.Queue()
+    q_in[2] = ctx.Queue()
+    p1 = ctx.Process(target=_worker, args=(free_port, 1, 1000, q, ready))
+    p1.start()
+    time.sleep(0.5)  # the first process founds the tensor
+    p2 = ctx.Process(target=_worker, args=(free_port, 2, 1000, q, ready))
+    p2.start()
+    time.sleep(0.5)
+    ready.set()
+    res = [q.get(timeout=60), q.get(timeout=60)]
+    init = [r[1] for r in res if r[1] is not None]
+    assert len(init) == 1, "exactly one process is the master"
+    expect = init[0] + res[0][2] + res[1][2]
+    q_in[1].put(expect)
+    q_in[2].put(expect)
+    verdicts = [q.get(timeout=60), q.get(timeout=60)]
+    done.set()
+    p1.join(20)
+    p2.join(20)
+    for seed, ok, rel, inf in verdicts:
+        assert ok, f"replica {seed}: rel-L2 {rel:.3g}, L-inf {inf:.3g}"
+
+
+@pytest.mark.parametrize("n_nodes", [3, 6])
+@pytest.mark.parametrize("tcp_scale_mode", ["tensor", "block32"])
+def test_sum_consistency_tree(free_port, n_nodes, tcp_scale_mode):
+    torch.manual_seed(n_nodes)
+    n = 1000
+    init = torch.randn(n)
+    nodes = [sharedtensor.createOrFetch("127.0.0.1", free_port, init, tcp_scale_mode=tcp_scale_mode)]
+    try:
+        for _ in range(n_nodes - 1):
+            nodes.append(sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), tcp_scale_mode=tcp_scale_mode))
+        expect = init.clone()
+        for it in range(30):
+            for i, node in enumerate(nodes):
+                d = torch.randn(n) * 1e-2 * (1 + i)
+                node.addFromTensor(d)
+                expect += d
+        _wait_equal(nodes, expect, tol_rel=2e-5 if tcp_scale_mode == "tensor" else 1e-5, tol_inf=5e-4)
+    finally:
+        for node in nodes:
+            node.cfg.rejoin = False
+        for node in reversed(nodes):
+            node.close()
+
+
+def test_push_update_and_late_joiner_with_history(free_port):
+    n = 513
+    torch.manual_seed(5)
+    init = torch.randn(n)
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init)
+    try:
+        cur = torch.zeros(n)
+        a.copyToTensor(cur)
+        new = cur + 0.5
+        a.pushUpdate(new, cur)
+        b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n))
+        _wait_equal([a, b], init + 0.5, tol_rel=2e-5, tol_inf=5e-4)
+        assert b.flush(10.0)
+        s = b.stats()
+        assert s["edges"]["up"]["frames_recv"] > 0 and not s["master"]
+        b.close()
+    finally:
+        a.close()
+
+
+def test_state_dict_roundtrip(free_port):
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.arange(10.0))
+    try:
+        sd = a.state_dict()
+        assert torch.equal(sd["values"], torch.arange(10.0))
+        sd["values"] = sd["values"] * 2
+        a.load_state_dict(sd)
+        out = torch.zeros(10)
+        a.copyToTensor(out)
+        assert torch.equal(out, torch.arange(10.0) * 2)
+    finally:
+        a.close()
+
+
+def test_rate_cap(free_port):
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.randn(64), max_frames_per_s=50.0)
+    try:
+        b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(64), ready_mode="first_frame")
+        t0 = time.time()
+        for _ in range(20):
+            a.addFromTensor(torch.randn(64))
+            time.sleep(0.02)
+        time.sleep(0.2)
+        sent = a.stats()["edges"]["left"]["frames_sent"]
+        elapsed = time.time() - t0
+        assert sent <= 50.0 * elapsed + 25, (sent, elapsed)
+        b.close()
+    finally:
+        a.close()

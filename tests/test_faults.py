@@ -1,0 +1,112 @@
+"""T7: failure detection and recovery, with every failure made on the host: a cut socket, a killed
+CPU process, frames dropped after they were read."""
+import multiprocessing as mp
+import os
+import signal
+import time
+
+import torch
+
+import sharedtensor
+
+
+def _poll(fn, timeout=20.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        if fn():
+            return True
+        time.sleep(0.05)
+    return False
+
+
+def test_child_loss_frees_the_slot_and_a_new_child_is_adopted(free_port):
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.arange(32.0))
+    try:
+        b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(32), rejoin=False)
+        assert a.stats()["edges"]["left"]["state"] == "connected"
+        b.close()  # peer goes away: EOF on a's left edge
+        assert _poll(lambda: a.stats()["edges"]["left"]["state"] == "free")
+        assert a.stats()["edge_failures"] == 1
+        a.addFromTensor(torch.ones(32))  # the master keeps working
+        c = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(32), rejoin=False)
+        out = torch.zeros(32)
+        c.copyToTensor(out)
+        assert torch.allclose(out, torch.arange(32.0) + 1, atol=1e-2)
+        assert a.stats()["edges"]["left"]["state"] == "connected", "the freed slot is used again"
+        c.close()
+    finally:
+        a.close()
+
+
+def test_severed_up_edge_rejoins_and_keeps_unsent_updates(free_port):
+    n = 128
+    torch.manual_seed(2)
+    init = torch.randn(n)
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init)
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=50)
+    try:
+        assert b.flush(10.0)
+        b._b.inject_sever("up")  # cut the socket under the edge
+        assert _poll(lambda: b.stats()["rejoins"] == 1), b.stats()
+        d = torch.randn(n) * 1e-2
+        b.addFromTensor(d)
+        expect = init + d
+        out = torch.zeros(n)
+        assert _poll(lambda: (a.copyToTensor(out) - expect).abs().max().item() < 1e-4)
+        assert _poll(lambda: (b.copyToTensor(out) - expect).abs().max().item() < 1e-4)
+    finally:
+        b.cfg.rejoin = False
+        b.close()
+        a.close()
+
+
+def _child(port, n):
+    st = sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n))
+    st.addFromTensor(torch.ones(n))
+    time.sleep(60)
+
+
+def test_killed_process_is_detected_and_survivors_continue(free_port):
+    n = 64
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n))
+    ctx = mp.get_context("fork")
+    p = ctx.Process(target=_child, args=(free_port, n))
+    p.start()
+    try:
+        out = torch.zeros(n)
+        assert _poll(lambda: (a.copyToTensor(out) - 1).abs().max().item() < 1e-4), "child's update arrives"
+        os.kill(p.pid, signal.SIGKILL)  # host-side failure: the rank simply dies
+        p.join(10)
+        assert _poll(lambda: a.stats()["edges"]["left"]["state"] == "free")
+        a.addFromTensor(torch.ones(n))
+        a.copyToTensor(out)
+        assert torch.allclose(out, torch.full((n,), 2.0), atol=1e-4)
+    finally:
+        if p.is_alive():
+            p.kill()
+        a.close()
+
+
+def test_dropped_frames_show_up_as_a_bounded_error(free_port):
+    """A lost frame is a permanent offset of at most the frame's scale per element (the protocol has
+    no sequence numbers, like the reference); the test checks the accounting and that later traffic
+    is still applied."""
+    n = 64
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n))
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n))
+    try:
+        assert b.flush(10.0)
+        b._b.inject_drop_frames("up", 1)
+        a.addFromTensor(torch.ones(n))
+        assert _poll(lambda: b.stats()["edges"]["up"]["dropped_by_injection"] == 1)
+        assert a.flush(10.0) and b.flush(10.0)
+        out = torch.zeros(n)
+        b.copyToTensor(out)
+        err = (out - 1).abs().max().item()
+        assert 0 < err <= 1.0
+        a.addFromTensor(torch.ones(n))
+        assert _poll(lambda: abs((b.copyToTensor(out) - 2).abs().max().item() - err) < 1e-4)
+    finally:
+        b.cfg.rejoin = False
+        b.close()
+        a.close()

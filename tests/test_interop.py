@@ -1,0 +1,84 @@
+"""T3: wire compatibility with the unmodified reference (built from its own C file, hosted by
+baseline/ref_host.c, one process per replica)."""
+import sys
+import time
+from pathlib import Path
+
+import pytest
+import torch
+
+import sharedtensor
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT / "baseline"))
+import build_ref  # noqa: E402
+from ref_worker import RefWorker  # noqa: E402
+
+pytestmark = pytest.mark.skipif(build_ref.build() is None, reason="reference source not available")
+
+
+def _close_to(values, expect, tol):
+    return (torch.tensor(values) - expect).abs().max().item() <= tol
+
+
+def _poll(fn, timeout=20.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        if fn():
+            return True
+        time.sleep(0.05)
+    return False
+
+
+def test_our_node_below_reference_master(free_port):
+    n = 240
+    torch.manual_seed(0)
+    init = torch.randn(n)
+    ref = RefWorker(n)
+    ours = None
+    try:
+        ref.call(op="create", host="127.0.0.1", port=free_port, n=n, values=init.tolist())
+        ours = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n))
+        out = torch.zeros(n)
+        ours.copyToTensor(out)
+        assert (out - init).abs().max() < 5e-3  # ready after the scale fell by 2^-12
+        d_ours = torch.randn(n) * 1e-2
+        d_ref = torch.randn(n) * 1e-2
+        ours.addFromTensor(d_ours)
+        ref.call(op="add", values=d_ref.tolist())
+        expect = init + d_ours + d_ref
+        # the reference sleeps one second whenever its residual is exactly zero (src/sharedtensor.c:163)
+        assert _poll(lambda: _close_to(ref.call(op="copy")["values"], expect, 2e-4)), "reference replica"
+        assert _poll(lambda: (ours.copyToTensor(out) - expect).abs().max().item() <= 2e-4), "our replica"
+    finally:
+        if ours is not None:
+            ours.cfg.rejoin = False
+            ours.close()
+        ref.kill()
+
+
+def test_reference_nodes_below_our_master_with_redirect(free_port):
+    """Our master adopts two reference joiners and redirects a third one to its right child, which is
+    a reference process: the 'N' + sockaddr_in reply must be understood by the reference client."""
+    n = 64
+    torch.manual_seed(1)
+    init = torch.randn(n)
+    ours = sharedtensor.createOrFetch("127.0.0.1", free_port, init)
+    refs = [RefWorker(n) for _ in range(3)]
+    try:
+        for r in refs:
+            r.call(op="create", host="127.0.0.1", port=free_port, n=n)
+        st = ours.stats()
+        assert st["edges"]["left"]["state"] == "connected" and st["edges"]["right"]["state"] == "connected"
+        assert st["redirects"] == 1
+        d = torch.randn(n) * 1e-2
+        refs[2].call(op="add", values=d.tolist())  # the redirected grandchild speaks up
+        expect = init + d
+        out = torch.zeros(n)
+        assert _poll(lambda: (ours.copyToTensor(out) - expect).abs().max().item() <= 2e-4)
+        for r in refs:
+            assert _poll(lambda r=r: _close_to(r.call(op="copy")["values"], expect, 2e-4))
+    finally:
+        ours.close()
+        for r in refs:
+            r.kill()

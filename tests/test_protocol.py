@@ -1,0 +1,117 @@
+"""T2: the tree-join wire protocol, byte for byte (reference src/sharedtensor.c:192-242, 244-332)."""
+import socket
+import struct
+import time
+
+import torch
+
+import sharedtensor
+
+
+def _connect(port):
+    s = socket.create_connection(("127.0.0.1", port), timeout=5)
+    s.settimeout(5)
+    return s
+
+
+def _recv_exact(s, n):
+    buf = b""
+    while len(buf) < n:
+        chunk = s.recv(n - len(buf))
+        assert chunk, "peer closed"
+        buf += chunk
+    return buf
+
+
+def test_handshake_bytes_and_redirect_alternation(free_port):
+    master = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.arange(8.0))
+    try:
+        # the first two inbound connections are adopted: exactly one byte 'Y', then frames
+        c1 = _connect(free_port)
+        assert _recv_exact(c1, 1) == b"Y"
+        c2 = _connect(free_port)
+        assert _recv_exact(c2, 1) == b"Y"
+        a1 = c1.getsockname()
+        a2 = c2.getsockname()
+        # every later one gets 'N' + a raw 16-byte sockaddr_in, alternating right, left, right
+        got = []
+        for _ in range(3):
+            c = _connect(free_port)
+            msg = _recv_exact(c, 17)
+            assert msg[:1] == b"N"
+            family, port_be = struct.unpack("<H", msg[1:3])[0], struct.unpack(">H", msg[3:5])[0]
+            ip = socket.inet_ntoa(msg[5:9])
+            assert family == socket.AF_INET
+            assert msg[9:17] == b"\0" * 8
+            got.append((ip, port_be))
+            assert c.recv(1) == b""  # server closes after the redirect
+            c.close()
+        assert got == [a2, a1, a2], "redirect targets are the children's own source addresses: right, left, right"
+        # the adopted connections carry tensor-scale frames: 4-byte scale + ceil(8/8) sign bytes
+        frame = _recv_exact(c1, 5)
+        scale = struct.unpack("<f", frame[:4])[0]
+        assert scale == 4.0  # rms of 0..7 is 4.18 -> 2^2
+        assert frame[4] == 0b00000001  # only element 0 (value 0) is "not positive"
+        c1.close()
+        c2.close()
+    finally:
+        master.close()
+
+
+def test_tree_shape_of_sequential_joins(free_port):
+    """Joiner 1 -> master.left, 2 -> master.right, 3 -> under right, 4 -> under left (2.2 of the protocol)."""
+    nodes = [sharedtensor.createOrFetch("127.0.0.1", free_port, torch.arange(4.0) + 1)]
+    try:
+        for _ in range(4):
+            nodes.append(sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(4)))
+        st = [n.stats() for n in nodes]
+        m = st[0]
+        assert m["master"] and m["edges"]["up"]["state"] == "free"
+        assert m["edges"]["left"]["peer"] == st[1]["listen_addr"]
+        assert m["edges"]["right"]["peer"] == st[2]["listen_addr"]
+        assert m["redirects"] == 2
+        # third joiner was sent to the right child first, fourth to the left child
+        assert st[2]["edges"]["left"]["peer"] == st[3]["listen_addr"]
+        assert st[1]["edges"]["left"]["peer"] == st[4]["listen_addr"]
+        out = torch.zeros(4)
+        for n in nodes:
+            n.copyToTensor(out)
+            assert torch.equal(out, torch.arange(4.0) + 1)
+    finally:
+        for n in reversed(nodes):
+            n.cfg.rejoin = False
+        for n in reversed(nodes):
+            n.close()
+
+
+def test_late_joiner_receives_state_and_all_zero_state_does_not_hang(free_port):
+    master = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(16))
+    try:
+        t0 = time.time()
+        j = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.ones(16))  # joiner's values are ignored
+        assert time.time() - t0 < 5, "an all-zero shared state must not block the joiner (the reference spins forever)"
+        out = torch.ones(16)
+        j.copyToTensor(out)
+        assert torch.equal(out, torch.zeros(16))
+        j.close()
+    finally:
+        master.close()
+
+
+def test_size_mismatch_is_an_error(free_port):
+    st = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(4, 5, 6, 2))
+    try:
+        import pytest
+
+        with pytest.raises(ValueError, match="Not the right size!"):
+            st.addFromTensor(torch.zeros(10))
+        with pytest.raises(ValueError, match="Not the right size!"):
+            st.copyToTensor(torch.zeros(241))
+        with pytest.raises(TypeError):
+            st.addFromTensor(torch.zeros(240, dtype=torch.float64))
+        st.addFromTensor(torch.ones(240))
+        out = torch.empty(4, 5, 6, 2)
+        st.copyToTensor(out)
+        assert torch.equal(out, torch.ones(4, 5, 6, 2))
+    finally:
+        st.close()
