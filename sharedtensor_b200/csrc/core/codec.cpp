@@ -111,14 +111,17 @@ static int ilog2(int b) {
   return l;
 }
 
-// Decides the exponent code of one block from its residual and value energies.
-static inline int block_code(float sx, float sv, int log2_block, const BlockGate& gate) {
+// Decides the exponent code of one block from its residual energy and the largest magnitude among its
+// values.  The relative cut-off is tied to the largest element, not to the RMS: a step of at least
+// 2^(emax - rel_bits) with rel_bits <= 22 is a whole number of ulps of every element of the block, so
+// stepping the mirror is exact and the stream cannot get stuck re-sending a step that rounds away.
+static inline int block_code(float sx, uint32_t vmax_bits, int log2_block, const BlockGate& gate) {
   if ((f32_bits(sx) >> 23) == 0) return kSilent;  // zero or denormal energy
   int kx = rms_exponent(sx, log2_block);
   if (kx < gate.min_exp) return kSilent;
-  if ((f32_bits(sv) >> 23) != 0) {
-    int kv = rms_exponent(sv, log2_block);
-    if (kx < kv - gate.rel_bits) return kSilent;
+  if ((vmax_bits >> 23) != 0) {
+    int emax = int(vmax_bits >> 23) - 127;
+    if (kx < emax - gate.rel_bits) return kSilent;
   }
   if (kx < kMinExp) return kSilent;
   if (kx > kMaxExp) kx = kMaxExp;
@@ -132,7 +135,7 @@ double encode_block(const float* v, float* k, size_t n, int block, const BlockGa
   const size_t nb = block_scales(n, block);
   double total = 0.0;
   std::vector<float> x(static_cast<size_t>(block), 0.0f), vv(static_cast<size_t>(block), 0.0f);
-  float sx32[128], sv32[128];
+  float sx32[128];
   for (size_t b = 0; b < nb; b++) {
     size_t base = b * size_t(block);
     for (int j = 0; j < block; j++) {
@@ -145,17 +148,19 @@ double encode_block(const float* v, float* k, size_t n, int block, const BlockGa
         x[j] = 0.0f;
       }
     }
-    for (int g = 0; g < m; g++) {
-      sx32[g] = group32_sumsq(&x[size_t(g) * 32]);
-      sv32[g] = group32_sumsq(&vv[size_t(g) * 32]);
+    for (int g = 0; g < m; g++) sx32[g] = group32_sumsq(&x[size_t(g) * 32]);
+    float sx = pairwise_tree(sx32, m);
+    uint32_t vmax = 0;
+    for (int j = 0; j < block; j++) {
+      uint32_t a = f32_bits(vv[j]) & 0x7fffffffu;
+      if (a > vmax) vmax = a;
     }
-    float sx = pairwise_tree(sx32, m), sv = pairwise_tree(sv32, m);
     total += double(sx);
     // The last block may be partly padding: its RMS is taken over the next power of two that
     // holds its valid elements, so that the zeros do not dilute the scale.
     int lb_eff = lb;
     if (base + size_t(block) > n) lb_eff = ilog2(int(n - base));
-    int code = block_code(sx, sv, lb_eff, gate);
+    int code = block_code(sx, vmax, lb_eff, gate);
     scales[b] = uint8_t(code);
     float scale = code ? exp2i(code - 127) : 0.0f;
     for (int g = 0; g < m; g++) {

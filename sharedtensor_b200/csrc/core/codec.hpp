@@ -61,7 +61,7 @@ inline float exp2i(int k) { return bits_f32(uint32_t(k + 127) << 23); }
 
 struct BlockGate {
   int min_exp = -100;  // blocks whose scale exponent is below this stay silent
-  int rel_bits = 22;   // ... or below (exponent of the block's value RMS) - rel_bits
+  int rel_bits = 22;   // ... or below (exponent of the block's largest |value|) - rel_bits
 };
 
 // ---------------------------------------------------------------------------------------------

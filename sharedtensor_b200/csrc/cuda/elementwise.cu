@@ -1,0 +1,413 @@
+// Bandwidth kernels around the sync round, sm_100a:
+//   snapshot      copyToTensor            out = values                  (reference src/sharedtensor.c:442-444)
+//   add / sub_add addFromTensor/pushUpdate values += d | values += a-b  (reference 338-343; one target instead of four)
+//   table_scales  per-tensor energies and exponent codes over a flat arena (the reference's README lists
+//                 "table sync" with per-tensor magnitudes as a TODO)
+//   sample_sqerr  convergence probe for benchmarks and tests
+//   delay         device-side pacing
+//   snapshot_join values -> a new child's replica and -> the new link's mirror in one pass
+//   tensor_*      tensor-scale frames (reference wire format) encoded/decoded on the device for TCP edges
+// All are grid-stride kernels with 16-byte accesses sized to 148 SMs; none waits on anything.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "round.h"
+
+namespace st {
+
+namespace {
+
+constexpr int kEwThreads = 256;
+
+inline int ew_blocks(int64_t work_items, int per_sm = 8) {
+  int64_t b = (work_items + kEwThreads - 1) / kEwThreads;
+  int64_t cap = 148 * per_sm;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return int(b);
+}
+
+__device__ __forceinline__ float4 ldg_stream(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void red_add_v4(float* p, float4 d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(d.x), "f"(d.y), "f"(d.z), "f"(d.w) : "memory");
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// snapshot
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kEwThreads) snapshot_f32_vec(const float4* __restrict__ src, float4* __restrict__ dst, int64_t n4) {
+  int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * kEwThreads;
+  // four independent 16-byte loads in flight per thread
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    float4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+    __stcs(dst + i, a);
+    __stcs(dst + i + stride, b);
+    __stcs(dst + i + 2 * stride, c);
+    __stcs(dst + i + 3 * stride, d);
+  }
+  for (; i < n4; i += stride) __stcs(dst + i, src[i]);
+}
+__global__ void snapshot_f32_scalar(const float* __restrict__ src, float* __restrict__ dst, int64_t begin, int64_t n) {
+  int64_t i = begin + int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (; i < n; i += stride) dst[i] = src[i];
+}
+__global__ void __launch_bounds__(kEwThreads) snapshot_bf16_vec(const float4* __restrict__ src, uint2* __restrict__ dst, int64_t n4) {
+  int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * kEwThreads;
+  for (; i < n4; i += stride) {
+    float4 a = src[i];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    dst[i] = o;
+  }
+}
+__global__ void snapshot_bf16_scalar(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t begin, int64_t n) {
+  int64_t i = begin + int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+int launch_snapshot_f32(const float* values, float* out, int64_t n, void* stream_v) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream_v);
+  int64_t n4 = aligned16(out) && aligned16(values) ? n / 4 : 0;
+  if (n4) snapshot_f32_vec<<<ew_blocks(n4 / 4 + 1), kEwThreads, 0, s>>>(reinterpret_cast<const float4*>(values), reinterpret_cast<float4*>(out), n4);
+  if (n4 * 4 < n) snapshot_f32_scalar<<<ew_blocks(n - n4 * 4), kEwThreads, 0, s>>>(values, out, n4 * 4, n);
+  return int(cudaGetLastError());
+}
+int launch_snapshot_bf16(const float* values, void* out, int64_t n, void* stream_v) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream_v);
+  bool al = aligned16(values) && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+  int64_t n4 = al ? n / 4 : 0;
+  if (n4) snapshot_bf16_vec<<<ew_blocks(n4), kEwThreads, 0, s>>>(reinterpret_cast<const float4*>(values), reinterpret_cast<uint2*>(out), n4);
+  if (n4 * 4 < n) snapshot_bf16_scalar<<<ew_blocks(n - n4 * 4), kEwThreads, 0, s>>>(values, static_cast<__nv_bfloat16*>(out), n4 * 4, n);
+  return int(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// add / sub_add
+// ---------------------------------------------------------------------------------------------
+template <bool SUB, bool ATOMIC>
+__global__ void __launch_bounds__(kEwThreads) add_vec(float4* __restrict__ values, const float4* __restrict__ a, const float4* __restrict__ b,
+                                                      int64_t n4, uint8_t* __restrict__ tile_state, int n_tiles) {
+  int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * kEwThreads;
+  for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
+  for (; i + stride < n4; i += 2 * stride) {
+    float4 d0 = ldg_stream(a + i), d1 = ldg_stream(a + i + stride);
+    if (SUB) {
+      float4 o0 = ldg_stream(b + i), o1 = ldg_stream(b + i + stride);
+      d0.x -= o0.x; d0.y -= o0.y; d0.z -= o0.z; d0.w -= o0.w;
+      d1.x -= o1.x; d1.y -= o1.y; d1.z -= o1.z; d1.w -= o1.w;
+    }
+    if (ATOMIC) {
+      red_add_v4(reinterpret_cast<float*>(values + i), d0);
+      red_add_v4(reinterpret_cast<float*>(values + i + stride), d1);
+    } else {
+      float4 v0 = values[i], v1 = values[i + stride];
+      v0.x += d0.x; v0.y += d0.y; v0.z += d0.z; v0.w += d0.w;
+      v1.x += d1.x; v1.y += d1.y; v1.z += d1.z; v1.w += d1.w;
+      values[i] = v0;
+      values[i + stride] = v1;
+    }
+  }
+  for (; i < n4; i += stride) {
+    float4 d0 = ldg_stream(a + i);
+    if (SUB) {
+      float4 o0 = ldg_stream(b + i);
+      d0.x -= o0.x; d0.y -= o0.y; d0.z -= o0.z; d0.w -= o0.w;
+    }
+    if (ATOMIC) {
+      red_add_v4(reinterpret_cast<float*>(values + i), d0);
+    } else {
+      float4 v0 = values[i];
+      v0.x += d0.x; v0.y += d0.y; v0.z += d0.z; v0.w += d0.w;
+      values[i] = v0;
+    }
+  }
+}
+template <bool SUB, bool ATOMIC>
+__global__ void add_scalar(float* __restrict__ values, const float* __restrict__ a, const float* __restrict__ b, int64_t begin, int64_t n,
+                           uint8_t* __restrict__ tile_state, int n_tiles, int mark) {
+  int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  if (mark)
+    for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
+  for (i += begin; i < n; i += stride) {
+    float d = SUB ? a[i] - b[i] : a[i];
+    if (ATOMIC)
+      atomicAdd(values + i, d);
+    else
+      values[i] += d;
+  }
+}
+
+template <bool SUB>
+static int launch_add_t(float* values, const float* a, const float* b, int64_t n, uint8_t* tile_state, int n_tiles, int atomic,
+                        cudaStream_t s) {
+  bool al = aligned16(values) && aligned16(a) && (!SUB || aligned16(b));
+  int64_t n4 = al ? n / 4 : 0;
+  if (n4) {
+    int blocks = ew_blocks(n4 / 2 + 1);
+    if (atomic)
+      add_vec<SUB, true><<<blocks, kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), reinterpret_cast<const float4*>(a),
+                                                       reinterpret_cast<const float4*>(b), n4, tile_state, n_tiles);
+    else
+      add_vec<SUB, false><<<blocks, kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), reinterpret_cast<const float4*>(a),
+                                                        reinterpret_cast<const float4*>(b), n4, tile_state, n_tiles);
+  }
+  if (n4 * 4 < n) {
+    int blocks = ew_blocks(n - n4 * 4);
+    if (atomic)
+      add_scalar<SUB, true><<<blocks, kEwThreads, 0, s>>>(values, a, b, n4 * 4, n, tile_state, n_tiles, n4 == 0);
+    else
+      add_scalar<SUB, false><<<blocks, kEwThreads, 0, s>>>(values, a, b, n4 * 4, n, tile_state, n_tiles, n4 == 0);
+  }
+  return int(cudaGetLastError());
+}
+
+int launch_add(float* values, const float* delta, int64_t n, uint8_t* tile_state, int n_tiles, int atomic, void* stream) {
+  return launch_add_t<false>(values, delta, nullptr, n, tile_state, n_tiles, atomic, static_cast<cudaStream_t>(stream));
+}
+int launch_sub_add(float* values, const float* neu, const float* old, int64_t n, uint8_t* tile_state, int n_tiles, int atomic,
+                   void* stream) {
+  return launch_add_t<true>(values, neu, old, n, tile_state, n_tiles, atomic, static_cast<cudaStream_t>(stream));
+}
+
+__global__ void fill_state_kernel(uint8_t* s, int n, uint8_t v) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) s[i] = v;
+}
+int launch_fill_state(uint8_t* tile_state, int n_tiles, int value, void* stream) {
+  fill_state_kernel<<<(n_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tile_state, n_tiles, uint8_t(value));
+  return int(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// table_scales: two passes.  Pass 1: every CTA owns a contiguous chunk of one segment and writes one
+// partial sum (double) into scratch.  Pass 2: one warp per segment adds that segment's partials in a
+// fixed order (deterministic result) and derives the exponent code of the segment's RMS.
+// ---------------------------------------------------------------------------------------------
+constexpr int64_t kTsChunk = 1 << 16;  // elements per pass-1 CTA
+
+int64_t table_scales_scratch_doubles(int n_seg, int64_t n_total) { return n_total / kTsChunk + 2 * int64_t(n_seg) + 2; }
+
+// chunk c of the arena's chunk list: segment s covers chunks [first[s], first[s+1])
+__global__ void __launch_bounds__(256) table_partial_kernel(const float* __restrict__ x, const int64_t* __restrict__ off, int n_seg,
+                                                            const int64_t* __restrict__ first_chunk, double* __restrict__ partials) {
+  __shared__ double red[8];
+  __shared__ int s_seg;
+  const int64_t c = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = n_seg - 1;  // last segment whose first chunk is <= c
+    while (lo < hi) {
+      int mid = (lo + hi + 1) / 2;
+      if (first_chunk[mid] <= c) lo = mid; else hi = mid - 1;
+    }
+    s_seg = lo;
+  }
+  __syncthreads();
+  const int seg = s_seg;
+  const int64_t begin = off[seg] + (c - first_chunk[seg]) * kTsChunk;
+  const int64_t end = min(begin + kTsChunk, off[seg + 1]);
+  double acc = 0.0;
+  for (int64_t i = begin + threadIdx.x; i < end; i += 256) {
+    float v = x[i];
+    acc += double(v) * double(v);
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < 8; w++) t += red[w];
+    partials[c] = t;
+  }
+}
+__global__ void table_final_kernel(const int64_t* __restrict__ off, int n_seg, const int64_t* __restrict__ first_chunk,
+                                   const double* __restrict__ partials, double* __restrict__ out_sumsq, int8_t* __restrict__ out_exp) {
+  int seg = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (seg >= n_seg) return;
+  const int lane = threadIdx.x & 31;
+  double acc = 0.0;
+  for (int64_t c = first_chunk[seg] + lane; c < first_chunk[seg + 1]; c += 32) acc += partials[c];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    out_sumsq[seg] = acc;
+    int64_t cnt = off[seg + 1] - off[seg];
+    int e = -128;
+    if (cnt > 0 && acc > 0.0) {
+      double rms = sqrt(acc / double(cnt));
+      int ex;
+      frexp(rms, &ex);
+      e = ex - 1;
+      if (e < -126) e = -128;
+      if (e > 127) e = 127;
+    }
+    out_exp[seg] = int8_t(e);
+  }
+}
+__global__ void table_chunks_kernel(const int64_t* __restrict__ off, int n_seg, int64_t* __restrict__ first_chunk) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int64_t c = 0;
+    for (int s = 0; s < n_seg; s++) {
+      first_chunk[s] = c;
+      c += (off[s + 1] - off[s] + kTsChunk - 1) / kTsChunk;
+    }
+    first_chunk[n_seg] = c;
+  }
+}
+
+int launch_table_scales(const float* x, const int64_t* seg_offsets_dev, int n_seg, int64_t n_total, double* scratch, double* out_sumsq,
+                        int8_t* out_exp, void* stream_v) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream_v);
+  // scratch layout: [first_chunk: n_seg+1 int64][partials: up to n_total/chunk + n_seg doubles]
+  int64_t* first_chunk = reinterpret_cast<int64_t*>(scratch);
+  double* partials = scratch + (n_seg + 1);
+  int64_t max_chunks = n_total / kTsChunk + n_seg;
+  table_chunks_kernel<<<1, 32, 0, s>>>(seg_offsets_dev, n_seg, first_chunk);
+  // the exact chunk count lives on the device; launching the upper bound is harmless because the
+  // surplus CTAs map to chunks past the end of the last segment and add zero-length ranges
+  table_partial_kernel<<<unsigned(max_chunks), 256, 0, s>>>(x, seg_offsets_dev, n_seg, first_chunk, partials);
+  table_final_kernel<<<(n_seg + 7) / 8, 256, 0, s>>>(seg_offsets_dev, n_seg, first_chunk, partials, out_sumsq, out_exp);
+  return int(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// sample_sqerr / delay / snapshot_join
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) sample_sqerr_kernel(const float* __restrict__ a, int64_t stride_a, const float* __restrict__ b,
+                                                           int64_t count, double* __restrict__ out) {
+  double acc = 0.0;
+  unsigned long long nan = 0;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < count; i += int64_t(gridDim.x) * 256) {
+    float d = a[i * stride_a] - b[i];
+    if (d != d) nan++;
+    acc += double(d) * double(d);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    nan += __shfl_xor_sync(0xffffffffu, nan, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(out, acc);
+    if (nan) atomicAdd(reinterpret_cast<unsigned long long*>(out + 1), nan);
+  }
+}
+int launch_sample_sqerr(const float* a, int64_t stride, const float* b, int64_t count, double* out, void* stream) {
+  sample_sqerr_kernel<<<ew_blocks(count, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, stride, b, count, out);
+  return int(cudaGetLastError());
+}
+
+__global__ void delay_kernel(uint64_t ns) {
+  uint64_t t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  // bounded by construction: the loop ends when the clock passes t0 + ns, and by an iteration cap
+  for (uint64_t it = 0; it < (1ull << 32); it++) {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 >= ns) break;
+    __nanosleep(200);
+  }
+}
+int launch_delay(uint64_t ns, void* stream) {
+  if (ns > 1000ull * 1000 * 1000) ns = 1000ull * 1000 * 1000;  // never longer than a second
+  delay_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(ns);
+  return int(cudaGetLastError());
+}
+
+__global__ void __launch_bounds__(kEwThreads) snapshot_join_kernel(const float4* __restrict__ values, float4* __restrict__ dst,
+                                                                   float4* __restrict__ mirror, int64_t n4) {
+  int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * kEwThreads;
+  for (; i < n4; i += stride) {
+    float4 v = values[i];
+    dst[i] = v;
+    mirror[i] = v;
+  }
+}
+int launch_snapshot_join(const float* values, float* dst_values, float* mirror, int64_t n_padded, void* stream) {
+  int64_t n4 = n_padded / 4;
+  snapshot_join_kernel<<<ew_blocks(n4), kEwThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(values), reinterpret_cast<float4*>(dst_values), reinterpret_cast<float4*>(mirror), n4);
+  return int(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// tensor-scale frames on the device (one scale for the whole tensor, 1 bit per element)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) tensor_sumsq_kernel(const float* __restrict__ v, const float* __restrict__ k, int64_t n,
+                                                           double* __restrict__ out2) {
+  double ax = 0.0, av = 0.0;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n; i += int64_t(gridDim.x) * 256) {
+    float a = v[i], x = a - k[i];
+    ax += double(x) * double(x);
+    av += double(a) * double(a);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    ax += __shfl_xor_sync(0xffffffffu, ax, o);
+    av += __shfl_xor_sync(0xffffffffu, av, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(out2, ax);
+    atomicAdd(out2 + 1, av);
+  }
+}
+int launch_tensor_sumsq(const float* v, const float* k, int64_t n, double* out2, void* stream) {
+  tensor_sumsq_kernel<<<ew_blocks(n, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(v, k, n, out2);
+  return int(cudaGetLastError());
+}
+// words[i/32] bit i%32 = !(v-k > 0); k steps by -/+ scale.  n is padded by the caller to a multiple of 32
+// with v = k = 0 beyond the valid range; `n_valid` stops the mirror update there.
+__global__ void __launch_bounds__(256) tensor_encode_kernel(const float* __restrict__ v, float* __restrict__ k, int64_t n_valid, float scale,
+                                                            uint32_t* __restrict__ words, int64_t n_words) {
+  const int lane = threadIdx.x & 31;
+  for (int64_t w = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 5; w < n_words; w += (int64_t(gridDim.x) * 256) >> 5) {
+    int64_t i = w * 32 + lane;
+    bool valid = i < n_valid;
+    float kk = valid ? k[i] : 0.f;
+    float x = valid ? v[i] - kk : 0.f;
+    bool neg = valid && !(x > 0.f);
+    uint32_t word = __ballot_sync(0xffffffffu, neg);
+    if (valid && scale != 0.f) k[i] = kk + (neg ? -scale : scale);
+    if (lane == 0) words[w] = word;
+  }
+}
+int launch_tensor_encode(const float* v, float* k, int64_t n, float scale, uint32_t* words, void* stream) {
+  int64_t n_words = (n + 31) / 32;
+  tensor_encode_kernel<<<ew_blocks(n_words * 32, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(v, k, n, scale, words, n_words);
+  return int(cudaGetLastError());
+}
+__global__ void __launch_bounds__(256) tensor_decode_kernel(const uint32_t* __restrict__ words, float scale, int64_t n, float* __restrict__ v,
+                                                            float* __restrict__ k, uint8_t* __restrict__ tile_state, int n_tiles) {
+  int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * 256;
+  if (tile_state)
+    for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
+  for (; i < n; i += stride) {
+    float f = ((words[i >> 5] >> (i & 31)) & 1u) ? -scale : scale;
+    v[i] += f;
+    if (k) k[i] += f;
+  }
+}
+int launch_tensor_decode(const uint32_t* words, float scale, int64_t n, float* v, float* k, uint8_t* tile_state, void* stream) {
+  if (scale == 0.f) return 0;
+  int n_tiles = int((n + kTile - 1) / kTile);
+  tensor_decode_kernel<<<ew_blocks(n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(words, scale, n, v, k, tile_state, n_tiles);
+  return int(cudaGetLastError());
+}
+
+}  // namespace st

@@ -1,0 +1,458 @@
+#include "engine.hpp"
+
+#include <cuda_runtime_api.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <stdexcept>
+
+namespace st {
+
+namespace {
+cudaStream_t S(void* p) { return static_cast<cudaStream_t>(p); }
+cudaEvent_t E(void* p) { return static_cast<cudaEvent_t>(p); }
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+}  // namespace
+
+void GpuReplica::check(int e, const char* what) {
+  if (e != int(cudaSuccess)) {
+    std::string msg = std::string(what) + ": " + cudaGetErrorString(cudaError_t(e));
+    error_ = msg;
+    throw std::runtime_error("sharedtensor GPU engine: " + msg);
+  }
+}
+
+GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(device), n_(n), cfg_(cfg) {
+  if (n <= 0) throw std::invalid_argument("shared tensor needs at least one element");
+  if (cfg.block < 32 || cfg.block > 4096 || (cfg.block & (cfg.block - 1)))
+    throw std::invalid_argument("block must be a power of two in 32..4096");
+  if (cfg.ring_slots < 2 || cfg.ring_slots > 64) throw std::invalid_argument("ring_slots must be in 2..64");
+  DeviceGuard g(device_);
+  n_tiles_ = int((n + kTile - 1) / kTile);
+  n_padded_ = int64_t(n_tiles_) * kTile;
+  int lb = 0;
+  while ((1 << lb) < cfg.block) lb++;
+  const int spt = kTile >> lb;
+  const int pb = 4 * kWordsPerTile + (spt < 16 ? 16 : spt);
+  layout_.off_payload = 0;
+  layout_.off_flags = align_up(size_t(cfg.ring_slots) * n_tiles_ * pb, 256);
+  layout_.off_credit = layout_.off_flags + align_up(size_t(cfg.ring_slots) * n_tiles_ * 4, 256);
+  layout_.bytes = layout_.off_credit + align_up(size_t(n_tiles_) * 4, 256);
+
+  std::string err;
+  values_ = vmm_alloc(device_, size_t(n_padded_) * 4, cfg.shareable, &err);
+  if (!values_.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate values: " + err);
+  links_.resize(kMaxLinks);
+  blocks_.resize(kMaxRings);
+  peers_.resize(kMaxRings);
+
+  check(cudaMalloc(reinterpret_cast<void**>(&ctrl_), size_t(n_tiles_) * 16), "cudaMalloc ctrl");
+  check(cudaMalloc(reinterpret_cast<void**>(&sent_), size_t(n_tiles_) * 8), "cudaMalloc sent");
+  check(cudaMalloc(reinterpret_cast<void**>(&tile_state_), size_t(n_tiles_)), "cudaMalloc tile_state");
+  check(cudaMalloc(reinterpret_cast<void**>(&worklist_), size_t(n_tiles_) * 4), "cudaMalloc worklist");
+  check(cudaMalloc(reinterpret_cast<void**>(&work_count_), 2 * 4), "cudaMalloc work_count");
+  check(cudaMalloc(reinterpret_cast<void**>(&status_), kStWords * 8), "cudaMalloc status");
+  check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), kStWords * 8), "cudaMallocHost status");
+  check(cudaMemset(ctrl_, 0, size_t(n_tiles_) * 16), "memset");
+  check(cudaMemset(sent_, 0, size_t(n_tiles_) * 8), "memset");
+  check(cudaMemset(tile_state_, 1, size_t(n_tiles_)), "memset");
+  check(cudaMemset(work_count_, 0, 8), "memset");
+  check(cudaMemset(status_, 0, kStWords * 8), "memset");
+  std::memset(status_host_, 0, kStWords * 8);
+
+  int lo = 0, hi = 0;
+  cudaDeviceGetStreamPriorityRange(&lo, &hi);
+  cudaStream_t s;
+  check(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi), "cudaStreamCreate");
+  comm_ = s;
+  cudaEvent_t e1, e2;
+  check(cudaEventCreateWithFlags(&e1, cudaEventDisableTiming), "cudaEventCreate");
+  check(cudaEventCreateWithFlags(&e2, cudaEventDisableTiming), "cudaEventCreate");
+  ev_user_ = e1;
+  ev_comm_ = e2;
+  for (int i = 0; i < (cfg.rounds_in_flight < 1 ? 1 : cfg.rounds_in_flight); i++) {
+    cudaEvent_t e;
+    check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+    ev_round_.push_back(e);
+  }
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_);
+  ctas_ = cfg.comm_ctas > 0 ? cfg.comm_ctas : sms;
+
+  params_.values = values();
+  params_.n = n_;
+  params_.n_tiles = n_tiles_;
+  params_.ring_slots = cfg.ring_slots;
+  params_.log2_block = lb;
+  params_.scales_per_tile = spt;
+  params_.payload_bytes = pb;
+  params_.min_exp = cfg.min_exp;
+  params_.rel_bits = cfg.rel_bits;
+  params_.ctrl = ctrl_;
+  params_.sent = sent_;
+  params_.tile_state = tile_state_;
+  params_.worklist = worklist_;
+  params_.work_count = work_count_;
+  params_.status = status_;
+  params_.atomic_values = cfg.atomic_values ? 1 : 0;
+  check(cudaDeviceSynchronize(), "init");
+}
+
+GpuReplica::~GpuReplica() {
+  stop_engine();
+  DeviceGuard g(device_);
+  if (comm_) cudaStreamSynchronize(S(comm_));
+  for (auto& p : peers_) {
+    if (p.rx_seq) cudaFree(p.rx_seq);
+    if (p.tx_seq) cudaFree(p.tx_seq);
+  }
+  for (auto& l : links_) vmm_free(&l.mirror);
+  for (auto& b : blocks_) vmm_free(&b.mem);
+  vmm_free(&values_);
+  cudaFree(ctrl_);
+  cudaFree(sent_);
+  cudaFree(tile_state_);
+  cudaFree(worklist_);
+  cudaFree(work_count_);
+  cudaFree(status_);
+  if (status_host_) cudaFreeHost(status_host_);
+  for (void* e : ev_round_) cudaEventDestroy(E(e));
+  if (ev_user_) cudaEventDestroy(E(ev_user_));
+  if (ev_comm_) cudaEventDestroy(E(ev_comm_));
+  if (comm_) cudaStreamDestroy(S(comm_));
+}
+
+// ---------------------------------------------------------------------------------------------
+// topology
+// ---------------------------------------------------------------------------------------------
+int GpuReplica::add_link() {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  for (int i = 0; i < kMaxLinks; i++) {
+    if (!links_[i].used) {
+      std::string err;
+      publish_pending();
+      links_[i].mirror = vmm_alloc(device_, size_t(n_padded_) * 4, false, &err);
+      if (!links_[i].mirror.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate mirror: " + err);
+      links_[i].used = true;
+      rebuild_params();
+      return i;
+    }
+  }
+  return -1;
+}
+
+void GpuReplica::remove_link(int link) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used) return;
+  publish_pending();
+  for (auto& p : peers_) {
+    if (p.used && p.link == link) {
+      p.used = false;
+      cudaFree(p.rx_seq);
+      cudaFree(p.tx_seq);
+      p.rx_seq = p.tx_seq = nullptr;
+    }
+  }
+  vmm_free(&links_[link].mirror);
+  links_[link].used = false;
+  rebuild_params();
+}
+
+int GpuReplica::alloc_edge_block() {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  for (int i = 0; i < kMaxRings; i++) {
+    if (!blocks_[i].used) {
+      std::string err;
+      blocks_[i].mem = vmm_alloc(device_, layout_.bytes, cfg_.shareable, &err);
+      if (!blocks_[i].mem.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate edge block: " + err);
+      blocks_[i].used = true;
+      return i;
+    }
+  }
+  return -1;
+}
+
+void GpuReplica::free_edge_block(int id) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (id < 0 || id >= kMaxRings || !blocks_[id].used) return;
+  cudaStreamSynchronize(S(comm_));
+  vmm_free(&blocks_[id].mem);
+  blocks_[id].used = false;
+}
+
+int GpuReplica::attach_peer(int link, int local_block, void* remote_base) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("attach_peer: no such link");
+  if (local_block < 0 || local_block >= kMaxRings || !blocks_[local_block].used)
+    throw std::invalid_argument("attach_peer: no such edge block");
+  for (int i = 0; i < kMaxRings; i++) {
+    if (!peers_[i].used) {
+      Peer& p = peers_[i];
+      publish_pending();
+      check(cudaMalloc(reinterpret_cast<void**>(&p.rx_seq), size_t(n_tiles_) * 4), "cudaMalloc rx_seq");
+      check(cudaMalloc(reinterpret_cast<void**>(&p.tx_seq), size_t(n_tiles_) * 4), "cudaMalloc tx_seq");
+      check(cudaMemset(p.rx_seq, 0, size_t(n_tiles_) * 4), "memset");
+      check(cudaMemset(p.tx_seq, 0, size_t(n_tiles_) * 4), "memset");
+      p.link = link;
+      p.local_block = local_block;
+      p.remote = static_cast<uint8_t*>(remote_base);
+      p.used = true;
+      // whatever the link still had to say must be looked at again
+      launch_fill_state(tile_state_, n_tiles_, 1, comm_);
+      rebuild_params();
+      return i;
+    }
+  }
+  return -1;
+}
+
+void GpuReplica::detach_peer(int peer) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (peer < 0 || peer >= kMaxRings || !peers_[peer].used) return;
+  publish_pending();
+  Peer& p = peers_[peer];
+  p.used = false;
+  cudaFree(p.rx_seq);
+  cudaFree(p.tx_seq);
+  p.rx_seq = p.tx_seq = nullptr;
+  rebuild_params();
+}
+
+int GpuReplica::n_links() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  int c = 0;
+  for (auto& l : links_) c += l.used;
+  return c;
+}
+int GpuReplica::n_peers() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  int c = 0;
+  for (auto& p : peers_) c += p.used;
+  return c;
+}
+
+void GpuReplica::publish_pending() {
+  // Ring numbering is about to change.  Every round ends with its publish kernel, so once the
+  // stream has drained nothing refers to the old numbering any more.
+  cudaStreamSynchronize(S(comm_));
+}
+
+void GpuReplica::rebuild_params() {
+  int dense = 0;
+  for (int i = 0; i < kMaxLinks; i++) {
+    map_link_[i] = -1;
+    params_.mirror[i] = nullptr;
+  }
+  // only links that have at least one peer take part in rounds
+  for (int i = 0; i < kMaxLinks; i++) {
+    if (!links_[i].used) continue;
+    bool has_peer = false;
+    for (auto& p : peers_) has_peer |= p.used && p.link == i;
+    if (!has_peer) continue;
+    map_link_[i] = dense;
+    params_.mirror[dense] = static_cast<float*>(links_[i].mirror.ptr);
+    dense++;
+  }
+  params_.n_links = dense;
+  int r = 0;
+  for (auto& p : peers_) {
+    if (!p.used) continue;
+    uint8_t* local = static_cast<uint8_t*>(blocks_[p.local_block].mem.ptr);
+    InRing& in = params_.in[r];
+    in.payload = local + layout_.off_payload;
+    in.flags = reinterpret_cast<const uint32_t*>(local + layout_.off_flags);
+    in.rx_seq = p.rx_seq;
+    in.credit_remote = reinterpret_cast<uint32_t*>(p.remote + layout_.off_credit);
+    in.link = map_link_[p.link];
+    OutRing& out = params_.out[r];
+    out.payload_remote = p.remote + layout_.off_payload;
+    out.flags_remote = reinterpret_cast<uint32_t*>(p.remote + layout_.off_flags);
+    out.tx_seq = p.tx_seq;
+    out.credit = reinterpret_cast<const uint32_t*>(local + layout_.off_credit);
+    out.link = map_link_[p.link];
+    r++;
+  }
+  params_.n_in = r;
+  params_.n_out = r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// data path
+// ---------------------------------------------------------------------------------------------
+void GpuReplica::order_after_user(void* user_stream) {
+  if (user_stream == comm_) return;
+  check(cudaEventRecord(E(ev_user_), S(user_stream)), "cudaEventRecord");
+  check(cudaStreamWaitEvent(S(comm_), E(ev_user_), 0), "cudaStreamWaitEvent");
+}
+void GpuReplica::order_user_after(void* user_stream) {
+  if (user_stream == comm_) return;
+  check(cudaEventRecord(E(ev_comm_), S(comm_)), "cudaEventRecord");
+  check(cudaStreamWaitEvent(S(user_stream), E(ev_comm_), 0), "cudaStreamWaitEvent");
+}
+
+void GpuReplica::load_values(const float* src, void* user_stream) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  order_after_user(user_stream);
+  check(cudaMemcpyAsync(values(), src, size_t(n_) * 4, cudaMemcpyDeviceToDevice, S(comm_)), "cudaMemcpyAsync");
+  check(launch_fill_state(tile_state_, n_tiles_, 1, comm_), "fill_state");
+  launches_ += 1;
+  order_user_after(user_stream);
+}
+
+void GpuReplica::add(const float* delta, void* user_stream) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  order_after_user(user_stream);
+  check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
+  launches_ += 1;
+  order_user_after(user_stream);
+}
+
+void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  order_after_user(user_stream);
+  check(launch_sub_add(values(), neu, old, n_, tile_state_, n_tiles_, 0, comm_), "sub_add kernel");
+  launches_ += 1;
+  order_user_after(user_stream);
+}
+
+void GpuReplica::snapshot(float* out, void* user_stream) {
+  DeviceGuard g(device_);
+  check(launch_snapshot_f32(values(), out, n_, user_stream), "snapshot kernel");
+  launches_ += 1;
+}
+
+void GpuReplica::snapshot_bf16(void* out, void* user_stream) {
+  DeviceGuard g(device_);
+  check(launch_snapshot_bf16(values(), out, n_, user_stream), "snapshot kernel");
+  launches_ += 1;
+}
+
+void GpuReplica::copy_mirror_from_values(int link) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
+  check(cudaMemcpyAsync(links_[link].mirror.ptr, values(), size_t(n_padded_) * 4, cudaMemcpyDeviceToDevice, S(comm_)),
+        "cudaMemcpyAsync");
+}
+
+void GpuReplica::push_snapshot(int link, float* remote_values) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
+  check(launch_snapshot_join(values(), remote_values, static_cast<float*>(links_[link].mirror.ptr), n_padded_, comm_),
+        "snapshot_join kernel");
+  launches_ += 1;
+  check(cudaStreamSynchronize(S(comm_)), "snapshot_join");
+}
+
+void GpuReplica::round(bool do_rx, bool do_tx) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (params_.n_in == 0 && params_.n_out == 0) return;
+  params_.round = round_no_++;
+  params_.do_rx = do_rx ? 1 : 0;
+  params_.do_tx = do_tx ? 1 : 0;
+  check(launch_round_begin(params_, comm_), "round_begin kernel");
+  check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
+  check(launch_round_publish(params_, comm_), "round_publish kernel");
+  launches_ += 3;
+}
+
+void GpuReplica::sync() {
+  DeviceGuard g(device_);
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+}
+
+std::vector<uint64_t> GpuReplica::status() {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  std::vector<uint64_t> out(kStWords);
+  check(cudaMemcpyAsync(status_host_, status_, kStWords * 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  std::memcpy(out.data(), status_host_, kStWords * 8);
+  return out;
+}
+
+std::string GpuReplica::last_error() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  return error_;
+}
+
+// ---------------------------------------------------------------------------------------------
+// engine thread
+// ---------------------------------------------------------------------------------------------
+void GpuReplica::start_engine() {
+  if (engine_on_.exchange(true)) return;
+  engine_stop_.store(false);
+  engine_ = std::thread([this] { engine_loop(); });
+}
+
+void GpuReplica::stop_engine() {
+  if (!engine_on_.load()) return;
+  engine_stop_.store(true);
+  if (engine_.joinable()) engine_.join();
+  engine_on_.store(false);
+}
+
+void GpuReplica::engine_loop() {
+  cudaSetDevice(device_);
+  const size_t depth = ev_round_.size();
+  uint64_t r = 0;
+  uint64_t idle_rounds = 0;
+  while (!engine_stop_.load()) {
+    bool launched = false;
+    try {
+      std::lock_guard<std::mutex> lk(mu_);
+      if (params_.n_in + params_.n_out > 0) {
+        params_.round = round_no_++;
+        params_.do_rx = 1;
+        params_.do_tx = 1;
+        check(launch_round_begin(params_, comm_), "round_begin kernel");
+        check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
+        check(launch_round_publish(params_, comm_), "round_publish kernel");
+        launches_ += 3;
+        // the work count of this round tells the thread whether anything is moving
+        cudaMemcpyAsync(status_host_ + kStLastWorkCount, status_ + kStLastWorkCount, 8, cudaMemcpyDeviceToHost, S(comm_));
+        cudaEventRecord(E(ev_round_[r % depth]), S(comm_));
+        launched = true;
+      }
+    } catch (const std::exception&) {
+      break;  // error_ holds the reason; the API surfaces it on the next call
+    }
+    if (!launched) {
+      ::usleep(1000);
+      continue;
+    }
+    r++;
+    if (r >= depth) cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
+    if (status_host_[kStLastWorkCount] == 0) {
+      idle_rounds++;
+      if (idle_rounds > 2 && cfg_.idle_sleep_us > 0) ::usleep(useconds_t(cfg_.idle_sleep_us));
+    } else {
+      idle_rounds = 0;
+    }
+  }
+  cudaStreamSynchronize(S(comm_));
+}
+
+}  // namespace st

@@ -1,0 +1,145 @@
+// GPU replica: device-resident values and mirrors, ring bookkeeping, and the stream/thread that runs
+// sync rounds.  This is the device-side counterpart of CpuNode (../core/node.hpp); it knows nothing
+// about sockets or membership, which live in gpu_node.hpp.
+//
+// Stream discipline: every kernel that writes `values` or a mirror runs on the replica's own comm
+// stream, so those kernels never race with each other; user-stream work is ordered against them with
+// events.  copyToTensor reads `values` from the caller's stream and may overlap a round (per-element
+// tearing is impossible, per-tensor tearing is allowed, as in the reference, src/sharedtensor.c:442-444).
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <cstdint>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "round.h"
+#include "vmm.hpp"
+
+namespace st {
+
+struct GpuConfig {
+  int block = 32;            // scale block, power of two 32..4096
+  int ring_slots = 4;
+  int min_exp = -60;
+  int rel_bits = 22;
+  int comm_ctas = 0;         // 0 = one CTA per SM
+  bool shareable = true;     // allocate edge blocks and values with the VMM API (needed across processes)
+  bool atomic_values = false;
+  int rounds_in_flight = 2;
+  int idle_sleep_us = 200;
+};
+
+struct EdgeBlockLayout {
+  size_t off_payload = 0, off_flags = 0, off_credit = 0, bytes = 0;
+};
+
+class GpuReplica {
+ public:
+  GpuReplica(int device, int64_t n, const GpuConfig& cfg);
+  ~GpuReplica();
+  GpuReplica(const GpuReplica&) = delete;
+
+  int device() const { return device_; }
+  int64_t size() const { return n_; }
+  int64_t padded() const { return n_padded_; }
+  int tiles() const { return n_tiles_; }
+  float* values() const { return static_cast<float*>(values_.ptr); }
+  const VmmBlock& values_block() const { return values_; }
+  float* mirror(int link) const { return static_cast<float*>(links_[link].mirror.ptr); }
+  EdgeBlockLayout edge_layout() const { return layout_; }
+  void* comm_stream() const { return comm_; }
+
+  // ---- topology ----
+  int add_link();                      // new mirror (zero); returns link id, -1 if none is free
+  void remove_link(int link);          // detaches the link's peers and frees the mirror
+  int alloc_edge_block();              // zeroed local block a neighbour will store into
+  void free_edge_block(int id);
+  const VmmBlock& edge_block(int id) const { return blocks_[id].mem; }
+  // Frames from the neighbour arrive in local block `local_block`; frames to it go to its block, mapped
+  // at `remote_base` in this process (same layout).  Returns a peer id.
+  int attach_peer(int link, int local_block, void* remote_base);
+  void detach_peer(int peer);
+  int n_links() const;
+  int n_peers() const;
+
+  // ---- data path ----
+  void load_values(const float* src, void* user_stream);
+  void add(const float* delta, void* user_stream);
+  void sub_add(const float* neu, const float* old, void* user_stream);
+  void snapshot(float* out, void* user_stream);
+  void snapshot_bf16(void* out, void* user_stream);
+  void copy_mirror_from_values(int link);                 // mirror <- values (neighbour is given a snapshot)
+  void push_snapshot(int link, float* remote_values);     // neighbour's values <- values, mirror <- values
+  void round(bool do_rx = true, bool do_tx = true);
+  void sync();
+
+  // ---- engine thread: free-running rounds ----
+  void start_engine();
+  void stop_engine();
+  bool engine_running() const { return engine_on_.load(); }
+
+  // ---- observation ----
+  std::vector<uint64_t> status();      // StatusWord order; synchronises the comm stream
+  uint64_t launches() const { return launches_.load(); }
+  std::string last_error() const;
+
+ private:
+  struct Link {
+    bool used = false;
+    VmmBlock mirror;
+  };
+  struct Block {
+    bool used = false;
+    VmmBlock mem;
+  };
+  struct Peer {
+    bool used = false;
+    int link = -1;
+    int local_block = -1;
+    uint8_t* remote = nullptr;
+    uint32_t* rx_seq = nullptr;
+    uint32_t* tx_seq = nullptr;
+  };
+  void rebuild_params();               // under mu_
+  void publish_pending();              // under mu_
+  void check(int cuda_err, const char* what);
+  void engine_loop();
+  void order_after_user(void* user_stream);
+  void order_user_after(void* user_stream);
+
+  int device_;
+  int64_t n_, n_padded_;
+  int n_tiles_;
+  GpuConfig cfg_;
+  EdgeBlockLayout layout_;
+  VmmBlock values_;
+  std::vector<Link> links_;
+  std::vector<Block> blocks_;
+  std::vector<Peer> peers_;
+  // scratch
+  uint8_t* ctrl_ = nullptr;
+  uint8_t* sent_ = nullptr;
+  uint8_t* tile_state_ = nullptr;
+  int32_t* worklist_ = nullptr;
+  int32_t* work_count_ = nullptr;
+  uint64_t* status_ = nullptr;
+  uint64_t* status_host_ = nullptr;    // pinned
+  RoundParams params_{};
+  int map_link_[kMaxLinks] = {0, 0, 0};  // dense link index of each link id
+  int round_no_ = 0;
+  int ctas_ = 148;
+  void* comm_ = nullptr;               // cudaStream_t
+  void* ev_user_ = nullptr;            // cudaEvent_t: user stream -> comm
+  void* ev_comm_ = nullptr;            // cudaEvent_t: comm -> user stream
+  std::vector<void*> ev_round_;
+  mutable std::mutex mu_;
+  std::thread engine_;
+  std::atomic<bool> engine_on_{false}, engine_stop_{false};
+  std::atomic<uint64_t> launches_{0};
+  std::string error_;
+};
+
+}  // namespace st

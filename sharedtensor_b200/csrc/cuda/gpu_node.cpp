@@ -1,0 +1,658 @@
+// GPU node = tree membership + GPU replica.
+//
+// Membership is the reference's TCP protocol, byte for byte (see ../core/tree.hpp): a joiner connects to
+// host:port, is adopted ('Y') or redirected ('N' + sockaddr_in), and listens on the local address of its
+// up connection.  What is new is what happens after 'Y' when both ends are GPU nodes on the same host:
+// every node also listens on an abstract AF_UNIX socket named after its TCP listen address.  The child
+// connects to its parent's, the two exchange a hello (element count, block size, ring geometry) and the
+// file descriptors of their edge blocks, map each other's block, and from then on the edge is a pair of
+// rings in peer memory; the TCP connection carries no data and serves as the liveness signal (EOF = the
+// neighbour is gone).  The parent then copies its replica into the child's with one kernel and sets its
+// mirror for the edge to the same snapshot, which replaces the reference's implicit state transfer
+// (streaming the whole history through the 1-bit codec, src/sharedtensor.c:379-387) by one bulk copy.
+// If the parent has no such socket (a CPU node, the reference, another host) the edge stays on TCP; that
+// case is handled by the TCP edge classes, not here.
+#include "gpu_node.hpp"
+
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cuda_runtime_api.h>
+
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <memory>
+#include <mutex>
+#include <thread>
+
+#include "../core/tree.hpp"
+#include "engine.hpp"
+#include "vmm.hpp"
+
+namespace st {
+
+namespace {
+
+constexpr uint32_t kHelloMagic = 0x32425453;  // "STB2"
+constexpr uint32_t kHelloVersion = 1;
+
+struct Hello {
+  uint32_t magic = kHelloMagic;
+  uint32_t version = kHelloVersion;
+  int64_t n = 0;
+  int32_t block = 0;
+  int32_t ring_slots = 0;
+  uint64_t edge_bytes = 0;     // mapped size of the sender's edge block
+  uint64_t values_bytes = 0;   // mapped size of the sender's values block
+  sockaddr_in listen_addr{};   // the sender's TCP listen address (identifies the child to its parent)
+  int32_t device = 0;
+  int32_t status = 0;          // reply only: 0 ok, else refusal code
+  char message[64] = {0};
+};
+
+uint64_t now_ms() {
+  using namespace std::chrono;
+  return uint64_t(duration_cast<milliseconds>(steady_clock::now().time_since_epoch()).count());
+}
+
+std::string unix_name(const sockaddr_in& a) { return "sharedtensor_b200/" + addr_to_string(a); }
+
+}  // namespace
+
+struct GpuNodeOptions {
+  bool rejoin = true;
+  int rejoin_backoff_ms = 200;
+  int upgrade_timeout_ms = 5000;
+  int listen_backlog = 5;
+  bool start_engine = true;
+};
+
+class GpuNode {
+ public:
+  GpuNode(int device, int64_t n, const GpuConfig& gcfg, const GpuNodeOptions& opt)
+      : rep_(new GpuReplica(device, n, gcfg)), gcfg_(gcfg), opt_(opt), device_(device), n_(n) {
+    for (int s = 0; s < kNumSlots; s++) edges_[s].slot = s;
+  }
+  ~GpuNode() { close(); }
+
+  GpuReplica& replica() { return *rep_; }
+
+  void start(const std::string& host, int port, const float* init_dev, void* stream) {
+    if (started_.exchange(true)) throw std::runtime_error("node already started");
+    host_ = host;
+    port_ = port;
+    listener_.reset(new TreeListener(
+        [this]() -> int {
+          std::lock_guard<std::mutex> g(mu_);
+          if (closed_.load()) return -1;
+          if (edges_[kSlotLeft].state == 0) return kSlotLeft;
+          if (edges_[kSlotRight].state == 0) return kSlotRight;
+          return -1;
+        },
+        [this](int slot, int fd, const sockaddr_in& peer) {
+          // adopted over TCP; the edge becomes usable once the child has come in over the unix socket
+          std::lock_guard<std::mutex> g(mu_);
+          Edge& e = edges_[slot];
+          e.state = 1;
+          e.tcp_fd = fd;
+          e.peer = peer;
+          e.adopted_ms = now_ms();
+          cv_.notify_all();
+        },
+        [this](int slot, sockaddr_in* out) -> bool {
+          std::lock_guard<std::mutex> g(mu_);
+          if (edges_[slot].state == 0) return false;
+          *out = edges_[slot].peer;
+          return true;
+        }));
+    if (!join(true, init_dev, stream)) {
+      started_.store(false);
+      listener_.reset();
+      throw std::runtime_error("shared tensor could not join or found a tree at " + host + ":" + std::to_string(port));
+    }
+    listener_->start();
+    upgrade_thread_ = std::thread([this] { upgrade_loop(); });
+    watch_thread_ = std::thread([this] { watch_loop(); });
+    if (opt_.start_engine) rep_->start_engine();
+  }
+
+  bool wait_ready(int timeout_ms) {
+    std::unique_lock<std::mutex> lk(mu_);
+    return cv_.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] { return ready_ || closed_.load(); }) && ready_;
+  }
+  bool is_master() const { return master_.load(); }
+
+  void close() {
+    if (closed_.exchange(true)) return;
+    stop_.store(true);
+    cv_.notify_all();
+    if (rep_) rep_->stop_engine();
+    if (listener_) listener_->stop();
+    if (unix_fd_ >= 0) ::shutdown(unix_fd_, SHUT_RDWR);
+    if (upgrade_thread_.joinable()) upgrade_thread_.join();
+    if (watch_thread_.joinable()) watch_thread_.join();
+    if (unix_fd_ >= 0) {
+      ::close(unix_fd_);
+      unix_fd_ = -1;
+    }
+    for (int s = 0; s < kNumSlots; s++) drop_edge(s, false);
+    rep_.reset();
+  }
+
+  pybind11::dict stats() {
+    namespace py = pybind11;
+    py::dict d;
+    std::vector<uint64_t> st;
+    {
+      py::gil_scoped_release rel;
+      st = rep_->status();
+    }
+    std::lock_guard<std::mutex> g(mu_);
+    d["master"] = master_.load();
+    d["ready"] = ready_;
+    d["closed"] = closed_.load();
+    d["n"] = n_;
+    d["listen_addr"] = addr_to_string(listen_addr_);
+    d["rejoins"] = rejoins_;
+    d["edge_failures"] = edge_failures_;
+    d["redirects"] = listener_ ? listener_->redirects() : 0;
+    d["launches"] = rep_->launches();
+    static const char* names[] = {"up", "left", "right"};
+    static const char* states[] = {"free", "adopted", "connected"};
+    py::dict edges;
+    for (int s = 0; s < kNumSlots; s++) {
+      py::dict e;
+      e["state"] = states[edges_[s].state];
+      e["peer"] = edges_[s].state ? addr_to_string(edges_[s].peer) : std::string();
+      e["transport"] = edges_[s].state == 2 ? "p2p" : "";
+      e["link"] = edges_[s].link;
+      edges[names[s]] = e;
+    }
+    d["edges"] = edges;
+    py::dict dev;
+    static const char* snames[] = {"rounds", "tiles_processed", "frames_sent", "frames_recv", "blocked_no_credit", "errors",
+                                   "last_work_count", "residual_sumsq0", "residual_sumsq1", "residual_sumsq2", "pending_tiles",
+                                   "wait_timeouts"};
+    for (int i = 0; i < 12; i++) {
+      if (i >= 7 && i <= 9) {
+        double v;
+        std::memcpy(&v, &st[i], 8);
+        dev[snames[i]] = v;
+      } else {
+        dev[snames[i]] = st[i];
+      }
+    }
+    d["device"] = dev;
+    return d;
+  }
+
+  // host-side fault injection for tests: cut the liveness connection of an edge
+  void inject_sever(int slot) {
+    std::lock_guard<std::mutex> g(mu_);
+    if (edges_[slot].tcp_fd >= 0) ::shutdown(edges_[slot].tcp_fd, SHUT_RDWR);
+  }
+
+ private:
+  struct Edge {
+    int slot = 0;
+    int state = 0;        // 0 free, 1 adopted over TCP (waiting for the peer-memory upgrade), 2 connected
+    int tcp_fd = -1;
+    sockaddr_in peer{};
+    uint64_t adopted_ms = 0;
+    int link = -1, peer_id = -1, block = -1;
+    VmmBlock remote;      // neighbour's edge block mapped here
+  };
+
+  Hello my_hello() const {
+    Hello h;
+    h.n = n_;
+    h.block = gcfg_.block;
+    h.ring_slots = gcfg_.ring_slots;
+    h.edge_bytes = 0;
+    h.values_bytes = rep_->values_block().bytes;
+    h.listen_addr = listen_addr_;
+    h.device = device_;
+    return h;
+  }
+
+  bool join(bool first, const float* init_dev, void* stream) {
+    JoinResult jr = join_tree(host_, port_, &stop_);
+    if (!jr.ok) {
+      std::fprintf(stderr, "[sharedtensor] join failed: %s\n", jr.error.c_str());
+      return false;
+    }
+    std::string err;
+    if (jr.master) {
+      int lfd = open_listener(jr.listen_addr, opt_.listen_backlog, &err);
+      if (lfd < 0) {
+        std::fprintf(stderr, "[sharedtensor] cannot serve %s:%d as master: %s\n", host_.c_str(), port_, err.c_str());
+        return false;
+      }
+      if (first) {
+        listen_addr_ = jr.listen_addr;
+        if (!open_unix(&err)) {
+          ::close(lfd);
+          std::fprintf(stderr, "[sharedtensor] %s\n", err.c_str());
+          return false;
+        }
+        if (init_dev) rep_->load_values(init_dev, stream);
+      }
+      listener_->add_listen_fd(lfd);
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        master_.store(true);
+        ready_ = true;
+      }
+      cv_.notify_all();
+      std::fprintf(stderr, "[sharedtensor] master of %s:%d (%lld elements, GPU %d)\n", host_.c_str(), port_, (long long)n_, device_);
+      return true;
+    }
+    if (first) {
+      int lfd = open_listener(jr.listen_addr, opt_.listen_backlog, &err);
+      if (lfd < 0) {
+        std::fprintf(stderr, "[sharedtensor] cannot listen on %s: %s\n", addr_to_string(jr.listen_addr).c_str(), err.c_str());
+        ::close(jr.fd);
+        return false;
+      }
+      listen_addr_ = jr.listen_addr;
+      listener_->add_listen_fd(lfd);
+      if (!open_unix(&err)) {
+        ::close(jr.fd);
+        std::fprintf(stderr, "[sharedtensor] %s\n", err.c_str());
+        return false;
+      }
+    }
+    master_.store(false);
+    if (!upgrade_as_child(jr, first, &err)) {
+      std::fprintf(stderr, "[sharedtensor] peer-memory upgrade with %s failed: %s\n", addr_to_string(jr.parent_addr).c_str(),
+                   err.c_str());
+      ::close(jr.fd);
+      return false;
+    }
+    std::fprintf(stderr, "[sharedtensor] joined %s:%d below %s after %d redirect(s), GPU %d, peer-memory edge\n", host_.c_str(), port_,
+                 addr_to_string(jr.parent_addr).c_str(), jr.hops, device_);
+    return true;
+  }
+
+  bool open_unix(std::string* err) {
+    unix_fd_ = unix_listen_abstract(unix_name(listen_addr_), err);
+    return unix_fd_ >= 0;
+  }
+
+  // ---- child side of the upgrade ----
+  bool upgrade_as_child(const JoinResult& jr, bool first, std::string* err) {
+    int us = unix_connect_abstract(unix_name(jr.parent_addr), opt_.upgrade_timeout_ms);
+    if (us < 0) {
+      *err = "parent has no peer-memory endpoint on this host (TCP-only parent)";
+      return false;
+    }
+    bool ok = false;
+    int block = -1, link = -1;
+    VmmBlock remote;
+    do {
+      block = rep_->alloc_edge_block();
+      link = rep_->add_link();
+      if (block < 0 || link < 0) {
+        *err = "out of links or edge blocks";
+        break;
+      }
+      Hello h = my_hello();
+      h.edge_bytes = rep_->edge_block(block).bytes;
+      if (!unix_send_fd(us, -1, &h, sizeof(h))) {
+        *err = "hello send failed";
+        break;
+      }
+      Hello reply;
+      if (!unix_recv_fd(us, nullptr, &reply, sizeof(reply), opt_.upgrade_timeout_ms) || reply.magic != kHelloMagic) {
+        *err = "no hello reply";
+        break;
+      }
+      if (reply.status != 0) {
+        *err = std::string("parent refused: ") + reply.message;
+        break;
+      }
+      // our fds: edge block, values
+      std::string e2;
+      int fd_edge = vmm_export_fd(rep_->edge_block(block), &e2);
+      int fd_vals = vmm_export_fd(rep_->values_block(), &e2);
+      if (fd_edge < 0 || fd_vals < 0) {
+        *err = "cannot export device memory: " + e2;
+        if (fd_edge >= 0) ::close(fd_edge);
+        if (fd_vals >= 0) ::close(fd_vals);
+        break;
+      }
+      // A re-joining node keeps what its lost parent had not been told: u = values - mirror_up is set
+      // aside now and added back on top of the new parent's snapshot.
+      bool sent = unix_send_fd(us, fd_edge, "E", 1) && unix_send_fd(us, fd_vals, "V", 1);
+      ::close(fd_edge);
+      ::close(fd_vals);
+      if (!sent) {
+        *err = "fd send failed";
+        break;
+      }
+      int fd_remote = -1;
+      char tag = 0;
+      if (!unix_recv_fd(us, &fd_remote, &tag, 1, opt_.upgrade_timeout_ms) || fd_remote < 0) {
+        *err = "parent's edge block did not arrive";
+        break;
+      }
+      remote = vmm_import_fd(fd_remote, size_t(reply.edge_bytes), device_, &e2);
+      ::close(fd_remote);
+      if (!remote.ptr) {
+        *err = "cannot map parent's edge block: " + e2;
+        break;
+      }
+      // wait for the snapshot
+      char rdy = 0;
+      if (!unix_recv_fd(us, nullptr, &rdy, 1, 60000) || rdy != 'R') {
+        *err = "snapshot did not arrive";
+        break;
+      }
+      rep_->copy_mirror_from_values(link);  // the parent knows exactly what it just gave us
+      if (!first && carry_valid_) {
+        rep_->add(carry_, rep_->comm_stream());
+        rep_->sync();
+        cudaFree(carry_);
+        carry_ = nullptr;
+        carry_valid_ = false;
+      }
+      int pid = rep_->attach_peer(link, block, remote.ptr);
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        Edge& e = edges_[kSlotUp];
+        e.state = 2;
+        e.tcp_fd = jr.fd;
+        e.peer = jr.parent_addr;
+        e.link = link;
+        e.block = block;
+        e.peer_id = pid;
+        e.remote = remote;
+        ready_ = true;
+      }
+      cv_.notify_all();
+      ok = true;
+    } while (false);
+    ::close(us);
+    if (!ok) {
+      if (remote.ptr) vmm_free(&remote);
+      if (link >= 0) rep_->remove_link(link);
+      if (block >= 0) rep_->free_edge_block(block);
+    }
+    return ok;
+  }
+
+  // ---- parent side of the upgrade ----
+  void upgrade_loop() {
+    while (!stop_.load()) {
+      struct pollfd pfd = {unix_fd_, POLLIN, 0};
+      int pr = ::poll(&pfd, 1, kPollMs);
+      if (pr <= 0) continue;
+      int us = ::accept(unix_fd_, nullptr, nullptr);
+      if (us < 0) continue;
+      serve_upgrade(us);
+      ::close(us);
+    }
+  }
+
+  void refuse(int us, const char* why) {
+    Hello r = my_hello();
+    r.status = 1;
+    std::snprintf(r.message, sizeof(r.message), "%s", why);
+    unix_send_fd(us, -1, &r, sizeof(r));
+  }
+
+  void serve_upgrade(int us) {
+    Hello h;
+    if (!unix_recv_fd(us, nullptr, &h, sizeof(h), opt_.upgrade_timeout_ms) || h.magic != kHelloMagic) return;
+    if (h.version != kHelloVersion) return refuse(us, "protocol version mismatch");
+    if (h.n != n_) return refuse(us, "Not the right size!");
+    if (h.block != gcfg_.block || h.ring_slots != gcfg_.ring_slots) return refuse(us, "scale block / ring geometry mismatch");
+    // find the TCP adoption this child belongs to (the two connections race)
+    int slot = -1;
+    {
+      std::unique_lock<std::mutex> lk(mu_);
+      cv_.wait_for(lk, std::chrono::milliseconds(opt_.upgrade_timeout_ms), [&] {
+        for (int s = kSlotLeft; s <= kSlotRight; s++) {
+          if (edges_[s].state == 1 && edges_[s].peer.sin_port == h.listen_addr.sin_port &&
+              edges_[s].peer.sin_addr.s_addr == h.listen_addr.sin_addr.s_addr) {
+            slot = s;
+            return true;
+          }
+        }
+        return stop_.load();
+      });
+    }
+    if (slot < 0) return refuse(us, "no matching TCP adoption");
+    int block = rep_->alloc_edge_block();
+    int link = rep_->add_link();
+    VmmBlock remote, child_values;
+    bool ok = false;
+    std::string err;
+    do {
+      if (block < 0 || link < 0) {
+        refuse(us, "parent is out of links");
+        break;
+      }
+      Hello r = my_hello();
+      r.edge_bytes = rep_->edge_block(block).bytes;
+      if (!unix_send_fd(us, -1, &r, sizeof(r))) break;
+      int fd_edge = -1, fd_vals = -1;
+      char tag = 0;
+      if (!unix_recv_fd(us, &fd_edge, &tag, 1, opt_.upgrade_timeout_ms) || fd_edge < 0) break;
+      if (!unix_recv_fd(us, &fd_vals, &tag, 1, opt_.upgrade_timeout_ms) || fd_vals < 0) {
+        ::close(fd_edge);
+        break;
+      }
+      remote = vmm_import_fd(fd_edge, size_t(h.edge_bytes), device_, &err);
+      child_values = vmm_import_fd(fd_vals, size_t(h.values_bytes), device_, &err);
+      ::close(fd_edge);
+      ::close(fd_vals);
+      if (!remote.ptr || !child_values.ptr) {
+        std::fprintf(stderr, "[sharedtensor] cannot map child's memory: %s\n", err.c_str());
+        break;
+      }
+      int my_fd = vmm_export_fd(rep_->edge_block(block), &err);
+      if (my_fd < 0) break;
+      bool sent = unix_send_fd(us, my_fd, "E", 1);
+      ::close(my_fd);
+      if (!sent) break;
+      // state transfer: one pass over the replica, in stream order with the rounds
+      rep_->push_snapshot(link, static_cast<float*>(child_values.ptr));
+      int pid = rep_->attach_peer(link, block, remote.ptr);
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        Edge& e = edges_[slot];
+        e.state = 2;
+        e.link = link;
+        e.block = block;
+        e.peer_id = pid;
+        e.remote = remote;
+      }
+      unix_send_fd(us, -1, "R", 1);
+      ok = true;
+    } while (false);
+    if (child_values.ptr) vmm_free(&child_values);
+    if (!ok) {
+      if (remote.ptr) vmm_free(&remote);
+      if (link >= 0) rep_->remove_link(link);
+      if (block >= 0) rep_->free_edge_block(block);
+      drop_edge(slot, true);
+    }
+  }
+
+  // ---- liveness ----
+  void watch_loop() {
+    while (!stop_.load()) {
+      std::vector<pollfd> pfds;
+      std::vector<int> slots;
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        for (int s = 0; s < kNumSlots; s++) {
+          if (edges_[s].state && edges_[s].tcp_fd >= 0) {
+            pfds.push_back({edges_[s].tcp_fd, POLLIN, 0});
+            slots.push_back(s);
+          }
+          // a child that was adopted over TCP but never came in over the unix socket is a TCP-only
+          // peer (CPU node, reference, other host): not served by this class
+          if (edges_[s].state == 1 && now_ms() - edges_[s].adopted_ms > uint64_t(opt_.upgrade_timeout_ms) * 2) {
+            pfds.push_back({-1, 0, 0});
+            slots.push_back(-(s + 1));
+          }
+        }
+      }
+      if (pfds.empty()) {
+        ::usleep(kPollMs * 1000);
+        continue;
+      }
+      int pr = ::poll(pfds.data(), pfds.size(), kPollMs);
+      for (size_t i = 0; i < pfds.size(); i++) {
+        if (slots[i] < 0) {
+          int s = -slots[i] - 1;
+          std::fprintf(stderr, "[sharedtensor] edge %d: peer never completed the peer-memory upgrade, dropping it\n", s);
+          drop_edge(s, true);
+          continue;
+        }
+        if (pr <= 0 || !(pfds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+        char buf[256];
+        ssize_t r = ::recv(pfds[i].fd, buf, sizeof(buf), MSG_DONTWAIT);
+        if (r > 0) continue;  // stray bytes on a liveness connection are ignored
+        if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;
+        int s = slots[i];
+        if (stop_.load()) break;
+        std::fprintf(stderr, "[sharedtensor] edge %d lost (neighbour closed its liveness connection)\n", s);
+        bool was_up = s == kSlotUp;
+        if (was_up && opt_.rejoin) save_carry();
+        drop_edge(s, true);
+        if (was_up) {
+          if (!opt_.rejoin) {
+            master_.store(true);
+            continue;
+          }
+          {
+            std::lock_guard<std::mutex> g(mu_);
+            ready_ = false;
+          }
+          // the new parent writes its snapshot into this replica's values: no round may run meanwhile
+          rep_->stop_engine();
+          int backoff = opt_.rejoin_backoff_ms;
+          while (!stop_.load()) {
+            if (join(false, nullptr, nullptr)) {
+              std::lock_guard<std::mutex> g(mu_);
+              rejoins_++;
+              break;
+            }
+            ::usleep(useconds_t(backoff) * 1000);
+            if (backoff < 5000) backoff *= 2;
+          }
+          if (opt_.start_engine && !stop_.load()) rep_->start_engine();
+          if (master_.load() && carry_) {  // became the root: nothing to add back, values are intact
+            cudaFree(carry_);
+            carry_ = nullptr;
+            carry_valid_ = false;
+          }
+        }
+      }
+    }
+  }
+
+  // u = values - mirror_up, kept in a scratch buffer until the re-join has a new snapshot to add it to
+  void save_carry() {
+    int link;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      link = edges_[kSlotUp].link;
+    }
+    if (link < 0) return;
+    cudaSetDevice(device_);
+    if (cudaMalloc(reinterpret_cast<void**>(&carry_), size_t(n_) * 4) != cudaSuccess) {
+      carry_ = nullptr;
+      return;
+    }
+    cudaMemsetAsync(carry_, 0, size_t(n_) * 4, static_cast<cudaStream_t>(rep_->comm_stream()));
+    launch_sub_add(carry_, rep_->values(), rep_->mirror(link), n_, nullptr, 0, 0, rep_->comm_stream());
+    rep_->sync();
+    carry_valid_ = true;
+  }
+
+  void drop_edge(int slot, bool count) {
+    Edge old;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      old = edges_[slot];
+      edges_[slot] = Edge();
+      edges_[slot].slot = slot;
+      if (count && old.state) edge_failures_++;
+    }
+    if (!old.state) return;
+    if (rep_) {
+      if (old.peer_id >= 0) rep_->detach_peer(old.peer_id);
+      if (old.link >= 0) rep_->remove_link(old.link);
+      if (old.block >= 0) rep_->free_edge_block(old.block);
+    }
+    if (old.remote.ptr) vmm_free(&old.remote);
+    if (old.tcp_fd >= 0) {
+      ::shutdown(old.tcp_fd, SHUT_RDWR);
+      ::close(old.tcp_fd);
+    }
+  }
+
+  std::unique_ptr<GpuReplica> rep_;
+  GpuConfig gcfg_;
+  GpuNodeOptions opt_;
+  int device_;
+  int64_t n_;
+  std::string host_;
+  int port_ = 0;
+  sockaddr_in listen_addr_{};
+  std::unique_ptr<TreeListener> listener_;
+  int unix_fd_ = -1;
+  Edge edges_[kNumSlots];
+  std::mutex mu_;
+  std::condition_variable cv_;
+  bool ready_ = false;
+  std::atomic<bool> master_{false}, closed_{false}, started_{false}, stop_{false};
+  std::thread upgrade_thread_, watch_thread_;
+  uint64_t rejoins_ = 0, edge_failures_ = 0;
+  float* carry_ = nullptr;
+  bool carry_valid_ = false;
+};
+
+}  // namespace st
+
+void bind_gpu_node(pybind11::module_& m) {
+  namespace py = pybind11;
+  using namespace st;
+  py::class_<GpuNodeOptions>(m, "GpuNodeOptions")
+      .def(py::init<>())
+      .def_readwrite("rejoin", &GpuNodeOptions::rejoin)
+      .def_readwrite("rejoin_backoff_ms", &GpuNodeOptions::rejoin_backoff_ms)
+      .def_readwrite("upgrade_timeout_ms", &GpuNodeOptions::upgrade_timeout_ms)
+      .def_readwrite("listen_backlog", &GpuNodeOptions::listen_backlog)
+      .def_readwrite("start_engine", &GpuNodeOptions::start_engine);
+  py::class_<GpuNode>(m, "GpuNode")
+      .def(py::init<int, int64_t, const GpuConfig&, const GpuNodeOptions&>())
+      .def("replica", &GpuNode::replica, py::return_value_policy::reference_internal)
+      .def(
+          "start",
+          [](GpuNode& n, const std::string& host, int port, uintptr_t init, uintptr_t stream) {
+            py::gil_scoped_release rel;
+            n.start(host, port, reinterpret_cast<const float*>(init), reinterpret_cast<void*>(stream));
+          },
+          py::arg("host"), py::arg("port"), py::arg("init") = 0, py::arg("stream") = 0)
+      .def("wait_ready",
+           [](GpuNode& n, int ms) {
+             py::gil_scoped_release rel;
+             return n.wait_ready(ms);
+           })
+      .def("is_master", &GpuNode::is_master)
+      .def("stats", &GpuNode::stats)
+      .def("inject_sever", &GpuNode::inject_sever)
+      .def("close", [](GpuNode& n) {
+        py::gil_scoped_release rel;
+        n.close();
+      });
+}

@@ -1,0 +1,657 @@
+// Sync-round kernels for sm_100a: round_begin, round_main and round_publish (see round.h for the protocol).
+//
+// round_main is the fused hot path.  A CTA is four independent groups of 128 threads; a group works
+// through its share of the listed tiles, one 16 KB array-tile (values, then each link's mirror) at a time:
+//   1. array-tiles are staged into shared memory with 1-D TMA bulk copies (cp.async.bulk, completion on an
+//      mbarrier, a three-slot ring per group so the next copy is in flight while this one is computed;
+//      every source is this GPU's own memory);
+//   2. a thread owns 32 consecutive elements (read with an XOR swizzle, so no bank conflicts): it decodes
+//      the frames that arrived (sign bit + per-block power-of-two scale) into the values and into the
+//      mirror of the link they came from                 (reference src/sharedtensor.c:106-111, 124-127);
+//   3. per link it forms the residual values - mirror, the block's sum of squares, the exponent code from
+//      the float's exponent bits, its 32 sign bits as one word, and steps the mirror by -/+ 2^k
+//                                                         (reference 156-174);
+//   4. changed array-tiles go back to global memory with TMA bulk stores, and the packed words + scale
+//      bytes go straight into the neighbours' ring slots with TMA bulk stores over NVLink
+//      (reference 176-177: two socket writes).
+// Nothing in here waits for another GPU.  The only waits are on this CTA's own TMA copies, and they are
+// bounded: on a timeout the group records an error in the status block and leaves.
+//
+// Arithmetic is written with explicit round-to-nearest multiplies and adds in the order documented in
+// ../core/codec.hpp, so that words, scales and mirrors are bit-identical to the host codec.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "round.h"
+
+namespace st {
+
+namespace {
+
+constexpr int kGroups = 4;          // independent 128-thread groups per CTA
+constexpr int kGroupThreads = 128;  // one thread per 32 consecutive elements of a tile
+constexpr int kThreads = kGroups * kGroupThreads;
+constexpr int kSlots = 3;           // array-tile slots per group
+constexpr int kTileBytes = kTile * 4;
+
+// ----------------------------------------------------------------------------------------------
+// small PTX wrappers
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// global -> this CTA's shared memory, completion counted in bytes on `bar`.  Source is always local
+// device memory; size and both addresses are multiples of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait on one of this CTA's own copy barriers.  20 ms is three orders of magnitude above the
+// time a stage takes; running into it means the copy was mis-issued, and the caller bails out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < (1u << 24); it++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63) == 63 && globaltimer_ns() - t0 > 20ull * 1000 * 1000) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ int floor_log2_dev(float x) { return int((__float_as_uint(x) >> 23) & 0xff) - 127; }
+
+__device__ __forceinline__ int block_code_dev(float sx, uint32_t vmax_bits, int lb, int min_exp, int rel_bits) {
+  if ((__float_as_uint(sx) >> 23) == 0) return 0;
+  int kx = (floor_log2_dev(sx) - lb) >> 1;
+  if (kx < min_exp) return 0;
+  if ((vmax_bits >> 23) != 0) {
+    int emax = int(vmax_bits >> 23) - 127;
+    if (kx < emax - rel_bits) return 0;
+  }
+  if (kx < -126) return 0;
+  if (kx > 127) kx = 127;
+  return kx + 127;
+}
+
+__device__ __forceinline__ float sumsq4(const float4& a) {
+  return __fadd_rn(__fadd_rn(__fmul_rn(a.x, a.x), __fmul_rn(a.y, a.y)), __fadd_rn(__fmul_rn(a.z, a.z), __fmul_rn(a.w, a.w)));
+}
+
+__device__ __forceinline__ int ceil_log2_dev(int64_t v) {
+  int l = 0;
+  while ((int64_t(1) << l) < v) l++;
+  return l;
+}
+
+}  // namespace
+
+// ----------------------------------------------------------------------------------------------
+// round_publish / round_begin: one thread per tile
+// ----------------------------------------------------------------------------------------------
+// After round_main: tell the neighbours what happened.  Credits for the frames this replica consumed
+// go to their senders, sequence flags for the frames it wrote go to their receivers.  round_main has
+// completed (stream order), so its peer stores are performed; the release stores below order them
+// before the flag for an observer at system scope.
+__global__ void __launch_bounds__(256) round_publish_kernel(const __grid_constant__ RoundParams p) {
+  const int tile = blockIdx.x * blockDim.x + threadIdx.x;
+  if (tile >= p.n_tiles) return;
+  uint8_t* cptr = p.ctrl + size_t(tile) * 16;
+  const uint4 prev = *reinterpret_cast<const uint4*>(cptr);
+  const uint8_t* pc = reinterpret_cast<const uint8_t*>(&prev);
+  const uint2 sentw = *reinterpret_cast<const uint2*>(p.sent + size_t(tile) * 8);
+  const uint8_t* ps = reinterpret_cast<const uint8_t*>(&sentw);
+  if ((prev.x | prev.y) == 0u && (sentw.x | sentw.y) == 0u) return;  // nothing consumed, nothing sent
+  for (int r = 0; r < p.n_in; r++) {
+    int avail = pc[r] >> 6;
+    if (avail) {
+      uint32_t seq = p.in[r].rx_seq[tile] + uint32_t(avail);
+      p.in[r].rx_seq[tile] = seq;
+      st_release_sys(p.in[r].credit_remote + tile, seq);
+    }
+  }
+  for (int r = 0; r < p.n_out; r++) {
+    if (ps[r]) {
+      uint32_t seq = p.out[r].tx_seq[tile] + 1;
+      int slot = pc[8 + r] & 63;
+      p.out[r].tx_seq[tile] = seq;
+      st_release_sys(p.out[r].flags_remote + size_t(slot) * p.n_tiles + tile, seq);
+    }
+  }
+  *reinterpret_cast<uint4*>(cptr) = make_uint4(0u, 0u, 0u, 0u);
+  *reinterpret_cast<uint2*>(p.sent + size_t(tile) * 8) = make_uint2(0u, 0u);
+}
+
+// Before round_main: look at every tile's rings once (frames that arrived, ring space) and list the
+// tiles that have something to do.
+__global__ void __launch_bounds__(256) round_begin_kernel(const __grid_constant__ RoundParams p) {
+  const int tile = blockIdx.x * blockDim.x + threadIdx.x;
+  const int par = p.round & 1;
+  if (tile == 0) {
+    p.work_count[par ^ 1] = 0;  // the next round appends to the other counter
+    p.status[kStPendingTiles] = 0;
+    p.status[kStResidualSumsq0] = 0;
+    p.status[kStResidualSumsq1] = 0;
+    p.status[kStResidualSumsq2] = 0;
+  }
+  if (tile >= p.n_tiles) return;
+  uint4 cur = make_uint4(0u, 0u, 0u, 0u);
+  uint8_t* cc = reinterpret_cast<uint8_t*>(&cur);
+  bool work = p.tile_state[tile] != 0;
+  const uint32_t S = uint32_t(p.ring_slots);
+  if (p.do_rx) {
+    for (int r = 0; r < p.n_in; r++) {
+      uint32_t e = p.in[r].rx_seq[tile];
+      int avail = 0;
+      while (avail < kRxMax) {
+        uint32_t slot = (e + uint32_t(avail)) % S;
+        uint32_t f = ld_acquire_sys(p.in[r].flags + size_t(slot) * p.n_tiles + tile);
+        if (f != e + uint32_t(avail) + 1u) break;
+        avail++;
+      }
+      cc[r] = uint8_t((avail << 6) | int(e % S));
+      if (avail) work = true;
+    }
+  }
+  if (p.do_tx) {
+    for (int r = 0; r < p.n_out; r++) {
+      uint32_t t = p.out[r].tx_seq[tile];
+      uint32_t c = ld_acquire_sys(p.out[r].credit + tile);
+      bool can = (t - c) < S;
+      cc[8 + r] = uint8_t((can ? 64 : 0) | int(t % S));
+    }
+  }
+  *reinterpret_cast<uint4*>(p.ctrl + size_t(tile) * 16) = cur;
+  if (work) {
+    int idx = atomicAdd(p.work_count + par, 1);
+    p.worklist[idx] = tile;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// round_main
+// ----------------------------------------------------------------------------------------------
+namespace {
+
+// shared -> global bulk store / reduce (this CTA's memory as source), tracked by bulk async-groups
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g_add_f32(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_gmem),
+               "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// barrier over one 128-thread group (hardware barrier 1 + group)
+__device__ __forceinline__ void group_bar(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kGroupThreads) : "memory");
+}
+constexpr uint32_t kFlagChanged = 1, kFlagNonsilent = 2, kFlagFailed = 4;
+
+__device__ __forceinline__ uint32_t ld_u32_ca(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.ca.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_u8_ca(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.ca.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+// f = +/- 2^(code-127) for element `bit` of word w, as raw bits: the sign bit is the frame's bit
+__device__ __forceinline__ float signed_scale(uint32_t scale_bits, uint32_t w, int bit) {
+  return __uint_as_float(scale_bits | ((w << (31 - bit)) & 0x80000000u));
+}
+
+struct GroupSmem {
+  int off_slots;    // [kGroups][kSlots][kTileBytes]
+  int off_out;      // [kGroups][2][payload_bytes]
+  int off_bar;      // uint64_t[kGroups][kSlots]
+  int off_red;      // float[kGroups][2][4]   cross-warp partials for blocks of 2048/4096
+  int off_flags;    // uint32_t[kGroups][3]  per-step OR flags (changed / nonsilent / wait failed)
+  int total;
+};
+__host__ __device__ inline GroupSmem group_layout(int payload_bytes) {
+  GroupSmem m;
+  int off = 0;
+  m.off_slots = off;
+  off += kGroups * kSlots * kTileBytes;
+  m.off_out = off;
+  off += kGroups * 2 * ((payload_bytes + 127) & ~127);
+  m.off_bar = off;
+  off += 8 * kGroups * kSlots;
+  m.off_red = off;
+  off += 4 * kGroups * 2 * 4;
+  m.off_flags = off;
+  off += 4 * kGroups * 4;
+  m.total = (off + 127) & ~127;
+  return m;
+}
+
+}  // namespace
+
+int round_main_smem_bytes(int, int, int payload_bytes, int* stages_out) {
+  if (stages_out) *stages_out = kSlots;
+  return group_layout(payload_bytes).total;
+}
+
+template <bool ATOMIC>
+__global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_constant__ RoundParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const GroupSmem lay = group_layout(p.payload_bytes);
+  const int tid = threadIdx.x;
+  const int g = tid >> 7;           // group
+  const int t = tid & 127;          // thread in group = 32-element chunk of the tile
+  const int lane = tid & 31;
+  const int wig = (tid >> 5) & 3;   // warp in group
+  const int sw = t & 7;             // XOR swizzle of this thread's eight 16-byte pieces
+  uint8_t* slots = smem + lay.off_slots + size_t(g) * kSlots * kTileBytes;
+  const int pb_pad = (p.payload_bytes + 127) & ~127;
+  uint8_t* outbuf = smem + lay.off_out + size_t(g) * 2 * pb_pad;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + g * kSlots;
+  float* s_red = reinterpret_cast<float*>(smem + lay.off_red) + g * 8;
+  uint32_t* s_flags = reinterpret_cast<uint32_t*>(smem + lay.off_flags) + g * 4;
+
+  const int par = p.round & 1;
+  const int count = p.work_count[par];
+  const int L = p.n_links;
+  const int arrays = 1 + L;
+  const int lb = p.log2_block;
+  const int pb = p.payload_bytes;
+  const int64_t n = p.n;
+  const int stride = int(gridDim.x) * kGroups;
+  const int first = int(blockIdx.x) * kGroups + g;
+  const int my_count = count > first ? (count - first + stride - 1) / stride : 0;
+  const int total_steps = my_count * arrays;
+  const int64_t tail_block = (n & ((int64_t(1) << lb) - 1)) ? (n >> lb) : int64_t(-1);
+  const int tail_lb = tail_block >= 0 ? ceil_log2_dev(n - (tail_block << lb)) : lb;
+  const int tpb = lb - 5;           // log2(threads per block)
+
+  if (t == 0) {
+    s_flags[0] = s_flags[1] = s_flags[2] = 0;
+    for (int s = 0; s < kSlots; s++) mbar_init(full + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  __syncthreads();
+
+  // ---- copy issue (thread 0 of the group).  Step c = (tile index c / arrays, array c % arrays).
+  // The tile ids of this and the next listed tile are kept in registers by every thread.
+  int tile_cur = my_count > 0 ? p.worklist[first] : 0;
+  int tile_next = my_count > 1 ? p.worklist[first + stride] : 0;
+  uint4 cw_cur = my_count > 0 ? *reinterpret_cast<const uint4*>(p.ctrl + size_t(tile_cur) * 16) : make_uint4(0u, 0u, 0u, 0u);
+  auto src_of = [&](int tile, int a) -> const float* {
+    return (a == 0 ? p.values : p.mirror[a - 1]) + size_t(tile) * kTile;
+  };
+  auto issue_load = [&](int c, int tile) {
+    const int s = c % kSlots;
+    mbar_expect_tx(full + s, kTileBytes);
+    bulk_g2s(slots + size_t(s) * kTileBytes, src_of(tile, c % arrays), kTileBytes, full + s);
+  };
+  if (t == 0) {
+    for (int c = 0; c < kSlots - 1 && c < total_steps; c++) issue_load(c, c / arrays == 0 ? tile_cur : tile_next);
+  }
+
+  float acc_res0 = 0.f, acc_res1 = 0.f, acc_res2 = 0.f;
+  uint32_t n_rx = 0, n_tx = 0, n_blocked = 0, n_pending = 0;
+  bool aborted = false;
+
+  for (int i = 0; i < my_count && !aborted; i++) {
+    const int tile = tile_cur;
+    const int tile_nn = (i + 2 < my_count) ? p.worklist[first + (i + 2) * stride] : 0;  // prefetched two tiles ahead
+    const uint4 cw = cw_cur;
+    if (i + 1 < my_count) cw_cur = *reinterpret_cast<const uint4*>(p.ctrl + size_t(tile_next) * 16);  // used one tile later
+    const uint32_t in_lo = cw.x, in_hi = cw.y, out_lo = cw.z, out_hi = cw.w;
+    auto in_byte = [&](int r) -> uint32_t { return ((r < 4 ? in_lo : in_hi) >> ((r & 3) * 8)) & 0xffu; };
+    auto out_byte = [&](int r) -> uint32_t { return ((r < 4 ? out_lo : out_hi) >> ((r & 3) * 8)) & 0xffu; };
+    const int64_t ebase = int64_t(tile) * kTile + int64_t(t) * 32;
+    const bool full_chunk = ebase + 32 <= n;
+    const bool rx_any = (in_lo & 0xc0c0c0c0u) != 0 || (in_hi & 0xc0c0c0c0u) != 0;
+    bool pend_tile = false;
+    uint32_t sent_lo = 0, sent_hi = 0;
+
+    float4 v[8];  // piece q holds elements 4*(q^sw) .. +3 of this thread's 32
+    for (int a = 0; a < arrays && !aborted; a++) {
+      const int c = i * arrays + a;
+      const int s = c % kSlots;
+      float4* slot4 = reinterpret_cast<float4*>(slots + size_t(s) * kTileBytes) + t * 8;
+      const int l = a - 1;
+
+      // frames that concern this step: all in-rings for the values, the link's own in-rings for a mirror
+      // (decoded a second time; they are a few hundred bytes per tile and come from L1/L2)
+      // A wait that runs out does not leave the loop by itself (the group's barrier below needs all 128
+      // threads): the thread finishes the step on whatever the slot holds and reports the failure through
+      // the step's flags, so that the whole group stops together before anything is stored.
+      const bool wait_failed = !mbar_wait_bounded(full + s, uint32_t(c / kSlots) & 1u);
+      if (t == 0) s_flags[(c + 1) % 3] = 0;  // flags of the next step; last read two barriers ago
+      float4 k[8];
+      if (a == 0) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) v[q] = slot4[q ^ sw];
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; q++) k[q] = slot4[q ^ sw];
+      }
+
+      bool changed = false;
+      if (rx_any) {
+        for (int r = 0; r < p.n_in; r++) {
+          const uint32_t ib = in_byte(r);
+          const int avail = int(ib >> 6);
+          if (!avail || (a > 0 && p.in[r].link != l)) continue;
+          for (int f = 0; f < avail; f++) {
+            const int slot_no = (int(ib & 63u) + f) % p.ring_slots;
+            const uint8_t* pay = p.in[r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
+            const uint32_t w = ld_u32_ca(pay + 4 * t);
+            const uint32_t code = ld_u8_ca(pay + 4 * kWordsPerTile + (t >> tpb));
+            if (!code) continue;
+            changed = true;
+            const uint32_t sb = code << 23;  // bits of 2^(code-127)
+            if (full_chunk) {
+#pragma unroll
+              for (int q = 0; q < 8; q++) {
+                const uint32_t wq = w >> (4 * (q ^ sw));
+                float4& d = a == 0 ? v[q] : k[q];
+                d.x = __fadd_rn(d.x, signed_scale(sb, wq, 0));
+                d.y = __fadd_rn(d.y, signed_scale(sb, wq, 1));
+                d.z = __fadd_rn(d.z, signed_scale(sb, wq, 2));
+                d.w = __fadd_rn(d.w, signed_scale(sb, wq, 3));
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; q++) {
+                const int m = q ^ sw;
+                const uint32_t wq = w >> (4 * m);
+                const int64_t e = ebase + 4 * m;
+                float4& d = a == 0 ? v[q] : k[q];
+                if (e + 0 < n) d.x = __fadd_rn(d.x, signed_scale(sb, wq, 0));
+                if (e + 1 < n) d.y = __fadd_rn(d.y, signed_scale(sb, wq, 1));
+                if (e + 2 < n) d.z = __fadd_rn(d.z, signed_scale(sb, wq, 2));
+                if (e + 3 < n) d.w = __fadd_rn(d.w, signed_scale(sb, wq, 3));
+              }
+            }
+            if (a == 0 && t == 0) n_rx++;
+          }
+        }
+      }
+
+      bool send = false;        // this link has room in every one of its out-rings
+      bool nonsilent = false;
+      if (a > 0) {
+        // ---------------- quantise values - mirror for link l
+        bool any_ring = false;
+        send = true;
+        for (int r = 0; r < p.n_out; r++) {
+          if (p.out[r].link != l) continue;
+          any_ring = true;
+          if (!(out_byte(r) & 64u)) send = false;
+        }
+        send = send && any_ring;
+        float px[8];
+        uint32_t vmax = 0;
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          float4 x;
+          x.x = __fsub_rn(v[q].x, k[q].x);
+          x.y = __fsub_rn(v[q].y, k[q].y);
+          x.z = __fsub_rn(v[q].z, k[q].z);
+          x.w = __fsub_rn(v[q].w, k[q].w);
+          px[q] = sumsq4(x);
+          vmax = max(max(vmax, __float_as_uint(v[q].x) & 0x7fffffffu), __float_as_uint(v[q].y) & 0x7fffffffu);
+          vmax = max(max(vmax, __float_as_uint(v[q].z) & 0x7fffffffu), __float_as_uint(v[q].w) & 0x7fffffffu);
+        }
+        // pairwise tree over the eight pieces; the XOR swizzle permutes pieces only within each level's pairs
+        float sx = __fadd_rn(__fadd_rn(__fadd_rn(px[0], px[1]), __fadd_rn(px[2], px[3])),
+                             __fadd_rn(__fadd_rn(px[4], px[5]), __fadd_rn(px[6], px[7])));
+        if (l == 0) acc_res0 += sx; else if (l == 1) acc_res1 += sx; else acc_res2 += sx;
+        // blocks larger than 32 elements: butterfly over lanes (up to 1024), then over the group's warps
+        for (int sft = 0; sft < tpb && sft < 5; sft++) {
+          sx = __fadd_rn(sx, __shfl_xor_sync(0xffffffffu, sx, 1 << sft));
+          vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1 << sft));
+        }
+        if (tpb > 5) {
+          if (lane == 0) {
+            s_red[wig] = sx;
+            s_red[4 + wig] = __uint_as_float(vmax);
+          }
+          group_bar(g);
+          const float a0 = s_red[0], a1 = s_red[1], a2 = s_red[2], a3 = s_red[3];
+          const uint32_t b0 = __float_as_uint(s_red[4]), b1 = __float_as_uint(s_red[5]);
+          const uint32_t b2 = __float_as_uint(s_red[6]), b3 = __float_as_uint(s_red[7]);
+          if (tpb == 6) {  // 2048: warps {0,1} and {2,3}
+            sx = wig < 2 ? __fadd_rn(a0, a1) : __fadd_rn(a2, a3);
+            vmax = wig < 2 ? max(b0, b1) : max(b2, b3);
+          } else {         // 4096: the whole tile
+            sx = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
+            vmax = max(max(b0, b1), max(b2, b3));
+          }
+          group_bar(g);  // s_red is reused by the next link
+        }
+        int lbe = lb;
+        if (tail_block >= 0 && (ebase >> lb) == tail_block) lbe = tail_lb;
+        const int code = block_code_dev(sx, vmax, lbe, p.min_exp, p.rel_bits);
+        nonsilent = code != 0;
+        if (send) {
+          const uint32_t sb = uint32_t(code) << 23;
+          uint32_t word = 0;
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            const int m = q ^ sw;
+            const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
+            const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
+            bool v0 = true, v1 = true, v2 = true, v3 = true;
+            if (!full_chunk) {
+              const int64_t e = ebase + 4 * m;
+              v0 = e + 0 < n;
+              v1 = e + 1 < n;
+              v2 = e + 2 < n;
+              v3 = e + 3 < n;
+            }
+            const uint32_t nib = uint32_t(n0 && v0) | (uint32_t(n1 && v1) << 1) | (uint32_t(n2 && v2) << 2) | (uint32_t(n3 && v3) << 3);
+            word |= nib << (4 * m);
+            if (code) {
+              if (v0) k[q].x = __fadd_rn(k[q].x, __uint_as_float(sb | (n0 ? 0x80000000u : 0u)));
+              if (v1) k[q].y = __fadd_rn(k[q].y, __uint_as_float(sb | (n1 ? 0x80000000u : 0u)));
+              if (v2) k[q].z = __fadd_rn(k[q].z, __uint_as_float(sb | (n2 ? 0x80000000u : 0u)));
+              if (v3) k[q].w = __fadd_rn(k[q].w, __uint_as_float(sb | (n3 ? 0x80000000u : 0u)));
+            }
+          }
+          if (code) changed = true;
+          uint8_t* ob = outbuf + size_t(c & 1) * pb_pad;
+          reinterpret_cast<uint32_t*>(ob)[t] = word;
+          if ((t & ((1 << tpb) - 1)) == 0) ob[4 * kWordsPerTile + (t >> tpb)] = uint8_t(code);
+        }
+      }
+
+      // ---------------- write the array-tile back into its slot if this thread changed it
+      if (changed) {
+        if (a == 0) {
+          if (ATOMIC) {
+            // the slot becomes the difference, added to global memory by the copy engine
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+              float4 o = slot4[q ^ sw];
+              slot4[q ^ sw] = make_float4(v[q].x - o.x, v[q].y - o.y, v[q].z - o.z, v[q].w - o.w);
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) slot4[q ^ sw] = v[q];
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 8; q++) slot4[q ^ sw] = k[q];
+        }
+      } else if (a == 0 && ATOMIC && rx_any) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) slot4[q ^ sw] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      fence_async_smem();
+      {
+        const uint32_t mine = (changed ? kFlagChanged : 0u) | (nonsilent ? kFlagNonsilent : 0u) | (wait_failed ? kFlagFailed : 0u);
+        const uint32_t warp_bits = __reduce_or_sync(0xffffffffu, mine);
+        if (lane == 0 && warp_bits) atomicOr(&s_flags[c % 3], warp_bits);
+      }
+      group_bar(g);
+      const uint32_t step_flags = s_flags[c % 3];
+      if (step_flags & kFlagFailed) {
+        aborted = true;
+        break;
+      }
+      const bool any_changed = (step_flags & kFlagChanged) != 0;
+      const bool any_nonsilent = (step_flags & kFlagNonsilent) != 0;
+      pend_tile |= any_nonsilent;
+
+      if (t == 0) {
+        void* gdst = const_cast<float*>(src_of(tile, a));
+        if (any_changed) {
+          if (a == 0 && ATOMIC)
+            bulk_s2g_add_f32(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
+          else
+            bulk_s2g(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
+        }
+        if (a > 0 && send && any_nonsilent) {
+          const uint8_t* ob = outbuf + size_t(c & 1) * pb_pad;
+          for (int r = 0; r < p.n_out; r++) {
+            if (p.out[r].link != l) continue;
+            const int slot_no = int(out_byte(r) & 63u);
+            bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + tile) * pb, ob, uint32_t(pb));
+            if (r < 4) sent_lo |= 1u << (r * 8); else sent_hi |= 1u << ((r - 4) * 8);
+            n_tx++;
+          }
+        } else if (a > 0 && any_nonsilent && p.do_tx) {
+          n_blocked++;
+        }
+        bulk_commit();
+        // the slot used one step ago is free once its store (if any) has read it: refill it
+        bulk_wait_read_1();
+        const int cn = c + kSlots - 1;
+        if (cn < total_steps) {
+          const int ti = cn / arrays;
+          issue_load(cn, ti == i ? tile : (ti == i + 1 ? tile_next : tile_nn));
+        }
+      }
+    }
+    if (aborted) break;
+    if (t == 0) {
+      *reinterpret_cast<uint2*>(p.sent + size_t(tile) * 8) = make_uint2(sent_lo, sent_hi);
+      p.tile_state[tile] = uint8_t(pend_tile ? 1 : 0);
+      n_pending += pend_tile ? 1 : 0;
+    }
+    tile_cur = tile_next;
+    tile_next = tile_nn;
+  }
+
+  if (t == 0) bulk_wait_all();  // every store of this thread has landed before the kernel ends
+  if (aborted) {
+    // Leave no copy in flight: give outstanding loads a bounded chance to land before the CTA's shared
+    // memory is released.
+    if (t == 0) {
+      atomicOr(reinterpret_cast<unsigned long long*>(p.status + kStErrors), (unsigned long long)kErrBarrierTimeout);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStWaitTimeouts), 1ull);
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2ull * 1000 * 1000) {
+      }
+    }
+    return;
+  }
+
+  // ---------------- statistics: one atomic per group and counter
+  {
+    float a0 = acc_res0, a1 = acc_res1, a2 = acc_res2;
+    for (int o = 16; o > 0; o >>= 1) {
+      a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+      a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+    }
+    if (lane == 0) {
+      if (a0 != 0.f) atomicAdd(reinterpret_cast<double*>(p.status + kStResidualSumsq0), double(a0));
+      if (a1 != 0.f) atomicAdd(reinterpret_cast<double*>(p.status + kStResidualSumsq1), double(a1));
+      if (a2 != 0.f) atomicAdd(reinterpret_cast<double*>(p.status + kStResidualSumsq2), double(a2));
+    }
+  }
+  if (t == 0) {
+    atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStTilesProcessed), (unsigned long long)my_count);
+    if (n_tx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStFramesSent), (unsigned long long)n_tx);
+    if (n_rx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStFramesRecv), (unsigned long long)n_rx);
+    if (n_blocked) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStBlockedNoCredit), (unsigned long long)n_blocked);
+    if (n_pending) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStPendingTiles), (unsigned long long)n_pending);
+    if (blockIdx.x == 0 && g == 0) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStRounds), 1ull);
+      p.status[kStLastWorkCount] = uint64_t(count);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// launchers
+// ----------------------------------------------------------------------------------------------
+int launch_round_begin(const RoundParams& p, void* stream) {
+  int blocks = (p.n_tiles + 255) / 256;
+  round_begin_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return int(cudaGetLastError());
+}
+int launch_round_publish(const RoundParams& p, void* stream) {
+  int blocks = (p.n_tiles + 255) / 256;
+  round_publish_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return int(cudaGetLastError());
+}
+
+template <bool ATOMIC>
+static int launch_main_t(const RoundParams& p, int ctas, cudaStream_t stream) {
+  const int smem = group_layout(p.payload_bytes).total;
+  static int configured_for = -1;  // per instantiation
+  if (configured_for < smem) {
+    cudaError_t e = cudaFuncSetAttribute(round_main_kernel<ATOMIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return int(e);
+    configured_for = smem;
+  }
+  round_main_kernel<ATOMIC><<<ctas, kThreads, smem, stream>>>(p);
+  return int(cudaGetLastError());
+}
+
+int launch_round_main(const RoundParams& p, int ctas, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (p.n_links < 1 || p.n_links > kMaxLinks) return int(cudaErrorInvalidValue);
+  return p.atomic_values ? launch_main_t<true>(p, ctas, stream) : launch_main_t<false>(p, ctas, stream);
+}
+
+}  // namespace st

@@ -1,0 +1,390 @@
+"""T5: every sm_100a kernel against the host codec / a plain PyTorch fp32 statement of the same operation.
+Two or three replicas live in one process on one GPU and are wired to each other directly."""
+import pytest
+import torch
+
+from sharedtensor_b200 import _native
+from sharedtensor_b200.parallel.local_wiring import connect_local, connect_mesh
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cu():
+    mod = _native.cuda()
+    assert torch.cuda.is_available()
+    return mod
+
+
+@pytest.fixture(scope="module")
+def core():
+    return _native.core()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _replica(cu, n, block=32, slots=4, shareable=True, atomic=False, rel_bits=22):
+    cfg = cu.GpuConfig()
+    cfg.block = block
+    cfg.ring_slots = slots
+    cfg.shareable = shareable
+    cfg.atomic_values = atomic
+    cfg.rel_bits = rel_bits
+    return cu.GpuReplica(0, n, cfg)
+
+
+def _read(ptr_fn, n, rep):
+    out = torch.empty(n, device="cuda")
+    rep.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    return out
+
+
+def _dev_view(ptr, n):
+    """Copies n floats from a raw device address."""
+    out = torch.empty(n, device="cuda")
+    _native.cuda().memcpy_d2d(out.data_ptr(), ptr, n * 4)
+    torch.cuda.synchronize()
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 3, 4, 1023, 4096, 4097, 1 << 20, (1 << 22) + 5])
+def test_snapshot_add_sub_add(cu, n):
+    torch.manual_seed(n)
+    rep = _replica(cu, n)
+    init = torch.randn(n, device="cuda")
+    rep.load_values(init.data_ptr(), _stream())
+    out = torch.empty(n, device="cuda")
+    rep.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(out, init)
+    d = torch.randn(n, device="cuda") * 1e-2
+    rep.add(d.data_ptr(), _stream())
+    rep.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(out, init + d)
+    new, old = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    rep.sub_add(new.data_ptr(), old.data_ptr(), _stream())
+    rep.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(out, (init + d) + (new - old))
+    bf = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    rep.snapshot_bf16(bf.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(bf, out.to(torch.bfloat16))
+
+
+def test_unaligned_user_tensors(cu):
+    n = 10001
+    rep = _replica(cu, n)
+    base = torch.randn(n + 3, device="cuda")
+    d = base[1:n + 1]  # 4-byte aligned only
+    assert d.data_ptr() % 16 != 0
+    rep.add(d.data_ptr(), _stream())
+    outbuf = torch.zeros(n + 3, device="cuda")
+    out = outbuf[3:n + 3]
+    rep.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(out, d)
+
+
+def test_atomic_add_kernels(cu):
+    n = 100003
+    torch.manual_seed(1)
+    v = torch.randn(n, device="cuda")
+    d = torch.randn(n, device="cuda")
+    ref = v + d
+    cu.add(v.data_ptr(), d.data_ptr(), n, 0, 0, True, _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(v, ref)
+    a, b = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    ref = v + (a - b)
+    cu.sub_add(v.data_ptr(), a.data_ptr(), b.data_ptr(), n, 0, 0, True, _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(v, ref)
+
+
+def test_table_scales(cu):
+    torch.manual_seed(3)
+    sizes = [5, 70000, 1, 300000, 4096, 0, 65536]
+    offs = [0]
+    for s in sizes:
+        offs.append(offs[-1] + s)
+    total = offs[-1]
+    x = torch.cat([torch.randn(s, device="cuda") * (10.0 ** (i - 3)) for i, s in enumerate(sizes)])
+    off_d = torch.tensor(offs, dtype=torch.int64, device="cuda")
+    scratch = torch.empty(cu.table_scales_scratch_doubles(len(sizes), total), dtype=torch.float64, device="cuda")
+    out = torch.empty(len(sizes), dtype=torch.float64, device="cuda")
+    exps = torch.empty(len(sizes), dtype=torch.int8, device="cuda")
+    cu.table_scales(x.data_ptr(), off_d.data_ptr(), len(sizes), total, scratch.data_ptr(), out.data_ptr(), exps.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    for i, s in enumerate(sizes):
+        seg = x[offs[i]:offs[i + 1]].double()
+        ref = float((seg * seg).sum())
+        assert abs(float(out[i]) - ref) <= 1e-9 * max(ref, 1e-30)
+        if s:
+            rms = (ref / s) ** 0.5
+            import math
+
+            assert int(exps[i]) == math.floor(math.log2(rms))
+        else:
+            assert int(exps[i]) == -128
+
+
+def test_sample_sqerr_and_delay(cu):
+    n = 1 << 20
+    a = torch.randn(n, device="cuda")
+    stride = 16
+    b = a[::stride].clone() + 0.5
+    out = torch.zeros(2, dtype=torch.float64, device="cuda")
+    cu.sample_sqerr(a.data_ptr(), stride, b.data_ptr(), b.numel(), out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert abs(float(out[0]) - 0.25 * b.numel()) < 1e-3 * b.numel()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    cu.delay(2_000_000, _stream())
+    e1.record()
+    torch.cuda.synchronize()
+    assert 1.9 <= e0.elapsed_time(e1) < 10.0
+
+
+# --------------------------------------------------------------------------------------------------
+class Oracle:
+    """Host model of a replica: values, one mirror per link, frames exchanged as (words, scales)."""
+
+    def __init__(self, core, n, block, n_links, min_exp=-60, rel_bits=22):
+        self.core, self.n, self.block = core, n, block
+        self.v = torch.zeros(n)
+        self.k = [torch.zeros(n) for _ in range(n_links)]
+        self.min_exp, self.rel_bits = min_exp, rel_bits
+
+    def encode(self, link):
+        words = torch.zeros(self.core.block_words(self.n), dtype=torch.int32)
+        scales = torch.zeros(self.core.block_scales(self.n, self.block), dtype=torch.uint8)
+        self.core.encode_block(self.v.data_ptr(), self.k[link].data_ptr(), self.n, self.block, self.min_exp, self.rel_bits,
+                               words.data_ptr(), scales.data_ptr())
+        return words, scales
+
+    def decode(self, link, frame):
+        words, scales = frame
+        self.core.decode_block_add(words.data_ptr(), scales.data_ptr(), self.n, self.block, self.v.data_ptr(),
+                                   self.k[link].data_ptr())
+
+
+def _state(cu, rep, link):
+    n = rep.size()
+    v = torch.empty(n, device="cuda")
+    rep.snapshot(v.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    k = _dev_view(rep.mirror_ptr(link), n)
+    return v.cpu(), k.cpu()
+
+
+@pytest.mark.parametrize("block", [32, 64, 128, 256, 1024, 4096])
+@pytest.mark.parametrize("n", [1, 31, 4096, 4097, 10000, 3 * 4096 + 77])
+def test_round_bit_exact_two_replicas(cu, core, n, block):
+    """A -> B streaming of A's state plus updates on both sides, compared bit for bit with the host codec."""
+    torch.manual_seed(n * 13 + block)
+    A, B = _replica(cu, n, block), _replica(cu, n, block)
+    la, lb = connect_local(A, B)
+    oa, ob = Oracle(core, n, block, 1), Oracle(core, n, block, 1)
+    init = torch.randn(n) * torch.logspace(-2, 1, n)
+    oa.v = init.clone()
+    A.load_values(init.cuda().data_ptr(), _stream())
+    for it in range(24):
+        if it in (5, 11):
+            da, db = torch.randn(n) * 1e-2, torch.randn(n) * 1e-1
+            oa.v += da
+            ob.v += db
+            A.add(da.cuda().data_ptr(), _stream())
+            B.add(db.cuda().data_ptr(), _stream())
+        # A's round: receives B's previous frame (if any), sends; then B's round
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+        # host model, same order: A decodes what B sent last time, encodes; B decodes, encodes
+        if it > 0:
+            oa.decode(0, frame_b)
+        frame_a = oa.encode(0)
+        ob.decode(0, frame_a)
+        frame_b = ob.encode(0)
+        va, ka = _state(cu, A, la)
+        vb, kb = _state(cu, B, lb)
+        assert torch.equal(va, oa.v), f"A values differ in round {it}"
+        assert torch.equal(ka, oa.k[0]), f"A mirror differs in round {it}"
+        assert torch.equal(vb, ob.v), f"B values differ in round {it}"
+        assert torch.equal(kb, ob.k[0]), f"B mirror differs in round {it}"
+    st = A.status()
+    assert st[5] == 0, "no error bits"
+
+
+def test_two_frames_per_round_and_ring_full(cu, core):
+    """The sender runs ahead: the receiver takes two frames per round in order; once the ring is full the
+    sender skips (nothing is lost, the residual simply stays) and counts it."""
+    n, block, slots = 2 * 4096 + 5, 32, 4
+    torch.manual_seed(7)
+    A, B = _replica(cu, n, block, slots), _replica(cu, n, block, slots)
+    la, lb = connect_local(A, B)
+    oa, ob = Oracle(core, n, block, 1), Oracle(core, n, block, 1)
+    init = torch.randn(n)
+    oa.v = init.clone()
+    A.load_values(init.cuda().data_ptr(), _stream())
+    frames = []
+    for _ in range(slots + 3):  # three rounds more than the ring holds
+        A.round()
+        A.sync()
+    for _ in range(slots):
+        frames.append(oa.encode(0))
+    va, ka = _state(cu, A, la)
+    assert torch.equal(ka, oa.k[0]), "only ring_slots frames were produced"
+    st = A.status()
+    names = cu.status_names()
+    assert st[names.index("blocked_no_credit")] == 3 * A.tiles()
+    assert st[names.index("frames_sent")] == slots * A.tiles()
+    # B drains two frames per round
+    for r in range(2):
+        B.round(True, False)  # receiver-only rounds
+        B.sync()
+        ob.decode(0, frames[2 * r])
+        ob.decode(0, frames[2 * r + 1])
+        vb, kb = _state(cu, B, lb)
+        assert torch.equal(vb, ob.v) and torch.equal(kb, ob.k[0])
+    # credits are back: A can send again
+    A.round()
+    A.sync()
+    oa.encode(0)
+    va, ka = _state(cu, A, la)
+    assert torch.equal(ka, oa.k[0])
+
+
+def test_chain_forwarding_converges_to_the_sum(cu):
+    """A - B - C: updates made at the ends reach the other end through B's forwarding."""
+    n = 5 * 4096 + 123
+    torch.manual_seed(11)
+    reps = [_replica(cu, n) for _ in range(3)]
+    connect_local(reps[0], reps[1])
+    connect_local(reps[1], reps[2])
+    init = torch.randn(n, device="cuda")
+    reps[0].load_values(init.data_ptr(), _stream())
+    # late-join emulation: B and C start from zero and are streamed the state
+    expect = init.clone()
+    for it in range(80):
+        if it in (10, 20, 30):
+            for i, r in enumerate(reps):
+                d = torch.randn(n, device="cuda") * 1e-2 * (i + 1)
+                r.add(d.data_ptr(), _stream())
+                expect += d
+        for r in reps:
+            r.round()
+        for r in reps:
+            r.sync()
+    out = torch.empty(n, device="cuda")
+    for r in reps:
+        r.snapshot(out.data_ptr(), _stream())
+        torch.cuda.synchronize()
+        rel = ((out - expect).norm() / expect.norm()).item()
+        assert rel < 5e-5, rel  # two hops, each with its own 2^-22 relative cut-off
+    # quiescent: an idle round lists no tile
+    for r in reps:
+        r.round()
+        r.sync()
+    names = cu.status_names()
+    for r in reps:
+        st = r.status()
+        assert st[names.index("last_work_count")] == 0
+        assert st[names.index("errors")] == 0
+
+
+def test_mesh_group_no_forwarding(cu):
+    """Four replicas as one mesh group: one mirror each, every update crosses exactly one hop."""
+    n = 3 * 4096 + 9
+    torch.manual_seed(5)
+    reps = [_replica(cu, n) for _ in range(4)]
+    connect_mesh(reps)
+    init = torch.randn(n, device="cuda")
+    for r in reps:  # a mesh group starts from a common state
+        r.load_values(init.data_ptr(), _stream())
+        r.copy_mirror_from_values(0)
+    expect = init.clone()
+    for it in range(60):
+        if it in (0, 7, 19):
+            for i, r in enumerate(reps):
+                d = torch.randn(n, device="cuda") * 1e-2 * (i + 1)
+                r.add(d.data_ptr(), _stream())
+                expect += d
+        for r in reps:
+            r.round()
+        for r in reps:
+            r.sync()
+    out = torch.empty(n, device="cuda")
+    for r in reps:
+        r.snapshot(out.data_ptr(), _stream())
+        torch.cuda.synchronize()
+        rel = ((out - expect).norm() / expect.norm()).item()
+        assert rel < 1e-5, rel
+
+
+def test_atomic_values_mode_matches_within_rounding(cu):
+    n = 4 * 4096
+    torch.manual_seed(2)
+    A, B = _replica(cu, n, atomic=True), _replica(cu, n, atomic=True)
+    connect_local(A, B)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    for _ in range(60):
+        A.round()
+        B.round()
+    A.sync()
+    B.sync()
+    out = torch.empty(n, device="cuda")
+    B.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert ((out - init).norm() / init.norm()).item() < 1e-5
+
+
+def test_engine_thread_free_running(cu):
+    n = 8 * 4096
+    torch.manual_seed(4)
+    A, B = _replica(cu, n), _replica(cu, n)
+    connect_local(A, B)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    A.start_engine()
+    B.start_engine()
+    import time
+
+    out = torch.empty(n, device="cuda")
+    deadline = time.time() + 10
+    ok = False
+    while time.time() < deadline:
+        B.snapshot(out.data_ptr(), _stream())
+        torch.cuda.synchronize()
+        if ((out - init).norm() / init.norm()).item() < 1e-5:
+            ok = True
+            break
+        time.sleep(0.01)
+    d = torch.randn(n, device="cuda")
+    B.add(d.data_ptr(), _stream())
+    ok2 = False
+    deadline = time.time() + 10
+    while time.time() < deadline:
+        A.snapshot(out.data_ptr(), _stream())
+        torch.cuda.synchronize()
+        if ((out - (init + d)).norm() / init.norm()).item() < 1e-5:
+            ok2 = True
+            break
+        time.sleep(0.01)
+    A.stop_engine()
+    B.stop_engine()
+    assert ok and ok2
+
+
+def test_vmm_blocks_when_available(cu):
+    rep = _replica(cu, 4096, shareable=True)
+    b = rep.alloc_edge_block()
+    if cu.vmm_available():
+        assert rep.edge_block_is_vmm(b)
