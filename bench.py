@@ -1,0 +1,441 @@
+#!/usr/bin/env python
+"""Headline benchmark: applied updates/s (and replica-convergence latency) of a shared 100M-element fp32
+tensor, each rank adding N(0,1e-3) deltas at a randomised 0.5-2 ms cadence.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 50 --warmup 5
+    python bench.py --impl reference ...      # the unmodified reference over loopback TCP, same workload
+
+One step of a rank = wait its cadence interval (a device-side delay kernel standing in for the compute
+between updates) + ``addFromTensor(delta)``.  The engine propagates in the background.  The timed region
+starts after a barrier and ends, on every rank, when its replica holds initial + the sum of ALL ranks'
+timed updates to within 1 % (relative L2 of the outstanding update, checked on a strided sample of the
+replica by a device kernel); the reported time is the maximum over ranks and
+value = world_size * steps / time.  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_ELEMENTS = 100_000_000
+INIT_STD, DELTA_STD = 1.0, 1e-3
+CADENCE_MS = (0.5, 2.0)
+POOL = 4                 # distinct deltas per rank, cycled
+SAMPLE_STRIDE = 64       # convergence is checked on every 64th element
+TOL = 1e-2               # "applied": outstanding error below 1 % of the update's norm
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--elements", type=int, default=N_ELEMENTS)
+    ap.add_argument("--probes", type=int, default=24, help="single-update latency probes after the timed region")
+    ap.add_argument("--topology", default="tree", choices=["tree"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ref-time-cap", type=float, default=120.0, help="wall-clock cap of the reference arm's wait, seconds")
+    return ap.parse_args()
+
+
+def env_rank():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        assert self.proc and self.proc.stdout
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ======================================================================================================
+# our arm
+# ======================================================================================================
+def seed_of(rank: int, p: int) -> int:
+    return 1_000_003 * (rank + 1) + p
+
+
+def run_ours(args) -> dict | None:
+    import torch
+    import torch.distributed as dist
+
+    import sharedtensor
+    from sharedtensor_b200 import _native
+
+    rank, local_rank, world = env_rank()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N>1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    cu = _native.cuda()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def allmax(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def allsum(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    n = args.elements
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device=dev)
+
+    def randn_seeded(seed: int, std: float) -> torch.Tensor:
+        gen.manual_seed(seed)
+        return torch.randn(n, generator=gen, device=dev, dtype=torch.float32) * std
+
+    # ---- synthetic data: the shared initial state and every rank's delta pool (samples of all, full tensors of ours)
+    init = randn_seeded(7, INIT_STD)
+    expect_s = init[::SAMPLE_STRIDE].clone()
+    pool, pool_s = [], {}
+    for r in range(world):
+        for p in range(POOL):
+            d = randn_seeded(seed_of(r, p), DELTA_STD)
+            pool_s[(r, p)] = d[::SAMPLE_STRIDE].clone()
+            if r == rank:
+                pool.append(d)
+            del d
+    n_s = expect_s.numel()
+    rng_cad = torch.Generator().manual_seed(99 + rank)
+    pinned = [torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(2)] if not args.no_e2e else []
+    for i, h in enumerate(pinned):
+        h.copy_(pool[i % POOL])
+    staging = torch.empty(n, device=dev)
+
+    # ---- the tree: ranks join one after the other so that the shape is the reference's (left, right, redirect ...)
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 17
+    st = None
+    for r in range(world):
+        if r == rank:
+            st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev))
+        barrier()
+    assert st is not None
+    del init
+    rep = st._b.rep
+    err_buf = torch.zeros(2, dtype=torch.float64, device=dev)
+    err_host = torch.zeros(2, dtype=torch.float64).pin_memory()
+    extra_launches = 0
+
+    def sampled_err2() -> float:
+        nonlocal extra_launches
+        err_buf.zero_()
+        cu.sample_sqerr(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, err_buf.data_ptr(), stream)
+        err_host.copy_(err_buf, non_blocking=True)
+        torch.cuda.synchronize()
+        extra_launches += 2
+        return float(err_host[0])
+
+    def add_expected(r: int, p: int, times: int = 1):
+        expect_s.add_(pool_s[(r, p)], alpha=float(times))
+
+    def cadence_ns() -> int:
+        u = float(torch.rand(1, generator=rng_cad))
+        return int((CADENCE_MS[0] + u * (CADENCE_MS[1] - CADENCE_MS[0])) * 1e6)
+
+    def run_steps(k0: int, steps: int, e2e: bool, pool_mod: int = POOL) -> tuple[float, float, int]:
+        """Issues `steps` updates on this rank (all ranks do the same), waits until the replica holds everybody's;
+        returns (seconds to local convergence, final relative error, bytes read back)."""
+        nonlocal extra_launches
+        # what everybody is about to add
+        upd2 = 0.0
+        total = torch.zeros_like(expect_s)
+        for r in range(world):
+            for j in range(steps):
+                total.add_(pool_s[(r, (k0 + j) % pool_mod)])
+        expect_s.add_(total)
+        upd2 = float((total.double() ** 2).sum())
+        del total
+        d2h = 0
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for j in range(steps):
+            p = (k0 + j) % pool_mod
+            cu.delay(cadence_ns(), stream)
+            extra_launches += 1
+            if e2e:
+                staging.copy_(pinned[p], non_blocking=True)   # this step's input: pinned host -> device
+                st.addFromTensor(staging)
+                err_buf.zero_()
+                cu.sample_sqerr(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, err_buf.data_ptr(), stream)
+                err_host.copy_(err_buf, non_blocking=True)                   # this step's result: device -> host
+                torch.cuda.synchronize()
+                extra_launches += 2
+                d2h += 16
+            else:
+                st.addFromTensor(pool[p])
+        deadline = time.time() + 60.0
+        rel = float("inf")
+        while time.time() < deadline:
+            e2 = sampled_err2()
+            rel = (e2 / upd2) ** 0.5 if upd2 > 0 else 0.0
+            if rel <= TOL:
+                break
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3, rel, d2h
+
+    # ---- warm-up (untimed), timed region, end-to-end region
+    if args.warmup:
+        run_steps(0, args.warmup, False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = rep.launches()
+    x0 = extra_launches
+    secs, rel, _ = run_steps(args.warmup, args.steps, False)
+    launches = int(allsum(float(rep.launches() - l0 + extra_launches - x0)))
+    secs = allmax(secs)
+    rel = allmax(rel)
+    clocks = sampler.stop() if rank == 0 else {}
+    e2e = None
+    if not args.no_e2e:
+        k_e2e = max(3, min(args.steps, 10))
+        if pinned:
+            for i, h in enumerate(pinned):
+                h.copy_(pool[i % POOL])
+        s2, rel2, d2h = run_steps(args.warmup + args.steps, k_e2e, True, pool_mod=len(pinned))
+        s2 = allmax(s2)
+        e2e = {"value": world * k_e2e / s2, "unit": "updates/s", "steps": k_e2e, "h2d_bytes_per_step": 4 * n,
+               "d2h_bytes_per_step": d2h // k_e2e, "final_rel_err": allmax(rel2)}
+
+    # ---- single-update convergence latency: one rank adds, everybody measures until its replica has it
+    lat = []
+    for i in range(args.probes if world > 1 else 0):
+        origin, p = i % world, i % POOL
+        add_expected(origin, p)
+        upd2 = float((pool_s[(origin, p)].double() ** 2).sum())
+        barrier()
+        t0 = time.perf_counter()
+        if rank == origin:
+            st.addFromTensor(pool[p])
+        while True:
+            e2 = sampled_err2()
+            if (e2 / upd2) ** 0.5 <= TOL or time.perf_counter() - t0 > 5.0:
+                break
+        lat.append(allmax(time.perf_counter() - t0))
+    stats = st.stats()
+    barrier()
+    st.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    lat_ms = sorted(x * 1e3 for x in lat)
+    out = {
+        "metric": "applied_updates_per_s", "value": world * args.steps / secs, "unit": "updates/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3 / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "ours",
+        "config": {"model": "shared parameter vector, 100M fp32 elements ~ N(0,1)", "elements": n, "global_batch": world,
+                   "seq_len": None, "parallelism": f"async-dp{world} (tree over NVLink peer memory)",
+                   "delta": "N(0,1e-3) fp32", "cadence_ms": list(CADENCE_MS), "scale_block": 32,
+                   "applied_when": f"rel-L2 of outstanding update <= {TOL} on every replica",
+                   "l2": "inputs larger than L2 (400 MB per array)"},
+        "final_rel_err": rel, "gpu_launches": launches, "clocks": clocks,
+        "latency_ms": {"p50": lat_ms[len(lat_ms) // 2] if lat_ms else None,
+                       "p99": lat_ms[min(len(lat_ms) - 1, int(0.99 * len(lat_ms)))] if lat_ms else None,
+                       "probes": len(lat_ms), "clock": "host wall clock after a barrier, max over ranks"},
+        "device_status": stats.get("device"),
+    }
+    if e2e:
+        out["e2e"] = e2e
+    return out
+
+
+# ======================================================================================================
+# reference arm: the unmodified reference (one CPU process per rank, loopback TCP), same workload
+# ======================================================================================================
+def run_reference(args) -> dict | None:
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import build_ref
+    from ref_worker import RefWorker
+
+    rank, local_rank, world = env_rank()
+    lib = build_ref.build()
+    if lib is None:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "reference source not found (baseline/_ref/sharedtensor.c missing)"}))
+        return None
+    if world > 1:
+        dist.init_process_group("gloo")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def allmax(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n = args.elements
+    threads = max(1, (os.cpu_count() or 8) // max(world, 1) // 2)
+
+    def randn_seeded(seed: int, std: float) -> torch.Tensor:
+        g = torch.Generator().manual_seed(seed)
+        return torch.randn(n, generator=g, dtype=torch.float32) * std
+
+    # expected values on the sample (every rank regenerates every rank's seeded deltas, as the worker does)
+    expect_s = randn_seeded(7, INIT_STD)[::SAMPLE_STRIDE].clone()
+    pool_s = {}
+    for r in range(world):
+        for p in range(POOL):
+            pool_s[(r, p)] = randn_seeded(seed_of(r, p), DELTA_STD)[::SAMPLE_STRIDE].clone()
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 23
+    w = RefWorker(n, threads=threads)
+    tmp = f"/tmp/ref_sample_{os.getpid()}.pt"
+    try:
+        for r in range(world):
+            if r == rank:
+                if rank == 0:
+                    w.call(op="create", host="127.0.0.1", port=port, n=n, seed=7, std=INIT_STD)
+                else:
+                    w.call(op="create", host="127.0.0.1", port=port, n=n)
+            barrier()
+        w.call(op="pool", seeds=[seed_of(rank, p) for p in range(POOL)], std=DELTA_STD)
+        rng = torch.Generator().manual_seed(99 + rank)
+
+        def rel_err(upd2: float) -> float:
+            w.call(op="sample", stride=SAMPLE_STRIDE, path=tmp)
+            s = torch.load(tmp)
+            return float(((s - expect_s).double() ** 2).sum() / upd2) ** 0.5 if upd2 > 0 else 0.0
+
+        def run_steps(k0: int, steps: int, cap: float):
+            total = torch.zeros_like(expect_s)
+            for r in range(world):
+                for j in range(steps):
+                    total.add_(pool_s[(r, (k0 + j) % POOL)])
+            expect_s.add_(total)
+            upd2 = float((total.double() ** 2).sum())
+            barrier()
+            t0 = time.perf_counter()
+            for j in range(steps):
+                u = float(torch.rand(1, generator=rng))
+                time.sleep((CADENCE_MS[0] + u * (CADENCE_MS[1] - CADENCE_MS[0])) / 1e3)
+                w.call(op="add_pool", seed=seed_of(rank, (k0 + j) % POOL))
+            rel, converged = float("inf"), False
+            while True:
+                rel = rel_err(upd2)
+                if rel <= TOL:
+                    converged = True
+                    break
+                if time.perf_counter() - t0 > cap:
+                    break
+            return time.perf_counter() - t0, rel, converged
+
+        if args.warmup:
+            run_steps(0, args.warmup, args.ref_time_cap / 2)
+        secs, rel, conv = run_steps(args.warmup, args.steps, args.ref_time_cap)
+        secs = allmax(secs)
+        rel = allmax(rel)
+        conv_all = allmax(0.0 if conv else 1.0) == 0.0
+        barrier()
+    finally:
+        w.kill()
+        if os.path.exists(tmp):
+            os.remove(tmp)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    return {
+        "metric": "applied_updates_per_s", "value": world * args.steps / secs, "unit": "updates/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3 / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "reference",
+        "converged": conv_all, "final_rel_err": rel,
+        "note": None if conv_all else f"replicas had not reached {TOL} relative error when the {args.ref_time_cap:.0f}s cap ended the wait; "
+                                      "value is an upper bound",
+        "config": {"model": "shared parameter vector, 100M fp32 elements ~ N(0,1)", "elements": n, "global_batch": world, "seq_len": None,
+                   "parallelism": f"async-dp{world} (reference: CPU processes, binary tree over loopback TCP)", "delta": "N(0,1e-3) fp32",
+                   "cadence_ms": list(CADENCE_MS), "applied_when": f"rel-L2 of outstanding update <= {TOL} on every replica"},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    args = parse_args()
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

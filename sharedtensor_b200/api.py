@@ -59,6 +59,23 @@ class SharedTensor:
         dev = self._b.device
         self._b.sub_add(_check(new, self._n, dev, "pushUpdate(new)"), _check(old, self._n, dev, "pushUpdate(old)"))
 
+    def copyToTensorBF16(self, t: torch.Tensor) -> torch.Tensor:
+        """``t <- bf16(values)`` in one pass (GPU replicas; bf16 compute over fp32 master weights)."""
+        if t.dtype != torch.bfloat16 or t.numel() != self._n or not t.is_contiguous():
+            raise ValueError("copyToTensorBF16 needs a contiguous bfloat16 tensor of the shared size")
+        if hasattr(self._b, "copy_to_bf16"):
+            self._b.copy_to_bf16(t)
+        else:
+            tmp = torch.empty(self._n, dtype=torch.float32, device=self._b.device)
+            self._b.copy_to(tmp)
+            t.copy_(tmp)
+        return t
+
+    def step(self, rounds: int = 1) -> None:
+        """Runs ``rounds`` sync rounds now (only needed with ``engine='manual'``)."""
+        if hasattr(self._b, "step"):
+            self._b.step(rounds)
+
     def flush(self, timeout: float = 30.0) -> bool:
         """Waits until this replica has nothing left to send and nothing arriving."""
         return self._b.flush(timeout)

@@ -1,0 +1,82 @@
+"""Child process of test_gpu_multi.py: one GPU replica per process, joined through the TCP tree and upgraded
+to peer-memory edges.  Prints one JSON line with what it observed."""
+import json
+import sys
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch  # noqa: E402
+
+import sharedtensor  # noqa: E402
+
+
+def main():
+    rank, world, port, n, scenario = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    init = torch.randn(n, generator=g, device=dev)
+    time.sleep(0.4 * rank)  # join in rank order
+    st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), rejoin_backoff_ms=100)
+    out = torch.empty(n, device=dev)
+    st.copyToTensor(out)
+    torch.cuda.synchronize()
+    res = {"rank": rank, "master": st.is_master, "joined_exact": bool(torch.equal(out, init))}
+    # every rank adds its own delta; all must reach the sum
+    deltas = []
+    for r in range(world):
+        g.manual_seed(77 + r)
+        deltas.append(torch.randn(n, generator=g, device=dev) * 1e-2)
+    time.sleep(0.5 * (world - rank))  # everybody is in
+    st.addFromTensor(deltas[rank])
+    expect = init + sum(deltas)
+    if scenario == "kill_leaf" and rank == world - 1:
+        # leave between steps with nothing in flight: wait for own update to be delivered, then exit
+        st.flush(10.0)
+        time.sleep(0.5)
+        res["exiting"] = True
+        print(json.dumps(res), flush=True)
+        import os
+
+        os._exit(0)
+    deadline = time.time() + 30
+    rel = None
+    while time.time() < deadline:
+        st.copyToTensor(out)
+        torch.cuda.synchronize()
+        rel = ((out - expect).norm() / expect.norm()).item()
+        if rel < 5e-5:
+            break
+        time.sleep(0.01)
+    res["rel"] = rel
+    if scenario == "kill_leaf":
+        # survivors: the dead neighbour is noticed on the host, the edge is dropped, work goes on
+        time.sleep(1.5)
+        extra = torch.full((n,), 0.5, device=dev)
+        if rank == 0:
+            st.addFromTensor(extra)
+        expect2 = expect + 0.5
+        deadline = time.time() + 20
+        while time.time() < deadline:
+            st.copyToTensor(out)
+            torch.cuda.synchronize()
+            rel2 = ((out - expect2).norm() / expect2.norm()).item()
+            if rel2 < 5e-5:
+                break
+            time.sleep(0.01)
+        res["rel_after_loss"] = rel2
+    s = st.stats()
+    res["edges"] = {k: v["state"] for k, v in s["edges"].items()}
+    res["edge_failures"] = s["edge_failures"]
+    res["errors"] = s["device"]["errors"]
+    res["frames_sent"] = s["device"]["frames_sent"]
+    print(json.dumps(res), flush=True)
+    time.sleep(1.0 + 0.3 * rank)  # leaves first
+    st.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -272,7 +272,7 @@ def test_chain_forwarding_converges_to_the_sum(cu):
     reps[0].load_values(init.data_ptr(), _stream())
     # late-join emulation: B and C start from zero and are streamed the state
     expect = init.clone()
-    for it in range(80):
+    for it in range(150):  # the 1-bit stream removes ~16 % of the outstanding error per round and hop
         if it in (10, 20, 30):
             for i, r in enumerate(reps):
                 d = torch.randn(n, device="cuda") * 1e-2 * (i + 1)

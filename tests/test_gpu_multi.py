@@ -1,0 +1,58 @@
+"""T6: GPU replicas in separate processes on separate GPUs: TCP join, upgrade to peer-memory rings, snapshot on
+join, convergence to the sum, and a rank that leaves (host-side failure: it exits between steps)."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = Path(__file__).resolve().parent
+
+
+def _run(world, port, n, scenario):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(HERE / "gpu_multi_worker.py"), str(r), str(world), str(port), str(n), scenario],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env) for r in range(world)]
+    results = []
+    for p in procs:
+        try:
+            out, err = p.communicate(timeout=180)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, err = p.communicate()
+        lines = [ln for ln in out.splitlines() if ln.startswith("{")]
+        assert lines, f"worker produced no result; rc={p.returncode}\n{err[-2000:]}"
+        results.append(json.loads(lines[-1]))
+    return results
+
+
+def _need(k):
+    if torch.cuda.device_count() < k:
+        pytest.skip(f"needs {k} GPUs")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tree_over_peer_memory(free_port, world):
+    _need(world)
+    res = _run(world, free_port, 5 * 4096 + 321, "sum")
+    assert sum(r["master"] for r in res) == 1
+    for r in res:
+        assert r["joined_exact"], "a joiner starts from an exact snapshot of its parent"
+        assert r["rel"] is not None and r["rel"] < 5e-5, r
+        assert r["errors"] == 0
+    assert res[1]["edges"]["up"] == "connected"
+
+
+def test_rank_leaves_between_steps(free_port):
+    _need(3)
+    res = _run(3, free_port, 3 * 4096 + 5, "kill_leaf")
+    assert res[2].get("exiting")
+    for r in res[:2]:
+        assert r["rel"] < 5e-5
+        assert r["rel_after_loss"] < 5e-5, r
+    assert res[0]["edge_failures"] == 1, "the master lost its right child and noticed it on the host"
+    assert res[0]["edges"]["right"] == "free"
