@@ -126,25 +126,27 @@ def run_ours(args) -> dict | None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     cu = _native.cuda()
+    # Host-side coordination only (barriers, max/sum of a few scalars) goes through gloo: a barrier kernel
+    # spinning on the GPU while a neighbour is still mapping memory would stall the driver calls it needs.
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("gloo")
 
     def barrier():
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
 
     def allmax(x: float) -> float:
         if world == 1:
             return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        t = torch.tensor([x], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
     def allsum(x: float) -> float:
         if world == 1:
             return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        t = torch.tensor([x], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 

@@ -1,5 +1,5 @@
 """``import sharedtensor`` — the module name the reference is loaded under (``require 'sharedtensor'``,
 example.lua:2).  Everything lives in :mod:`sharedtensor_b200`."""
-from sharedtensor_b200 import Config, SharedTensor, createOrFetch  # noqa: F401
+from sharedtensor_b200 import Config, SharedTable, SharedTensor, createOrFetch, createOrFetchTable  # noqa: F401
 
-__all__ = ["createOrFetch", "SharedTensor", "Config"]
+__all__ = ["createOrFetch", "createOrFetchTable", "SharedTensor", "SharedTable", "Config"]

@@ -5,7 +5,8 @@ Same API and tree-join protocol as Hello1024/shared-tensor (``createOrFetch``, `
 error-feedback deltas through peer memory over NVLink.
 """
 from .api import SharedTensor, createOrFetch
+from .ops.table import SharedTable, createOrFetchTable
 from .utils.config import Config
 
-__all__ = ["SharedTensor", "createOrFetch", "Config"]
+__all__ = ["SharedTensor", "createOrFetch", "SharedTable", "createOrFetchTable", "Config"]
 __version__ = "0.1.0"

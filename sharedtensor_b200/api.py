@@ -71,6 +71,15 @@ class SharedTensor:
             t.copy_(tmp)
         return t
 
+    def addScaledBF16(self, g: torch.Tensor, alpha: float) -> None:
+        """``values += alpha * g`` for a bfloat16 ``g`` (an SGD step on bf16 gradients fused with the add)."""
+        if g.dtype != torch.bfloat16 or g.numel() != self._n or not g.is_contiguous():
+            raise ValueError("addScaledBF16 needs a contiguous bfloat16 tensor of the shared size")
+        if hasattr(self._b, "add_scaled_bf16"):
+            self._b.add_scaled_bf16(g, float(alpha))
+        else:
+            self._b.add((g.to(torch.float32) * alpha).to(self._b.device))
+
     def step(self, rounds: int = 1) -> None:
         """Runs ``rounds`` sync rounds now (only needed with ``engine='manual'``)."""
         if hasattr(self._b, "step"):

@@ -120,6 +120,7 @@ PYBIND11_MODULE(_cuda, m) {
       .def("load_values", [](GpuReplica& r, uintptr_t src, uintptr_t s) { r.load_values(ptr<float>(src), strm(s)); })
       .def("add", [](GpuReplica& r, uintptr_t d, uintptr_t s) { r.add(ptr<float>(d), strm(s)); })
       .def("sub_add", [](GpuReplica& r, uintptr_t a, uintptr_t b, uintptr_t s) { r.sub_add(ptr<float>(a), ptr<float>(b), strm(s)); })
+      .def("add_scaled_bf16", [](GpuReplica& r, uintptr_t g, float alpha, uintptr_t s) { r.add_scaled_bf16(ptr<void>(g), alpha, strm(s)); })
       .def("snapshot", [](GpuReplica& r, uintptr_t out, uintptr_t s) { r.snapshot(ptr<float>(out), strm(s)); })
       .def("snapshot_bf16", [](GpuReplica& r, uintptr_t out, uintptr_t s) { r.snapshot_bf16(ptr<void>(out), strm(s)); })
       .def("copy_mirror_from_values", &GpuReplica::copy_mirror_from_values)

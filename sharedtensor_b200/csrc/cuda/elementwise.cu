@@ -188,6 +188,46 @@ int launch_sub_add(float* values, const float* neu, const float* old, int64_t n,
   return launch_add_t<true>(values, neu, old, n, tile_state, n_tiles, atomic, static_cast<cudaStream_t>(stream));
 }
 
+// values += alpha * g for a bf16 gradient: the optimiser step of plain SGD fused with addFromTensor, so
+// that bf16 training never materialises an fp32 delta.
+__global__ void __launch_bounds__(kEwThreads) add_scaled_bf16_vec(float4* __restrict__ values, const uint2* __restrict__ g, float alpha,
+                                                                  int64_t n4, uint8_t* __restrict__ tile_state, int n_tiles) {
+  int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * kEwThreads;
+  for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
+  for (; i < n4; i += stride) {
+    uint2 raw = g[i];
+    __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+    float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    float4 v = values[i];
+    v.x += alpha * a.x;
+    v.y += alpha * a.y;
+    v.z += alpha * b.x;
+    v.w += alpha * b.y;
+    values[i] = v;
+  }
+}
+__global__ void add_scaled_bf16_scalar(float* __restrict__ values, const __nv_bfloat16* __restrict__ g, float alpha, int64_t begin,
+                                       int64_t n, uint8_t* __restrict__ tile_state, int n_tiles, int mark) {
+  int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  if (mark)
+    for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
+  for (i += begin; i < n; i += stride) values[i] += alpha * __bfloat162float(g[i]);
+}
+int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, uint8_t* tile_state, int n_tiles, void* stream_v) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream_v);
+  bool al = aligned16(values) && (reinterpret_cast<uintptr_t>(g_bf16) & 7) == 0;
+  int64_t n4 = al ? n / 4 : 0;
+  if (n4)
+    add_scaled_bf16_vec<<<ew_blocks(n4), kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), static_cast<const uint2*>(g_bf16), alpha,
+                                                            n4, tile_state, n_tiles);
+  if (n4 * 4 < n)
+    add_scaled_bf16_scalar<<<ew_blocks(n - n4 * 4), kEwThreads, 0, s>>>(values, static_cast<const __nv_bfloat16*>(g_bf16), alpha, n4 * 4,
+                                                                        n, tile_state, n_tiles, n4 == 0);
+  return int(cudaGetLastError());
+}
+
 __global__ void fill_state_kernel(uint8_t* s, int n, uint8_t v) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) s[i] = v;

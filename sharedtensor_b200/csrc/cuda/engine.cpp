@@ -335,6 +335,15 @@ void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) 
   order_user_after(user_stream);
 }
 
+void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) {
+  DeviceGuard gd(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  order_after_user(user_stream);
+  check(launch_add_scaled_bf16(values(), g, alpha, n_, tile_state_, n_tiles_, comm_), "add_scaled_bf16 kernel");
+  launches_ += 1;
+  order_user_after(user_stream);
+}
+
 void GpuReplica::snapshot(float* out, void* user_stream) {
   DeviceGuard g(device_);
   check(launch_snapshot_f32(values(), out, n_, user_stream), "snapshot kernel");
@@ -402,12 +411,15 @@ std::string GpuReplica::last_error() const {
 // engine thread
 // ---------------------------------------------------------------------------------------------
 void GpuReplica::start_engine() {
-  if (engine_on_.exchange(true)) return;
+  std::lock_guard<std::mutex> g(engine_mu_);
+  if (engine_on_.load()) return;
   engine_stop_.store(false);
   engine_ = std::thread([this] { engine_loop(); });
+  engine_on_.store(true);
 }
 
 void GpuReplica::stop_engine() {
+  std::lock_guard<std::mutex> g(engine_mu_);
   if (!engine_on_.load()) return;
   engine_stop_.store(true);
   if (engine_.joinable()) engine_.join();

@@ -69,6 +69,7 @@ class GpuReplica {
   void load_values(const float* src, void* user_stream);
   void add(const float* delta, void* user_stream);
   void sub_add(const float* neu, const float* old, void* user_stream);
+  void add_scaled_bf16(const void* g_bf16, float alpha, void* user_stream);  // values += alpha * g
   void snapshot(float* out, void* user_stream);
   void snapshot_bf16(void* out, void* user_stream);
   void copy_mirror_from_values(int link);                 // mirror <- values (neighbour is given a snapshot)
@@ -136,6 +137,7 @@ class GpuReplica {
   void* ev_comm_ = nullptr;            // cudaEvent_t: comm -> user stream
   std::vector<void*> ev_round_;
   mutable std::mutex mu_;
+  std::mutex engine_mu_;               // serialises start_engine / stop_engine
   std::thread engine_;
   std::atomic<bool> engine_on_{false}, engine_stop_{false};
   std::atomic<uint64_t> launches_{0};

@@ -203,6 +203,7 @@ class GpuNode {
     int tcp_fd = -1;
     sockaddr_in peer{};
     uint64_t adopted_ms = 0;
+    bool upgrading = false;  // the parent side of the upgrade is at work on this edge
     int link = -1, peer_id = -1, block = -1;
     VmmBlock remote;      // neighbour's edge block mapped here
   };
@@ -420,6 +421,7 @@ class GpuNode {
           if (edges_[s].state == 1 && edges_[s].peer.sin_port == h.listen_addr.sin_port &&
               edges_[s].peer.sin_addr.s_addr == h.listen_addr.sin_addr.s_addr) {
             slot = s;
+            edges_[s].upgrading = true;
             return true;
           }
         }
@@ -467,6 +469,7 @@ class GpuNode {
         std::lock_guard<std::mutex> g(mu_);
         Edge& e = edges_[slot];
         e.state = 2;
+        e.upgrading = false;
         e.link = link;
         e.block = block;
         e.peer_id = pid;
@@ -498,7 +501,8 @@ class GpuNode {
           }
           // a child that was adopted over TCP but never came in over the unix socket is a TCP-only
           // peer (CPU node, reference, other host): not served by this class
-          if (edges_[s].state == 1 && now_ms() - edges_[s].adopted_ms > uint64_t(opt_.upgrade_timeout_ms) * 2) {
+          if (edges_[s].state == 1 && !edges_[s].upgrading &&
+              now_ms() - edges_[s].adopted_ms > uint64_t(opt_.upgrade_timeout_ms) * 2) {
             pfds.push_back({-1, 0, 0});
             slots.push_back(-(s + 1));
           }

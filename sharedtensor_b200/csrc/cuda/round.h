@@ -102,6 +102,8 @@ int launch_snapshot_bf16(const float* values, void* out_bf16, int64_t n, void* s
 int launch_add(float* values, const float* delta, int64_t n, uint8_t* tile_state, int n_tiles, int atomic, void* stream);
 int launch_sub_add(float* values, const float* neu, const float* old, int64_t n, uint8_t* tile_state, int n_tiles,
                    int atomic, void* stream);
+int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, uint8_t* tile_state, int n_tiles,
+                           void* stream);
 int launch_fill_state(uint8_t* tile_state, int n_tiles, int value, void* stream);
 // Per-segment sum of squares (table sync).  partials: scratch of table_scales_scratch_doubles(...) doubles.
 int64_t table_scales_scratch_doubles(int n_seg, int64_t n_total);

@@ -60,6 +60,9 @@ class GpuBackend:
     def sub_add(self, new: torch.Tensor, old: torch.Tensor) -> None:
         self.rep.sub_add(new.data_ptr(), old.data_ptr(), _stream(self.device))
 
+    def add_scaled_bf16(self, g: torch.Tensor, alpha: float) -> None:
+        self.rep.add_scaled_bf16(g.data_ptr(), alpha, _stream(self.device))
+
     def copy_to(self, out: torch.Tensor) -> None:
         self.rep.snapshot(out.data_ptr(), _stream(self.device))
 

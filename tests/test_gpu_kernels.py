@@ -310,7 +310,7 @@ def test_mesh_group_no_forwarding(cu):
         r.load_values(init.data_ptr(), _stream())
         r.copy_mirror_from_values(0)
     expect = init.clone()
-    for it in range(60):
+    for it in range(110):
         if it in (0, 7, 19):
             for i, r in enumerate(reps):
                 d = torch.randn(n, device="cuda") * 1e-2 * (i + 1)
@@ -335,7 +335,7 @@ def test_atomic_values_mode_matches_within_rounding(cu):
     connect_local(A, B)
     init = torch.randn(n, device="cuda")
     A.load_values(init.data_ptr(), _stream())
-    for _ in range(60):
+    for _ in range(110):
         A.round()
         B.round()
     A.sync()
