@@ -23,7 +23,7 @@ CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 
 CORE_SOURCES = ["core/codec.cpp", "core/tree.cpp", "core/node.cpp", "core/bindings.cpp"]
-CUDA_SOURCES_CU = ["cuda/elementwise.cu", "cuda/round.cu"]
+CUDA_SOURCES_CU = ["cuda/elementwise.cu", "cuda/round.cu", "cuda/noalloc.cu"]
 CUDA_SOURCES_CPP = ["core/codec.cpp", "core/tree.cpp", "cuda/vmm.cpp", "cuda/engine.cpp", "cuda/gpu_node.cpp",
                     "cuda/bindings_cuda.cpp"]
 
