@@ -45,7 +45,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--elements", type=int, default=N_ELEMENTS)
     ap.add_argument("--probes", type=int, default=24, help="single-update latency probes after the timed region")
-    ap.add_argument("--topology", default="tree", choices=["tree"])
+    ap.add_argument("--topology", default="tree", choices=["tree", "mesh"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ref-time-cap", type=float, default=120.0, help="wall-clock cap of the reference arm's wait, seconds")
     return ap.parse_args()
@@ -179,10 +179,15 @@ def run_ours(args) -> dict | None:
     # ---- the tree: ranks join one after the other so that the shape is the reference's (left, right, redirect ...)
     port = int(os.environ.get("MASTER_PORT", "29500")) + 17
     st = None
-    for r in range(world):
-        if r == rank:
-            st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev))
+    if args.topology == "mesh":
+        st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev), topology="mesh",
+                                        group_rank=rank, group_size=world)
         barrier()
+    else:
+        for r in range(world):
+            if r == rank:
+                st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev))
+            barrier()
     assert st is not None
     del init
     rep = st._b.rep
@@ -302,7 +307,7 @@ def run_ours(args) -> dict | None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3 / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "ours",
         "config": {"model": "shared parameter vector, 100M fp32 elements ~ N(0,1)", "elements": n, "global_batch": world,
-                   "seq_len": None, "parallelism": f"async-dp{world} (tree over NVLink peer memory)",
+                   "seq_len": None, "parallelism": f"async-dp{world} ({args.topology} over NVLink peer memory)",
                    "delta": "N(0,1e-3) fp32", "cadence_ms": list(CADENCE_MS), "scale_block": 32,
                    "applied_when": f"rel-L2 of outstanding update <= {TOL} on every replica",
                    "l2": "inputs larger than L2 (400 MB per array)"},

@@ -1,0 +1,158 @@
+#!/usr/bin/env python
+"""Sync bandwidth / latency sweep over tensor sizes (1 Ki .. 1 Gi fp32 elements, powers of 4).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29500 \
+        benchmarks/sync_sweep.py [--max-log4 15] [--out gpurun_out/sweep.json]
+
+For every size and the N ranks of one box it measures, with deltas ~ N(0,1):
+  * the compressed path of this framework: device time of one sync round under load (max over ranks), the
+    HBM bytes that round moves per rank and the packed bytes it puts on each edge, and the wall-clock time
+    until one update has reached every replica to 1 % (engine free-running);
+  * the baseline: an NCCL all-reduce of the uncompressed fp32 delta followed by the local add.
+It prints one JSON object per size on rank 0 and a summary table at the end.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+import sharedtensor  # noqa: E402
+from sharedtensor_b200 import _native  # noqa: E402
+
+TOL = 1e-2
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-log4", type=int, default=5)    # 4^5 = 1 Ki
+    ap.add_argument("--max-log4", type=int, default=15)   # 4^15 = 1 Gi
+    ap.add_argument("--probes", type=int, default=8)
+    ap.add_argument("--rounds", type=int, default=20)
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    rank, local, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cu = _native.cuda()
+    dist.init_process_group("gloo")
+    nccl = dist.new_group(backend="nccl") if world > 1 else None
+    stream = torch.cuda.current_stream().cuda_stream
+    base_port = int(os.environ.get("MASTER_PORT", "29500")) + 100
+    peaks = {}
+    pk = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+    hbm = peaks.get("hbm_gbs", 6650.0)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    def allmax(x):
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    rows = []
+    for i, k in enumerate(range(args.min_log4, args.max_log4 + 1)):
+        n = 4 ** k
+        g = torch.Generator(device=dev).manual_seed(5)
+        init = torch.randn(n, generator=g, device=dev)
+        deltas = []
+        for r in range(world):
+            g.manual_seed(100 + r)
+            deltas.append(torch.randn(n, generator=g, device=dev))
+        # ---- our path
+        st = None
+        for r in range(world):
+            if r == rank:
+                st = sharedtensor.createOrFetch("127.0.0.1", base_port + i, init if rank == 0 else torch.empty(n, device=dev))
+            barrier()
+        rep = st._b.rep
+        expect = init.clone()
+        out = torch.empty(n, device=dev)
+        lat = []
+        for pr in range(args.probes):
+            origin = pr % world
+            expect += deltas[origin]
+            upd = float(deltas[origin].norm())
+            barrier()
+            t0 = time.perf_counter()
+            if rank == origin:
+                st.addFromTensor(deltas[origin])
+            while True:
+                st.copyToTensor(out)
+                torch.cuda.synchronize()
+                if float((out - expect).norm()) <= TOL * upd or time.perf_counter() - t0 > 10:
+                    break
+            lat.append(allmax(time.perf_counter() - t0))
+        # device time of a round under load: stop the engine thread and drive rounds by hand
+        rep.stop_engine()
+        barrier()
+        cs = torch.cuda.ExternalStream(rep.comm_stream())
+        times = []
+        for j in range(args.rounds):
+            rep.add(deltas[rank].data_ptr(), rep.comm_stream())
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(cs)
+            rep.round()
+            e1.record(cs)
+            rep.sync()
+            times.append(e0.elapsed_time(e1))
+            if j % 4 == 3:
+                barrier()
+        times = sorted(times[3:])
+        round_ms = allmax(times[len(times) // 2])
+        links = sum(1 for e in st.stats()["edges"].values() if e["state"] == "connected")
+        max_links = int(allmax(float(links)))
+        barrier()
+        st.close()
+        barrier()
+        # ---- baseline: NCCL all-reduce of the fp32 delta + local add
+        ar_ms = None
+        if nccl is not None:
+            buf = deltas[rank].clone()
+            for _ in range(3):
+                dist.all_reduce(buf, group=nccl)
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(10):
+                buf.copy_(deltas[rank])
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                dist.all_reduce(buf, group=nccl)
+                out.add_(buf)
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ar_ms = allmax(sorted(ts)[len(ts) // 2])
+        lat_ms = sorted(x * 1e3 for x in lat)
+        hbm_bytes = (8 + 8 * max_links) * n  # values + one mirror per link, read and written
+        edge_bytes = 3 * (n / 8 + n / 32)   # three 1-bit frames with block-32 scales per round and edge direction
+        row = {"elements": n, "n_gpus": world, "round_ms": round_ms, "links_max": max_links,
+               "round_hbm_GBs": hbm_bytes / round_ms / 1e6, "round_hbm_frac_of_measured": hbm_bytes / round_ms / 1e6 / hbm,
+               "edge_bytes_per_round": edge_bytes, "edge_GBs": edge_bytes / round_ms / 1e6,
+               "nvlink_roofline_ms": edge_bytes / 770e9 * 1e3, "hbm_roofline_ms": hbm_bytes / (hbm * 1e9) * 1e3,
+               "latency_ms_p50": lat_ms[len(lat_ms) // 2], "latency_ms_max": lat_ms[-1],
+               "nccl_allreduce_add_ms": ar_ms}
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+        del init, deltas, expect, out
+        torch.cuda.empty_cache()
+    if rank == 0 and args.out:
+        Path(args.out).write_text(json.dumps(rows, indent=1))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

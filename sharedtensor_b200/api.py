@@ -159,7 +159,11 @@ def createOrFetch(host: str, port: int, tensor: torch.Tensor, **options: Any) ->
         transport = "gpu" if on_gpu else "tcp"
     if transport == "gpu" and not on_gpu:
         raise ValueError("transport='gpu' needs a CUDA tensor")
-    if transport == "gpu":
+    if transport == "gpu" and cfg.topology == "mesh":
+        from .parallel.gpu_backend import GpuMeshBackend
+
+        backend = GpuMeshBackend(n, cfg, flat.device)
+    elif transport == "gpu":
         from .parallel.gpu_backend import GpuBackend
 
         backend = GpuBackend(n, cfg, flat.device)

@@ -30,6 +30,7 @@ struct GpuConfig {
   bool atomic_values = false;
   int rounds_in_flight = 2;
   int idle_sleep_us = 200;
+  int frames_per_round = 1;  // successive 1-bit frames per link and round (1..3)
 };
 
 struct EdgeBlockLayout {

@@ -143,11 +143,15 @@ __global__ void __launch_bounds__(256) round_publish_kernel(const __grid_constan
     }
   }
   for (int r = 0; r < p.n_out; r++) {
-    if (ps[r]) {
-      uint32_t seq = p.out[r].tx_seq[tile] + 1;
-      int slot = pc[8 + r] & 63;
+    const int frames = ps[r];  // frames written for this ring, in consecutive slots
+    if (frames) {
+      uint32_t seq = p.out[r].tx_seq[tile];
+      const int slot0 = pc[8 + r] & 63;
+      for (int f = 0; f < frames; f++) {
+        seq++;
+        st_release_sys(p.out[r].flags_remote + size_t((slot0 + f) % p.ring_slots) * p.n_tiles + tile, seq);
+      }
       p.out[r].tx_seq[tile] = seq;
-      st_release_sys(p.out[r].flags_remote + size_t(slot) * p.n_tiles + tile, seq);
     }
   }
   *reinterpret_cast<uint4*>(cptr) = make_uint4(0u, 0u, 0u, 0u);
@@ -189,8 +193,9 @@ __global__ void __launch_bounds__(256) round_begin_kernel(const __grid_constant_
     for (int r = 0; r < p.n_out; r++) {
       uint32_t t = p.out[r].tx_seq[tile];
       uint32_t c = ld_acquire_sys(p.out[r].credit + tile);
-      bool can = (t - c) < S;
-      cc[8 + r] = uint8_t((can ? 64 : 0) | int(t % S));
+      uint32_t used = t - c;
+      uint32_t room = used < S ? S - used : 0u;  // free slots, reported up to 3
+      cc[8 + r] = uint8_t((min(room, 3u) << 6) | (t % S));
     }
   }
   *reinterpret_cast<uint4*>(p.ctrl + size_t(tile) * 16) = cur;
@@ -224,7 +229,8 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ void group_bar(int group) {
   asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kGroupThreads) : "memory");
 }
-constexpr uint32_t kFlagChanged = 1, kFlagNonsilent = 2, kFlagFailed = 4;
+constexpr uint32_t kFlagChanged = 1, kFlagFailed = 2, kFlagNonsilent0 = 4;  // nonsilent: one bit per pass, 4 << f
+constexpr int kMaxFrames = 3;       // 1-bit frames per link, tile and round
 
 __device__ __forceinline__ uint32_t ld_u32_ca(const void* p) {
   uint32_t v;
@@ -244,7 +250,7 @@ __device__ __forceinline__ float signed_scale(uint32_t scale_bits, uint32_t w, i
 
 struct GroupSmem {
   int off_slots;    // [kGroups][kSlots][kTileBytes]
-  int off_out;      // [kGroups][2][payload_bytes]
+  int off_out;      // [kGroups][2][3 frames][payload_bytes]
   int off_bar;      // uint64_t[kGroups][kSlots]
   int off_red;      // float[kGroups][2][4]   cross-warp partials for blocks of 2048/4096
   int off_flags;    // uint32_t[kGroups][3]  per-step OR flags (changed / nonsilent / wait failed)
@@ -256,7 +262,7 @@ __host__ __device__ inline GroupSmem group_layout(int payload_bytes) {
   m.off_slots = off;
   off += kGroups * kSlots * kTileBytes;
   m.off_out = off;
-  off += kGroups * 2 * ((payload_bytes + 127) & ~127);
+  off += kGroups * 2 * 3 * ((payload_bytes + 127) & ~127);
   m.off_bar = off;
   off += 8 * kGroups * kSlots;
   m.off_red = off;
@@ -286,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
   const int sw = t & 7;             // XOR swizzle of this thread's eight 16-byte pieces
   uint8_t* slots = smem + lay.off_slots + size_t(g) * kSlots * kTileBytes;
   const int pb_pad = (p.payload_bytes + 127) & ~127;
-  uint8_t* outbuf = smem + lay.off_out + size_t(g) * 2 * pb_pad;
+  uint8_t* outbuf = smem + lay.off_out + size_t(g) * 2 * kMaxFrames * pb_pad;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + g * kSlots;
   float* s_red = reinterpret_cast<float*>(smem + lay.off_red) + g * 8;
   uint32_t* s_flags = reinterpret_cast<uint32_t*>(smem + lay.off_flags) + g * 4;
@@ -414,91 +420,99 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
         }
       }
 
-      bool send = false;        // this link has room in every one of its out-rings
-      bool nonsilent = false;
+      int n_frames = 0;             // frames this step may push: room in every out-ring of the link, at most frames_per_round
+      uint32_t nonsilent_mask = 0;  // bit f: this thread's block had something to say in pass f
       if (a > 0) {
-        // ---------------- quantise values - mirror for link l
+        // ---------------- quantise values - mirror for link l, up to frames_per_round times in a row:
+        // every pass is one more 1-bit frame of the same stream, made while the data is in registers
+        int room = 3;             // free ring slots, the minimum over the link's out-rings
         bool any_ring = false;
-        send = true;
         for (int r = 0; r < p.n_out; r++) {
           if (p.out[r].link != l) continue;
           any_ring = true;
-          if (!(out_byte(r) & 64u)) send = false;
+          room = min(room, int(out_byte(r) >> 6));
         }
-        send = send && any_ring;
-        float px[8];
+        n_frames = any_ring ? min(room, p.frames_per_round) : 0;
         uint32_t vmax = 0;
 #pragma unroll
         for (int q = 0; q < 8; q++) {
-          float4 x;
-          x.x = __fsub_rn(v[q].x, k[q].x);
-          x.y = __fsub_rn(v[q].y, k[q].y);
-          x.z = __fsub_rn(v[q].z, k[q].z);
-          x.w = __fsub_rn(v[q].w, k[q].w);
-          px[q] = sumsq4(x);
           vmax = max(max(vmax, __float_as_uint(v[q].x) & 0x7fffffffu), __float_as_uint(v[q].y) & 0x7fffffffu);
           vmax = max(max(vmax, __float_as_uint(v[q].z) & 0x7fffffffu), __float_as_uint(v[q].w) & 0x7fffffffu);
         }
-        // pairwise tree over the eight pieces; the XOR swizzle permutes pieces only within each level's pairs
-        float sx = __fadd_rn(__fadd_rn(__fadd_rn(px[0], px[1]), __fadd_rn(px[2], px[3])),
-                             __fadd_rn(__fadd_rn(px[4], px[5]), __fadd_rn(px[6], px[7])));
-        if (l == 0) acc_res0 += sx; else if (l == 1) acc_res1 += sx; else acc_res2 += sx;
-        // blocks larger than 32 elements: butterfly over lanes (up to 1024), then over the group's warps
-        for (int sft = 0; sft < tpb && sft < 5; sft++) {
-          sx = __fadd_rn(sx, __shfl_xor_sync(0xffffffffu, sx, 1 << sft));
-          vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1 << sft));
-        }
-        if (tpb > 5) {
-          if (lane == 0) {
-            s_red[wig] = sx;
-            s_red[4 + wig] = __uint_as_float(vmax);
-          }
-          group_bar(g);
-          const float a0 = s_red[0], a1 = s_red[1], a2 = s_red[2], a3 = s_red[3];
-          const uint32_t b0 = __float_as_uint(s_red[4]), b1 = __float_as_uint(s_red[5]);
-          const uint32_t b2 = __float_as_uint(s_red[6]), b3 = __float_as_uint(s_red[7]);
-          if (tpb == 6) {  // 2048: warps {0,1} and {2,3}
-            sx = wig < 2 ? __fadd_rn(a0, a1) : __fadd_rn(a2, a3);
-            vmax = wig < 2 ? max(b0, b1) : max(b2, b3);
-          } else {         // 4096: the whole tile
-            sx = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
-            vmax = max(max(b0, b1), max(b2, b3));
-          }
-          group_bar(g);  // s_red is reused by the next link
-        }
+        for (int sft = 0; sft < tpb && sft < 5; sft++) vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1 << sft));
         int lbe = lb;
         if (tail_block >= 0 && (ebase >> lb) == tail_block) lbe = tail_lb;
-        const int code = block_code_dev(sx, vmax, lbe, p.min_exp, p.rel_bits);
-        nonsilent = code != 0;
-        if (send) {
-          const uint32_t sb = uint32_t(code) << 23;
-          uint32_t word = 0;
+        const int passes = n_frames > 0 ? n_frames : 1;  // without ring space one pass still tells whether work is left
+        for (int f = 0; f < passes; f++) {
+          float px[8];
 #pragma unroll
           for (int q = 0; q < 8; q++) {
-            const int m = q ^ sw;
-            const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
-            const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
-            bool v0 = true, v1 = true, v2 = true, v3 = true;
-            if (!full_chunk) {
-              const int64_t e = ebase + 4 * m;
-              v0 = e + 0 < n;
-              v1 = e + 1 < n;
-              v2 = e + 2 < n;
-              v3 = e + 3 < n;
-            }
-            const uint32_t nib = uint32_t(n0 && v0) | (uint32_t(n1 && v1) << 1) | (uint32_t(n2 && v2) << 2) | (uint32_t(n3 && v3) << 3);
-            word |= nib << (4 * m);
-            if (code) {
-              if (v0) k[q].x = __fadd_rn(k[q].x, __uint_as_float(sb | (n0 ? 0x80000000u : 0u)));
-              if (v1) k[q].y = __fadd_rn(k[q].y, __uint_as_float(sb | (n1 ? 0x80000000u : 0u)));
-              if (v2) k[q].z = __fadd_rn(k[q].z, __uint_as_float(sb | (n2 ? 0x80000000u : 0u)));
-              if (v3) k[q].w = __fadd_rn(k[q].w, __uint_as_float(sb | (n3 ? 0x80000000u : 0u)));
-            }
+            float4 x;
+            x.x = __fsub_rn(v[q].x, k[q].x);
+            x.y = __fsub_rn(v[q].y, k[q].y);
+            x.z = __fsub_rn(v[q].z, k[q].z);
+            x.w = __fsub_rn(v[q].w, k[q].w);
+            px[q] = sumsq4(x);
           }
-          if (code) changed = true;
-          uint8_t* ob = outbuf + size_t(c & 1) * pb_pad;
-          reinterpret_cast<uint32_t*>(ob)[t] = word;
-          if ((t & ((1 << tpb) - 1)) == 0) ob[4 * kWordsPerTile + (t >> tpb)] = uint8_t(code);
+          // pairwise tree over the eight pieces; the XOR swizzle permutes pieces only within each level's pairs
+          float sx = __fadd_rn(__fadd_rn(__fadd_rn(px[0], px[1]), __fadd_rn(px[2], px[3])),
+                               __fadd_rn(__fadd_rn(px[4], px[5]), __fadd_rn(px[6], px[7])));
+          if (f == 0) {
+            if (l == 0) acc_res0 += sx; else if (l == 1) acc_res1 += sx; else acc_res2 += sx;
+          }
+          // blocks larger than 32 elements: butterfly over lanes (up to 1024), then over the group's warps
+          for (int sft = 0; sft < tpb && sft < 5; sft++) sx = __fadd_rn(sx, __shfl_xor_sync(0xffffffffu, sx, 1 << sft));
+          uint32_t vm = vmax;
+          if (tpb > 5) {
+            if (lane == 0) {
+              s_red[wig] = sx;
+              s_red[4 + wig] = __uint_as_float(vmax);
+            }
+            group_bar(g);
+            const float a0 = s_red[0], a1 = s_red[1], a2 = s_red[2], a3 = s_red[3];
+            const uint32_t b0 = __float_as_uint(s_red[4]), b1 = __float_as_uint(s_red[5]);
+            const uint32_t b2 = __float_as_uint(s_red[6]), b3 = __float_as_uint(s_red[7]);
+            if (tpb == 6) {  // 2048: warps {0,1} and {2,3}
+              sx = wig < 2 ? __fadd_rn(a0, a1) : __fadd_rn(a2, a3);
+              vm = wig < 2 ? max(b0, b1) : max(b2, b3);
+            } else {         // 4096: the whole tile
+              sx = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
+              vm = max(max(b0, b1), max(b2, b3));
+            }
+            group_bar(g);  // s_red is reused by the next pass
+          }
+          const int code = block_code_dev(sx, vm, lbe, p.min_exp, p.rel_bits);
+          if (code) nonsilent_mask |= 1u << f;
+          if (n_frames > 0) {
+            const uint32_t sb = uint32_t(code) << 23;
+            uint32_t word = 0;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+              const int m = q ^ sw;
+              const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
+              const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
+              bool v0 = true, v1 = true, v2 = true, v3 = true;
+              if (!full_chunk) {
+                const int64_t e = ebase + 4 * m;
+                v0 = e + 0 < n;
+                v1 = e + 1 < n;
+                v2 = e + 2 < n;
+                v3 = e + 3 < n;
+              }
+              const uint32_t nib = uint32_t(n0 && v0) | (uint32_t(n1 && v1) << 1) | (uint32_t(n2 && v2) << 2) | (uint32_t(n3 && v3) << 3);
+              word |= nib << (4 * m);
+              if (code) {
+                if (v0) k[q].x = __fadd_rn(k[q].x, __uint_as_float(sb | (n0 ? 0x80000000u : 0u)));
+                if (v1) k[q].y = __fadd_rn(k[q].y, __uint_as_float(sb | (n1 ? 0x80000000u : 0u)));
+                if (v2) k[q].z = __fadd_rn(k[q].z, __uint_as_float(sb | (n2 ? 0x80000000u : 0u)));
+                if (v3) k[q].w = __fadd_rn(k[q].w, __uint_as_float(sb | (n3 ? 0x80000000u : 0u)));
+              }
+            }
+            if (code) changed = true;
+            uint8_t* ob = outbuf + size_t((c & 1) * kMaxFrames + f) * pb_pad;
+            reinterpret_cast<uint32_t*>(ob)[t] = word;
+            if ((t & ((1 << tpb) - 1)) == 0) ob[4 * kWordsPerTile + (t >> tpb)] = uint8_t(code);
+          }
         }
       }
 
@@ -526,7 +540,7 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
       }
       fence_async_smem();
       {
-        const uint32_t mine = (changed ? kFlagChanged : 0u) | (nonsilent ? kFlagNonsilent : 0u) | (wait_failed ? kFlagFailed : 0u);
+        const uint32_t mine = (changed ? kFlagChanged : 0u) | (nonsilent_mask * kFlagNonsilent0) | (wait_failed ? kFlagFailed : 0u);
         const uint32_t warp_bits = __reduce_or_sync(0xffffffffu, mine);
         if (lane == 0 && warp_bits) atomicOr(&s_flags[c % 3], warp_bits);
       }
@@ -537,8 +551,9 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
         break;
       }
       const bool any_changed = (step_flags & kFlagChanged) != 0;
-      const bool any_nonsilent = (step_flags & kFlagNonsilent) != 0;
-      pend_tile |= any_nonsilent;
+      const uint32_t ns_bits = step_flags / kFlagNonsilent0;  // bit f: pass f produced a frame worth sending
+      // work is left if the last pass still had something to say (or nothing could be sent at all)
+      pend_tile |= (ns_bits >> (n_frames > 0 ? n_frames - 1 : 0)) != 0;
 
       if (t == 0) {
         void* gdst = const_cast<float*>(src_of(tile, a));
@@ -548,16 +563,24 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
           else
             bulk_s2g(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
         }
-        if (a > 0 && send && any_nonsilent) {
-          const uint8_t* ob = outbuf + size_t(c & 1) * pb_pad;
+        if (a > 0 && n_frames > 0 && ns_bits) {
+          int sent_here = 0;
+          for (int f = 0; f < n_frames; f++) {
+            if (!((ns_bits >> f) & 1u)) continue;  // an all-silent pass is not a frame
+            const uint8_t* ob = outbuf + size_t((c & 1) * kMaxFrames + f) * pb_pad;
+            for (int r = 0; r < p.n_out; r++) {
+              if (p.out[r].link != l) continue;
+              const int slot_no = (int(out_byte(r) & 63u) + sent_here) % p.ring_slots;
+              bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + tile) * pb, ob, uint32_t(pb));
+              n_tx++;
+            }
+            sent_here++;
+          }
           for (int r = 0; r < p.n_out; r++) {
             if (p.out[r].link != l) continue;
-            const int slot_no = int(out_byte(r) & 63u);
-            bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + tile) * pb, ob, uint32_t(pb));
-            if (r < 4) sent_lo |= 1u << (r * 8); else sent_hi |= 1u << ((r - 4) * 8);
-            n_tx++;
+            if (r < 4) sent_lo |= uint32_t(sent_here) << (r * 8); else sent_hi |= uint32_t(sent_here) << ((r - 4) * 8);
           }
-        } else if (a > 0 && any_nonsilent && p.do_tx) {
+        } else if (a > 0 && ns_bits && p.do_tx) {
           n_blocked++;
         }
         bulk_commit();

@@ -27,7 +27,7 @@ namespace st {
 constexpr int kTile = 4096;         // elements per tile (= per independent stream)
 constexpr int kMaxLinks = 3;        // mirrors per replica
 constexpr int kMaxRings = 8;        // inbound rings, and outbound rings, per replica
-constexpr int kRxMax = 2;           // frames taken per ring per tile per round
+constexpr int kRxMax = 3;           // frames taken per ring per tile per round
 constexpr int kWordsPerTile = kTile / 32;
 
 struct InRing {
@@ -61,8 +61,8 @@ struct RoundParams {
   int32_t payload_bytes;         // 4*kWordsPerTile + max(16, scales_per_tile)
   int32_t min_exp, rel_bits;     // gate, see BlockGate
   // per-round scratch (all local)
-  uint8_t* ctrl;                 // [tile][16]: bytes 0..7 in-rings (avail<<6 | first slot), 8..15 out-rings (can_send<<6 | slot)
-  uint8_t* sent;                 // [tile][8]: 1 if round_main wrote a frame for out-ring r
+  uint8_t* ctrl;                 // [tile][16]: bytes 0..7 in-rings (avail<<6 | first slot), 8..15 out-rings (free slots, up to 3, <<6 | slot)
+  uint8_t* sent;                 // [tile][8]: number of frames round_main wrote for out-ring r
   uint8_t* tile_state;           // [tile]: 1 = something may be left to send
   int32_t* worklist;             // [n_tiles]
   int32_t* work_count;           // [2], double buffered by round parity
@@ -70,6 +70,7 @@ struct RoundParams {
   int32_t round;
   int32_t do_rx, do_tx;          // receiver-only / sender-only rounds
   int32_t atomic_values;         // values are updated with red.add (a concurrent add kernel may run)
+  int32_t frames_per_round;      // 1..3 successive 1-bit frames per link, tile and round
 };
 
 // indices into the status block (uint64 each)

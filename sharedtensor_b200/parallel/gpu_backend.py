@@ -25,6 +25,7 @@ def _gpu_config(cfg: Config):
     g.atomic_values = False
     g.rounds_in_flight = cfg.rounds_in_flight
     g.idle_sleep_us = cfg.idle_sleep_us
+    g.frames_per_round = cfg.frames_per_round
     return g
 
 
@@ -120,6 +121,45 @@ class GpuBackend:
 
     def inject_sever(self, slot: str) -> None:
         self.node.inject_sever(_SLOTS[slot])
+
+
+class GpuMeshBackend(GpuBackend):
+    """Fixed, fully connected group of GPU replicas on one host (``topology='mesh'``): one hop, no forwarding."""
+
+    def __init__(self, n: int, cfg: Config, device: torch.device):
+        import os
+
+        if not torch.cuda.is_available():
+            raise RuntimeError("the GPU transport needs a CUDA device")
+        cu = _native.cuda()
+        self.n = n
+        self.cfg = cfg
+        self.device = torch.device("cuda", device.index if device.index is not None else torch.cuda.current_device())
+        self.rank = cfg.group_rank if cfg.group_rank >= 0 else int(os.environ.get("RANK", "0"))
+        self.world = cfg.group_size if cfg.group_size > 0 else int(os.environ.get("WORLD_SIZE", "1"))
+        self.node = cu.GpuMeshNode(self.device.index, n, _gpu_config(cfg), self.rank, self.world, cfg.engine == "thread")
+        self.rep = self.node.replica()
+
+    def start(self, host: str, port: int, init: torch.Tensor | None) -> None:
+        self.node.start(host, port, init.data_ptr() if (init is not None and self.rank == 0) else 0, _stream(self.device),
+                        int(self.cfg.ready_timeout_s * 1000))
+
+    def wait_ready(self, timeout_s: float) -> bool:
+        return True  # start() returns once the common initial state is in place
+
+    def is_master(self) -> bool:
+        return self.rank == 0
+
+    def stats(self) -> dict:
+        names = _native.cuda().status_names()
+        st = self.rep.status()
+        dev = {k: v for k, v in zip(names, st)}
+        return {"backend": "gpu/p2p-mesh", "master": self.rank == 0, "ready": True, "n": self.n, "rank": self.rank,
+                "group_size": self.world, "members_alive": self.node.members_alive(), "dropped": self.node.dropped(),
+                "launches": self.rep.launches(), "device": dev, "edges": {}}
+
+    def inject_sever(self, slot: str) -> None:
+        raise NotImplementedError("mesh groups have no tree slots")
 
 
 class GpuTcpBackend:

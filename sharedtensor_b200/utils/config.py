@@ -21,6 +21,8 @@ class Config:
     # --- where the replica lives and how edges are carried -------------------------------------
     transport: str = "auto"          # auto | gpu | tcp   (auto: gpu for CUDA tensors, tcp for CPU tensors)
     topology: str = "tree"           # tree (reference semantics, dynamic join) | mesh (fixed group over NVSwitch)
+    group_rank: int = -1             # mesh only: this member's rank (default: $RANK)
+    group_size: int = 0              # mesh only: number of members (default: $WORLD_SIZE)
     # --- quantiser ------------------------------------------------------------------------------
     scale_mode: str = "block32"      # GPU edges: block32 .. block4096
     tcp_scale_mode: str = "tensor"   # TCP edges: tensor (reference wire format) | block32 .. block4096
@@ -29,7 +31,8 @@ class Config:
     min_scale_abs: float = 0.0       # tensor mode cut-offs
     min_scale_rel: float = 2.0 ** -22
     # --- GPU engine -----------------------------------------------------------------------------
-    ring_slots: int = 4              # frames in flight per edge direction
+    ring_slots: int = 8              # frames in flight per edge direction
+    frames_per_round: int = 3        # successive 1-bit frames per link and round (refinement in registers)
     engine: str = "thread"           # thread: free-running rounds on a comm stream | manual: caller drives step()
     comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
     rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
@@ -86,6 +89,8 @@ class Config:
             raise ValueError("ring_slots must be in 2..64")
         if self.rel_bits < 1 or self.rel_bits > 60:
             raise ValueError("rel_bits must be in 1..60")
+        if not 1 <= self.frames_per_round <= 3:
+            raise ValueError("frames_per_round must be in 1..3")
         if self.rounds_in_flight < 1:
             raise ValueError("rounds_in_flight must be >= 1")
 

@@ -19,8 +19,12 @@ def main():
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
     init = torch.randn(n, generator=g, device=dev)
-    time.sleep(0.4 * rank)  # join in rank order
-    st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), rejoin_backoff_ms=100)
+    if scenario == "mesh":
+        st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), topology="mesh",
+                                        group_rank=rank, group_size=world)
+    else:
+        time.sleep(0.4 * rank)  # join in rank order
+        st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), rejoin_backoff_ms=100)
     out = torch.empty(n, device=dev)
     st.copyToTensor(out)
     torch.cuda.synchronize()
@@ -70,7 +74,8 @@ def main():
         res["rel_after_loss"] = rel2
     s = st.stats()
     res["edges"] = {k: v["state"] for k, v in s["edges"].items()}
-    res["edge_failures"] = s["edge_failures"]
+    res["edge_failures"] = s.get("edge_failures", 0)
+    res["members_alive"] = s.get("members_alive")
     res["errors"] = s["device"]["errors"]
     res["frames_sent"] = s["device"]["frames_sent"]
     print(json.dumps(res), flush=True)

@@ -25,8 +25,9 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _replica(cu, n, block=32, slots=4, shareable=True, atomic=False, rel_bits=22):
+def _replica(cu, n, block=32, slots=4, shareable=True, atomic=False, rel_bits=22, frames=1):
     cfg = cu.GpuConfig()
+    cfg.frames_per_round = frames
     cfg.block = block
     cfg.ring_slots = slots
     cfg.shareable = shareable
@@ -220,6 +221,43 @@ def test_round_bit_exact_two_replicas(cu, core, n, block):
         assert torch.equal(kb, ob.k[0]), f"B mirror differs in round {it}"
     st = A.status()
     assert st[5] == 0, "no error bits"
+
+
+@pytest.mark.parametrize("frames", [2, 3])
+@pytest.mark.parametrize("block,n", [(32, 3 * 4096 + 77), (256, 4097), (4096, 2 * 4096)])
+def test_round_multi_frame_bit_exact(cu, core, frames, block, n):
+    """Several successive 1-bit frames per round (refinement while the tile is in registers): same stream as
+    encoding that many frames one after the other on the host."""
+    torch.manual_seed(n + frames)
+    A, B = _replica(cu, n, block, 8, frames=frames), _replica(cu, n, block, 8, frames=frames)
+    la, lb = connect_local(A, B)
+    oa, ob = Oracle(core, n, block, 1), Oracle(core, n, block, 1)
+    init = torch.randn(n) * torch.logspace(-2, 1, n)
+    oa.v = init.clone()
+    A.load_values(init.cuda().data_ptr(), _stream())
+    frames_b = []
+    for it in range(12):
+        if it == 5:
+            da, db = torch.randn(n) * 1e-2, torch.randn(n) * 1e-1
+            oa.v += da
+            ob.v += db
+            A.add(da.cuda().data_ptr(), _stream())
+            B.add(db.cuda().data_ptr(), _stream())
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+        for fr in frames_b:
+            oa.decode(0, fr)
+        frames_a = [oa.encode(0) for _ in range(frames)]
+        for fr in frames_a:
+            ob.decode(0, fr)
+        frames_b = [ob.encode(0) for _ in range(frames)]
+        va, ka = _state(cu, A, la)
+        vb, kb = _state(cu, B, lb)
+        assert torch.equal(va, oa.v) and torch.equal(ka, oa.k[0]), f"A differs in round {it}"
+        assert torch.equal(vb, ob.v) and torch.equal(kb, ob.k[0]), f"B differs in round {it}"
+    assert A.status()[5] == 0
 
 
 def test_two_frames_per_round_and_ring_full(cu, core):

@@ -47,6 +47,17 @@ def test_tree_over_peer_memory(free_port, world):
     assert res[1]["edges"]["up"] == "connected"
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_mesh_group(free_port, world):
+    _need(world)
+    res = _run(world, free_port, 5 * 4096 + 321, "mesh")
+    for r in res:
+        assert r["joined_exact"], "every member starts from member 0's values"
+        assert r["rel"] is not None and r["rel"] < 5e-5, r
+        assert r["errors"] == 0
+        assert r["members_alive"] == world
+
+
 def test_rank_leaves_between_steps(free_port):
     _need(3)
     res = _run(3, free_port, 3 * 4096 + 5, "kill_leaf")

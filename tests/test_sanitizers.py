@@ -1,0 +1,20 @@
+"""Race detection: the host core under ThreadSanitizer (five nodes, concurrent adds, an injected edge loss)."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+HERE = Path(__file__).resolve().parent
+
+
+def _have(lib):
+    out = subprocess.run(["g++", f"-print-file-name={lib}"], capture_output=True, text=True).stdout.strip()
+    return "/" in out
+
+
+@pytest.mark.skipif(not _have("libtsan.so"), reason="ThreadSanitizer runtime not installed")
+def test_core_is_race_free_under_tsan():
+    res = subprocess.run([sys.executable, str(HERE / "sanitize_core.py"), "thread"], capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
+    assert "reports=0" in res.stdout
