@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "round.h"
 
@@ -29,9 +30,8 @@ namespace st {
 
 namespace {
 
-constexpr int kGroups = 4;          // independent 128-thread groups per CTA
+constexpr int kMaxGroups = 4;       // independent 128-thread groups per CTA (3 or 4, chosen at launch)
 constexpr int kGroupThreads = 128;  // one thread per 32 consecutive elements of a tile
-constexpr int kThreads = kGroups * kGroupThreads;
 constexpr int kSlots = 3;           // array-tile slots per group
 constexpr int kTileBytes = kTile * 4;
 
@@ -248,6 +248,89 @@ __device__ __forceinline__ float signed_scale(uint32_t scale_bits, uint32_t w, i
   return __uint_as_float(scale_bits | ((w << (31 - bit)) & 0x80000000u));
 }
 
+// ---- per-thread arithmetic on 32 consecutive elements held as eight float4 pieces; piece q holds elements
+// 4*(q^sw) .. +3.  VMASK: bit i set = element i of the 32 exists (all ones except in a tensor's last chunk).
+
+// d += frame: element i moves by +/- 2^(code-127) according to bit i of w
+template <bool FULL>
+__device__ __forceinline__ void apply_frame(float4 (&d)[8], uint32_t w, uint32_t sb, int sw, uint32_t vmask) {
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    const int sh = 4 * (q ^ sw);
+    const uint32_t wq = w >> sh;
+    if (FULL) {
+      d[q].x = __fadd_rn(d[q].x, signed_scale(sb, wq, 0));
+      d[q].y = __fadd_rn(d[q].y, signed_scale(sb, wq, 1));
+      d[q].z = __fadd_rn(d[q].z, signed_scale(sb, wq, 2));
+      d[q].w = __fadd_rn(d[q].w, signed_scale(sb, wq, 3));
+    } else {
+      const uint32_t vq = vmask >> sh;
+      if (vq & 1u) d[q].x = __fadd_rn(d[q].x, signed_scale(sb, wq, 0));
+      if (vq & 2u) d[q].y = __fadd_rn(d[q].y, signed_scale(sb, wq, 1));
+      if (vq & 4u) d[q].z = __fadd_rn(d[q].z, signed_scale(sb, wq, 2));
+      if (vq & 8u) d[q].w = __fadd_rn(d[q].w, signed_scale(sb, wq, 3));
+    }
+  }
+}
+
+// sum of squares of v - k over the 32 elements, in the canonical order (per piece, then a pairwise tree; the XOR
+// swizzle permutes pieces only within each level's pairs, and addition commutes)
+__device__ __forceinline__ float residual_sumsq(const float4 (&v)[8], const float4 (&k)[8]) {
+  float px[8];
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    float4 x;
+    x.x = __fsub_rn(v[q].x, k[q].x);
+    x.y = __fsub_rn(v[q].y, k[q].y);
+    x.z = __fsub_rn(v[q].z, k[q].z);
+    x.w = __fsub_rn(v[q].w, k[q].w);
+    px[q] = sumsq4(x);
+  }
+  return __fadd_rn(__fadd_rn(__fadd_rn(px[0], px[1]), __fadd_rn(px[2], px[3])),
+                   __fadd_rn(__fadd_rn(px[4], px[5]), __fadd_rn(px[6], px[7])));
+}
+
+// bits of the largest |v| among the 32 elements
+__device__ __forceinline__ uint32_t max_abs_bits(const float4 (&v)[8]) {
+  float m = 0.f;
+#pragma unroll
+  for (int q = 0; q < 8; q++) m = fmaxf(fmaxf(fmaxf(m, fabsf(v[q].x)), fabsf(v[q].y)), fmaxf(fabsf(v[q].z), fabsf(v[q].w)));
+  return __float_as_uint(m);
+}
+
+// the sign word of v - k (bit i set = element i is not positive) and, if code != 0, the step of the mirror
+template <bool FULL>
+__device__ __forceinline__ uint32_t sign_word_and_step(const float4 (&v)[8], float4 (&k)[8], uint32_t code, int sw, uint32_t vmask) {
+  const float sp = __uint_as_float(code << 23), sn = __uint_as_float((code << 23) | 0x80000000u);
+  uint32_t word = 0;
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    const int sh = 4 * (q ^ sw);
+    const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
+    const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
+    uint32_t nib = (n0 ? 1u : 0u) | (n1 ? 2u : 0u) | (n2 ? 4u : 0u) | (n3 ? 8u : 0u);
+    if (FULL) {
+      if (code) {
+        k[q].x = __fadd_rn(k[q].x, n0 ? sn : sp);
+        k[q].y = __fadd_rn(k[q].y, n1 ? sn : sp);
+        k[q].z = __fadd_rn(k[q].z, n2 ? sn : sp);
+        k[q].w = __fadd_rn(k[q].w, n3 ? sn : sp);
+      }
+    } else {
+      const uint32_t vq = (vmask >> sh) & 0xfu;
+      nib &= vq;
+      if (code) {
+        if (vq & 1u) k[q].x = __fadd_rn(k[q].x, n0 ? sn : sp);
+        if (vq & 2u) k[q].y = __fadd_rn(k[q].y, n1 ? sn : sp);
+        if (vq & 4u) k[q].z = __fadd_rn(k[q].z, n2 ? sn : sp);
+        if (vq & 8u) k[q].w = __fadd_rn(k[q].w, n3 ? sn : sp);
+      }
+    }
+    word |= nib << sh;
+  }
+  return word;
+}
+
 struct GroupSmem {
   int off_slots;    // [kGroups][kSlots][kTileBytes]
   int off_out;      // [kGroups][2][3 frames][payload_bytes]
@@ -256,7 +339,7 @@ struct GroupSmem {
   int off_flags;    // uint32_t[kGroups][3]  per-step OR flags (changed / nonsilent / wait failed)
   int total;
 };
-__host__ __device__ inline GroupSmem group_layout(int payload_bytes) {
+__host__ __device__ inline GroupSmem group_layout(int payload_bytes, int kGroups) {
   GroupSmem m;
   int off = 0;
   m.off_slots = off;
@@ -277,13 +360,13 @@ __host__ __device__ inline GroupSmem group_layout(int payload_bytes) {
 
 int round_main_smem_bytes(int, int, int payload_bytes, int* stages_out) {
   if (stages_out) *stages_out = kSlots;
-  return group_layout(payload_bytes).total;
+  return group_layout(payload_bytes, kMaxGroups).total;
 }
 
-template <bool ATOMIC>
-__global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_constant__ RoundParams p) {
+template <bool ATOMIC, int kGroups>
+__global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(const __grid_constant__ RoundParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const GroupSmem lay = group_layout(p.payload_bytes);
+  const GroupSmem lay = group_layout(p.payload_bytes, kGroups);
   const int tid = threadIdx.x;
   const int g = tid >> 7;           // group
   const int t = tid & 127;          // thread in group = 32-element chunk of the tile
@@ -351,6 +434,8 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
     auto out_byte = [&](int r) -> uint32_t { return ((r < 4 ? out_lo : out_hi) >> ((r & 3) * 8)) & 0xffu; };
     const int64_t ebase = int64_t(tile) * kTile + int64_t(t) * 32;
     const bool full_chunk = ebase + 32 <= n;
+    const int64_t left = n - ebase;  // elements of this thread's chunk that exist
+    const uint32_t vmask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << int(left)) - 1u));
     const bool rx_any = (in_lo & 0xc0c0c0c0u) != 0 || (in_hi & 0xc0c0c0c0u) != 0;
     bool pend_tile = false;
     uint32_t sent_lo = 0, sent_hi = 0;
@@ -362,8 +447,35 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
       float4* slot4 = reinterpret_cast<float4*>(slots + size_t(s) * kTileBytes) + t * 8;
       const int l = a - 1;
 
-      // frames that concern this step: all in-rings for the values, the link's own in-rings for a mirror
-      // (decoded a second time; they are a few hundred bytes per tile and come from L1/L2)
+      // Frames that concern this step: all in-rings for the values, the link's own in-rings for a mirror
+      // (decoded a second time; they are a few hundred bytes per tile and come from L1/L2).  They are fetched
+      // three at a time so that their load latencies overlap, the first batch before the wait on the slot.
+      int it_r = -1, it_f = 0, it_avail = 0;
+      uint32_t it_ib = 0;
+      auto next_frame = [&]() -> const uint8_t* {
+        if (!rx_any) return nullptr;
+        while (true) {
+          if (it_r >= 0 && it_f < it_avail) {
+            const int slot_no = (int(it_ib & 63u) + it_f) % p.ring_slots;
+            it_f++;
+            return p.in[it_r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
+          }
+          it_r++;
+          if (it_r >= p.n_in) return nullptr;
+          it_ib = in_byte(it_r);
+          it_avail = (a > 0 && p.in[it_r].link != l) ? 0 : int(it_ib >> 6);
+          it_f = 0;
+        }
+      };
+      const uint8_t *fp0 = next_frame(), *fp1 = fp0 ? next_frame() : nullptr, *fp2 = fp1 ? next_frame() : nullptr;
+      uint32_t fw0 = 0, fc0 = 0, fw1 = 0, fc1 = 0, fw2 = 0, fc2 = 0;
+      auto load_batch = [&]() {
+        if (fp0) { fw0 = ld_u32_ca(fp0 + 4 * t); fc0 = ld_u8_ca(fp0 + 4 * kWordsPerTile + (t >> tpb)); }
+        if (fp1) { fw1 = ld_u32_ca(fp1 + 4 * t); fc1 = ld_u8_ca(fp1 + 4 * kWordsPerTile + (t >> tpb)); }
+        if (fp2) { fw2 = ld_u32_ca(fp2 + 4 * t); fc2 = ld_u8_ca(fp2 + 4 * kWordsPerTile + (t >> tpb)); }
+      };
+      load_batch();
+
       // A wait that runs out does not leave the loop by itself (the group's barrier below needs all 128
       // threads): the thread finishes the step on whatever the slot holds and reports the failure through
       // the step's flags, so that the whole group stops together before anything is stored.
@@ -379,45 +491,27 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
       }
 
       bool changed = false;
-      if (rx_any) {
-        for (int r = 0; r < p.n_in; r++) {
-          const uint32_t ib = in_byte(r);
-          const int avail = int(ib >> 6);
-          if (!avail || (a > 0 && p.in[r].link != l)) continue;
-          for (int f = 0; f < avail; f++) {
-            const int slot_no = (int(ib & 63u) + f) % p.ring_slots;
-            const uint8_t* pay = p.in[r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
-            const uint32_t w = ld_u32_ca(pay + 4 * t);
-            const uint32_t code = ld_u8_ca(pay + 4 * kWordsPerTile + (t >> tpb));
-            if (!code) continue;
-            changed = true;
-            const uint32_t sb = code << 23;  // bits of 2^(code-127)
-            if (full_chunk) {
-#pragma unroll
-              for (int q = 0; q < 8; q++) {
-                const uint32_t wq = w >> (4 * (q ^ sw));
-                float4& d = a == 0 ? v[q] : k[q];
-                d.x = __fadd_rn(d.x, signed_scale(sb, wq, 0));
-                d.y = __fadd_rn(d.y, signed_scale(sb, wq, 1));
-                d.z = __fadd_rn(d.z, signed_scale(sb, wq, 2));
-                d.w = __fadd_rn(d.w, signed_scale(sb, wq, 3));
-              }
-            } else {
-#pragma unroll
-              for (int q = 0; q < 8; q++) {
-                const int m = q ^ sw;
-                const uint32_t wq = w >> (4 * m);
-                const int64_t e = ebase + 4 * m;
-                float4& d = a == 0 ? v[q] : k[q];
-                if (e + 0 < n) d.x = __fadd_rn(d.x, signed_scale(sb, wq, 0));
-                if (e + 1 < n) d.y = __fadd_rn(d.y, signed_scale(sb, wq, 1));
-                if (e + 2 < n) d.z = __fadd_rn(d.z, signed_scale(sb, wq, 2));
-                if (e + 3 < n) d.w = __fadd_rn(d.w, signed_scale(sb, wq, 3));
-              }
-            }
-            if (a == 0 && t == 0) n_rx++;
-          }
+      auto apply_one = [&](uint32_t w, uint32_t code) {
+        if (a == 0 && t == 0) n_rx++;
+        if (!code) return;
+        changed = true;
+        const uint32_t sb = code << 23;  // bits of 2^(code-127)
+        if (a == 0) {
+          if (full_chunk) apply_frame<true>(v, w, sb, sw, vmask); else apply_frame<false>(v, w, sb, sw, vmask);
+        } else {
+          if (full_chunk) apply_frame<true>(k, w, sb, sw, vmask); else apply_frame<false>(k, w, sb, sw, vmask);
         }
+      };
+      while (fp0) {
+        const uint32_t w0 = fw0, c0 = fc0, w1 = fw1, c1 = fc1, w2 = fw2, c2 = fc2;
+        const bool h1 = fp1 != nullptr, h2 = fp2 != nullptr;
+        fp0 = h2 ? next_frame() : nullptr;   // the next batch goes out before this one is applied
+        fp1 = fp0 ? next_frame() : nullptr;
+        fp2 = fp1 ? next_frame() : nullptr;
+        load_batch();
+        apply_one(w0, c0);
+        if (h1) apply_one(w1, c1);
+        if (h2) apply_one(w2, c2);
       }
 
       int n_frames = 0;             // frames this step may push: room in every out-ring of the link, at most frames_per_round
@@ -433,30 +527,13 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
           room = min(room, int(out_byte(r) >> 6));
         }
         n_frames = any_ring ? min(room, p.frames_per_round) : 0;
-        uint32_t vmax = 0;
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-          vmax = max(max(vmax, __float_as_uint(v[q].x) & 0x7fffffffu), __float_as_uint(v[q].y) & 0x7fffffffu);
-          vmax = max(max(vmax, __float_as_uint(v[q].z) & 0x7fffffffu), __float_as_uint(v[q].w) & 0x7fffffffu);
-        }
+        uint32_t vmax = max_abs_bits(v);
         for (int sft = 0; sft < tpb && sft < 5; sft++) vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1 << sft));
         int lbe = lb;
         if (tail_block >= 0 && (ebase >> lb) == tail_block) lbe = tail_lb;
         const int passes = n_frames > 0 ? n_frames : 1;  // without ring space one pass still tells whether work is left
         for (int f = 0; f < passes; f++) {
-          float px[8];
-#pragma unroll
-          for (int q = 0; q < 8; q++) {
-            float4 x;
-            x.x = __fsub_rn(v[q].x, k[q].x);
-            x.y = __fsub_rn(v[q].y, k[q].y);
-            x.z = __fsub_rn(v[q].z, k[q].z);
-            x.w = __fsub_rn(v[q].w, k[q].w);
-            px[q] = sumsq4(x);
-          }
-          // pairwise tree over the eight pieces; the XOR swizzle permutes pieces only within each level's pairs
-          float sx = __fadd_rn(__fadd_rn(__fadd_rn(px[0], px[1]), __fadd_rn(px[2], px[3])),
-                               __fadd_rn(__fadd_rn(px[4], px[5]), __fadd_rn(px[6], px[7])));
+          float sx = residual_sumsq(v, k);
           if (f == 0) {
             if (l == 0) acc_res0 += sx; else if (l == 1) acc_res1 += sx; else acc_res2 += sx;
           }
@@ -484,30 +561,8 @@ __global__ void __launch_bounds__(kThreads, 1) round_main_kernel(const __grid_co
           const int code = block_code_dev(sx, vm, lbe, p.min_exp, p.rel_bits);
           if (code) nonsilent_mask |= 1u << f;
           if (n_frames > 0) {
-            const uint32_t sb = uint32_t(code) << 23;
-            uint32_t word = 0;
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-              const int m = q ^ sw;
-              const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
-              const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
-              bool v0 = true, v1 = true, v2 = true, v3 = true;
-              if (!full_chunk) {
-                const int64_t e = ebase + 4 * m;
-                v0 = e + 0 < n;
-                v1 = e + 1 < n;
-                v2 = e + 2 < n;
-                v3 = e + 3 < n;
-              }
-              const uint32_t nib = uint32_t(n0 && v0) | (uint32_t(n1 && v1) << 1) | (uint32_t(n2 && v2) << 2) | (uint32_t(n3 && v3) << 3);
-              word |= nib << (4 * m);
-              if (code) {
-                if (v0) k[q].x = __fadd_rn(k[q].x, __uint_as_float(sb | (n0 ? 0x80000000u : 0u)));
-                if (v1) k[q].y = __fadd_rn(k[q].y, __uint_as_float(sb | (n1 ? 0x80000000u : 0u)));
-                if (v2) k[q].z = __fadd_rn(k[q].z, __uint_as_float(sb | (n2 ? 0x80000000u : 0u)));
-                if (v3) k[q].w = __fadd_rn(k[q].w, __uint_as_float(sb | (n3 ? 0x80000000u : 0u)));
-              }
-            }
+            const uint32_t word = full_chunk ? sign_word_and_step<true>(v, k, uint32_t(code), sw, vmask)
+                                             : sign_word_and_step<false>(v, k, uint32_t(code), sw, vmask);
             if (code) changed = true;
             uint8_t* ob = outbuf + size_t((c & 1) * kMaxFrames + f) * pb_pad;
             reinterpret_cast<uint32_t*>(ob)[t] = word;
@@ -658,23 +713,30 @@ int launch_round_publish(const RoundParams& p, void* stream) {
   return int(cudaGetLastError());
 }
 
-template <bool ATOMIC>
+template <bool ATOMIC, int G>
 static int launch_main_t(const RoundParams& p, int ctas, cudaStream_t stream) {
-  const int smem = group_layout(p.payload_bytes).total;
+  const int smem = group_layout(p.payload_bytes, G).total;
   static int configured_for = -1;  // per instantiation
   if (configured_for < smem) {
-    cudaError_t e = cudaFuncSetAttribute(round_main_kernel<ATOMIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(round_main_kernel<ATOMIC, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
     configured_for = smem;
   }
-  round_main_kernel<ATOMIC><<<ctas, kThreads, smem, stream>>>(p);
+  round_main_kernel<ATOMIC, G><<<ctas, G * kGroupThreads, smem, stream>>>(p);
   return int(cudaGetLastError());
 }
 
 int launch_round_main(const RoundParams& p, int ctas, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (p.n_links < 1 || p.n_links > kMaxLinks) return int(cudaErrorInvalidValue);
-  return p.atomic_values ? launch_main_t<true>(p, ctas, stream) : launch_main_t<false>(p, ctas, stream);
+  // 4 groups of 128 threads (128 registers each) or 3 groups (168 registers each, no spills)
+  static const int groups = [] {
+    const char* e = getenv("SHAREDTENSOR_ROUND_GROUPS");
+    int g = e ? atoi(e) : 4;
+    return g == 3 ? 3 : 4;
+  }();
+  if (groups == 3) return p.atomic_values ? launch_main_t<true, 3>(p, ctas, stream) : launch_main_t<false, 3>(p, ctas, stream);
+  return p.atomic_values ? launch_main_t<true, 4>(p, ctas, stream) : launch_main_t<false, 4>(p, ctas, stream);
 }
 
 }  // namespace st

@@ -260,8 +260,8 @@ def test_round_multi_frame_bit_exact(cu, core, frames, block, n):
     assert A.status()[5] == 0
 
 
-def test_two_frames_per_round_and_ring_full(cu, core):
-    """The sender runs ahead: the receiver takes two frames per round in order; once the ring is full the
+def test_several_frames_per_round_and_ring_full(cu, core):
+    """The sender runs ahead: the receiver takes up to three frames per round in order; once the ring is full the
     sender skips (nothing is lost, the residual simply stays) and counts it."""
     n, block, slots = 2 * 4096 + 5, 32, 4
     torch.manual_seed(7)
@@ -283,12 +283,14 @@ def test_two_frames_per_round_and_ring_full(cu, core):
     names = cu.status_names()
     assert st[names.index("blocked_no_credit")] == 3 * A.tiles()
     assert st[names.index("frames_sent")] == slots * A.tiles()
-    # B drains two frames per round
-    for r in range(2):
+    # B drains up to three frames per round, in order
+    taken = 0
+    for take in (3, 1):
         B.round(True, False)  # receiver-only rounds
         B.sync()
-        ob.decode(0, frames[2 * r])
-        ob.decode(0, frames[2 * r + 1])
+        for fr in frames[taken:taken + take]:
+            ob.decode(0, fr)
+        taken += take
         vb, kb = _state(cu, B, lb)
         assert torch.equal(vb, ob.v) and torch.equal(kb, ob.k[0])
     # credits are back: A can send again
