@@ -46,9 +46,12 @@ void bind_core(py::module_& m) {
   m.def("ref_scale_of", [](uintptr_t r, size_t n) { return ref_scale_of(ptr<float>(r), n); });
   m.def("encode_residual_ref",
         [](uintptr_t r, size_t n, uintptr_t bits) { return encode_residual_ref(ptr<float>(r), n, ptr<uint8_t>(bits)); });
-  m.def("encode_tensor", [](uintptr_t v, uintptr_t k, size_t n, uintptr_t bits, float min_scale) {
-    return encode_tensor(ptr<float>(v), ptr<float>(k), n, ptr<uint8_t>(bits), min_scale);
-  });
+  m.def(
+      "encode_tensor",
+      [](uintptr_t v, uintptr_t k, size_t n, uintptr_t bits, float min_scale, int rule) {
+        return encode_tensor(ptr<float>(v), ptr<float>(k), n, ptr<uint8_t>(bits), min_scale, rule);
+      },
+      py::arg("v"), py::arg("k"), py::arg("n"), py::arg("bits"), py::arg("min_scale"), py::arg("rule") = 1);
   m.def("decode_tensor_add", [](uintptr_t bits, float scale, size_t n, uintptr_t dst, uintptr_t dst2) {
     decode_tensor_add(ptr<uint8_t>(bits), scale, n, ptr<float>(dst), dst2 ? ptr<float>(dst2) : nullptr);
   });
@@ -94,6 +97,7 @@ void bind_core(py::module_& m) {
   py::class_<NodeConfig>(m, "NodeConfig")
       .def(py::init<>())
       .def_readwrite("tcp_block", &NodeConfig::tcp_block)
+      .def_readwrite("tcp_rule", &NodeConfig::tcp_rule)
       .def_readwrite("min_scale_abs", &NodeConfig::min_scale_abs)
       .def_readwrite("min_scale_rel", &NodeConfig::min_scale_rel)
       .def_readwrite("max_frames_per_s", &NodeConfig::max_frames_per_s)

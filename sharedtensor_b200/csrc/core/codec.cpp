@@ -41,14 +41,24 @@ float encode_residual_ref(float* r, size_t n, uint8_t* bits) {
   return scale;
 }
 
-float encode_tensor(const float* v, float* k, size_t n, uint8_t* bits, float min_scale) {
-  float acc = 0.0f;
-  for (size_t i = 0; i < n; i++) {
-    float x = v[i] - k[i];
-    acc += x * x;
+float encode_tensor(const float* v, float* k, size_t n, uint8_t* bits, float min_scale, int rule) {
+  float scale;
+  if (rule == 0) {  // the reference's rule: power-of-two floor of the RMS
+    float acc = 0.0f;
+    for (size_t i = 0; i < n; i++) {
+      float x = v[i] - k[i];
+      acc += x * x;
+    }
+    float mean = acc / float(n);
+    scale = pow2_floor(float(std::sqrt(double(mean))));
+  } else {          // bisection: power-of-two floor of two thirds of the largest residual
+    float xmax = 0.0f;
+    for (size_t i = 0; i < n; i++) {
+      float ax = std::fabs(v[i] - k[i]);
+      if (ax > xmax) xmax = ax;
+    }
+    scale = pow2_floor(xmax * 0.6666667f);
   }
-  float mean = acc / float(n);
-  float scale = pow2_floor(float(std::sqrt(double(mean))));
   if (scale < min_scale) scale = 0.0f;
   std::memset(bits, 0, sign_bytes(n));
   if (scale == 0.0f) {
@@ -84,40 +94,22 @@ void decode_tensor_add(const uint8_t* bits, float scale, size_t n, float* dst, f
   }
 }
 
-float group32_sumsq(const float* x) {
-  float p[8];
-  for (int q = 0; q < 8; q++) {
-    const float* a = x + 4 * q;
-    p[q] = (a[0] * a[0] + a[1] * a[1]) + (a[2] * a[2] + a[3] * a[3]);
-  }
-  // butterfly order of a xor-shuffle reduction over 8 lanes: offsets 1, 2, 4
-  float l1[4] = {p[0] + p[1], p[2] + p[3], p[4] + p[5], p[6] + p[7]};
-  float l2[2] = {l1[0] + l1[1], l1[2] + l1[3]};
-  return l2[0] + l2[1];
-}
-
-static float pairwise_tree(const float* s, int m) {
-  // m is a power of two <= 128; adjacent pairs, level by level
-  float buf[128];
-  for (int i = 0; i < m; i++) buf[i] = s[i];
-  for (int w = m; w > 1; w >>= 1)
-    for (int i = 0; i < w / 2; i++) buf[i] = buf[2 * i] + buf[2 * i + 1];
-  return buf[0];
-}
-
-static int ilog2(int b) {
-  int l = 0;
-  while ((1 << l) < b) l++;
-  return l;
-}
-
-// Decides the exponent code of one block from its residual energy and the largest magnitude among its
-// values.  The relative cut-off is tied to the largest element, not to the RMS: a step of at least
-// 2^(emax - rel_bits) with rel_bits <= 22 is a whole number of ulps of every element of the block, so
-// stepping the mirror is exact and the stream cannot get stuck re-sending a step that rounds away.
-static inline int block_code(float sx, uint32_t vmax_bits, int log2_block, const BlockGate& gate) {
-  if ((f32_bits(sx) >> 23) == 0) return kSilent;  // zero or denormal energy
-  int kx = rms_exponent(sx, log2_block);
+// Decides the exponent code of one block from its largest residual magnitude and the largest magnitude among
+// its values.
+//
+// Step rule: 2^floor(log2(2/3 * max|x|)), i.e. between a third and two thirds of the largest residual.  Every
+// element moves by that step towards zero or past it, so after the pass no residual exceeds max(step, max - step)
+// <= 2/3 max, and from the second pass on the bound halves with every pass (bisection).  The reference takes
+// the power-of-two floor of the RMS instead (src/sharedtensor.c:156-159), which never overshoots but removes
+// only ~16 % of the error per frame and leaves outliers for hundreds of frames.
+//
+// Cut-off: a step below 2^(emax - rel_bits), emax the exponent of the block's largest |value|, is not sent.
+// With rel_bits <= 22 every step is a whole number of ulps of every element of the block, so stepping the
+// mirror is exact and the stream cannot get stuck re-sending a step that rounds away.
+static inline int block_code(float xmax, uint32_t vmax_bits, const BlockGate& gate) {
+  float scaled = xmax * 0.6666667f;
+  if ((f32_bits(scaled) >> 23) == 0) return kSilent;  // zero or denormal
+  int kx = floor_log2_f32(scaled);
   if (kx < gate.min_exp) return kSilent;
   if ((vmax_bits >> 23) != 0) {
     int emax = int(vmax_bits >> 23) - 127;
@@ -131,36 +123,27 @@ static inline int block_code(float sx, uint32_t vmax_bits, int log2_block, const
 double encode_block(const float* v, float* k, size_t n, int block, const BlockGate& gate,
                     uint32_t* words, uint8_t* scales) {
   const int m = block / 32;
-  const int lb = ilog2(block);
   const size_t nb = block_scales(n, block);
-  double total = 0.0;
-  std::vector<float> x(static_cast<size_t>(block), 0.0f), vv(static_cast<size_t>(block), 0.0f);
-  float sx32[128];
+  double worst = 0.0;
+  std::vector<float> x(static_cast<size_t>(block), 0.0f);
   for (size_t b = 0; b < nb; b++) {
     size_t base = b * size_t(block);
+    float xmax = 0.0f;
+    uint32_t vmax = 0;
     for (int j = 0; j < block; j++) {
       size_t i = base + size_t(j);
       if (i < n) {
-        vv[j] = v[i];
         x[j] = v[i] - k[i];
+        float ax = std::fabs(x[j]);
+        if (ax > xmax) xmax = ax;
+        uint32_t a = f32_bits(v[i]) & 0x7fffffffu;
+        if (a > vmax) vmax = a;
       } else {
-        vv[j] = 0.0f;
         x[j] = 0.0f;
       }
     }
-    for (int g = 0; g < m; g++) sx32[g] = group32_sumsq(&x[size_t(g) * 32]);
-    float sx = pairwise_tree(sx32, m);
-    uint32_t vmax = 0;
-    for (int j = 0; j < block; j++) {
-      uint32_t a = f32_bits(vv[j]) & 0x7fffffffu;
-      if (a > vmax) vmax = a;
-    }
-    total += double(sx);
-    // The last block may be partly padding: its RMS is taken over the next power of two that
-    // holds its valid elements, so that the zeros do not dilute the scale.
-    int lb_eff = lb;
-    if (base + size_t(block) > n) lb_eff = ilog2(int(n - base));
-    int code = block_code(sx, vmax, lb_eff, gate);
+    if (double(xmax) > worst) worst = double(xmax);
+    int code = block_code(xmax, vmax, gate);
     scales[b] = uint8_t(code);
     float scale = code ? exp2i(code - 127) : 0.0f;
     for (int g = 0; g < m; g++) {
@@ -177,7 +160,7 @@ double encode_block(const float* v, float* k, size_t n, int block, const BlockGa
       words[wbase / 32] = w;
     }
   }
-  return total;
+  return worst;
 }
 
 void decode_block_add(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst,

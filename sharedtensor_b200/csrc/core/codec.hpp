@@ -50,12 +50,6 @@ inline float bits_f32(uint32_t u) {
 // denormals returns -127 (callers treat anything that small as silent).
 inline int floor_log2_f32(float x) { return int((f32_bits(x) >> 23) & 0xff) - 127; }
 
-// Exponent k of the power-of-two floor of sqrt(sumsq / B): floor((floor_log2(sumsq) - log2 B) / 2).
-inline int rms_exponent(float sumsq, int log2_block) {
-  int e = floor_log2_f32(sumsq) - log2_block;
-  return e >> 1;  // arithmetic shift = floor division by two
-}
-
 // 2^k as fp32 for k in [-126, 127].
 inline float exp2i(int k) { return bits_f32(uint32_t(k + 127) << 23); }
 
@@ -80,8 +74,10 @@ float encode_residual_ref(float* r, size_t n, uint8_t* bits);
 
 // Mirror-form encoder: quantises v - k with one scale for the whole tensor, adds the step to k.
 // `min_scale`: if the chosen scale is below it the frame is a no-op (scale 0, k untouched).
+// `rule`: 0 = the reference's scale (power-of-two floor of the RMS), 1 = bisection (power-of-two floor of 2/3 of
+// the largest residual; the error bound halves with every frame).
 // Returns the scale written on the wire.
-float encode_tensor(const float* v, float* k, size_t n, uint8_t* bits, float min_scale);
+float encode_tensor(const float* v, float* k, size_t n, uint8_t* bits, float min_scale, int rule = 1);
 
 // Decoder: dst[i] += (bit ? -scale : +scale).  `dst2` may be null; if not it gets the same step.
 void decode_tensor_add(const uint8_t* bits, float scale, size_t n, float* dst, float* dst2);
@@ -93,13 +89,9 @@ void decode_tensor_add(const uint8_t* bits, float scale, size_t n, float* dst, f
 size_t block_words(size_t n);              // ceil(n/32)
 size_t block_scales(size_t n, int block);  // ceil(n/block)
 
-// Sum of squares of one 32-element group in the canonical order used by the kernels:
-// per 4 consecutive elements ((x0^2 + x1^2) + (x2^2 + x3^2)), then a pairwise tree over the 8 partial sums.
-float group32_sumsq(const float* x);
-
 // Encodes n elements (n need not be a multiple of anything; missing elements count as zero residual
 // and their bits are 1).  v: values, k: mirror (updated), words/scales: outputs.
-// Returns the sum of squared residual (before the update), a cheap convergence statistic.
+// Returns the largest |residual| (before the update), a cheap convergence statistic.
 double encode_block(const float* v, float* k, size_t n, int block, const BlockGate& gate,
                     uint32_t* words, uint8_t* scales);
 

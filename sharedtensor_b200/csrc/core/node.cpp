@@ -174,15 +174,19 @@ void CpuNode::tx_loop(Edge* e) {
       my_version = e->dirty;
       double resid = 0.0;
       if (B == 0) {
-        // min scale relative to the replica's own magnitude
+        // smallest step worth sending, relative to the replica's largest element: a step of at least
+        // 2^-22 of it is a whole number of ulps of every element, so it can never round away
         float min_scale = cfg_.min_scale_abs;
         if (cfg_.min_scale_rel > 0.0f) {
-          double acc = 0.0;
-          for (size_t i = 0; i < n; i++) acc += double(values_[i]) * double(values_[i]);
-          float rel = float(std::sqrt(acc / double(n))) * cfg_.min_scale_rel;
+          float vmax = 0.0f;
+          for (size_t i = 0; i < n; i++) {
+            float a = std::fabs(values_[i]);
+            if (a > vmax) vmax = a;
+          }
+          float rel = vmax * cfg_.min_scale_rel;
           if (rel > min_scale) min_scale = rel;
         }
-        float scale = encode_tensor(values_.data(), e->mirror.data(), n, frame.data() + 4, min_scale);
+        float scale = encode_tensor(values_.data(), e->mirror.data(), n, frame.data() + 4, min_scale, cfg_.tcp_rule);
         std::memcpy(frame.data(), &scale, 4);
         noop = scale == 0.0f;
         e->st.last_scale_sent = scale;
@@ -203,7 +207,7 @@ void CpuNode::tx_loop(Edge* e) {
           if (scales[i] > maxc) maxc = scales[i];
         }
         e->st.last_scale_sent = maxc ? exp2i(maxc - 127) : 0.0f;
-        resid = std::sqrt(ss / double(n));
+        resid = ss;  // largest outstanding |residual|
       }
       e->st.residual_rms = resid;
       e->idle = noop;

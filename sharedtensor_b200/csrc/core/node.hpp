@@ -26,9 +26,10 @@ namespace st {
 struct NodeConfig {
   // wire format on TCP edges: 0 = tensor scale (what the reference speaks), else block size (32..4096)
   int tcp_block = 0;
+  int tcp_rule = 1;               // tensor mode scale: 0 = the reference's RMS rule, 1 = bisection (see codec.hpp)
   BlockGate gate;                 // block mode cut-offs
   float min_scale_abs = 0.0f;     // tensor mode: frames with a smaller scale become no-ops
-  float min_scale_rel = 2.3841858e-07f;  // ... or smaller than this times rms(values)   (2^-22)
+  float min_scale_rel = 2.3841858e-07f;  // ... or smaller than this times max|values|   (2^-22)
   double max_frames_per_s = 0.0;  // per-edge rate cap, 0 = as fast as TCP takes them
   int idle_keepalive_ms = 0;      // send a scale-0 frame this often while idle (0 = never)
   int listen_backlog = 5;

@@ -33,7 +33,7 @@ PYBIND11_MODULE(_cuda, m) {
   m.attr("STATUS_WORDS") = int(kStWords);
   m.def("status_names", [] {
     return std::vector<std::string>{"rounds", "tiles_processed", "frames_sent", "frames_recv", "blocked_no_credit", "errors",
-                                    "last_work_count", "residual_sumsq0", "residual_sumsq1", "residual_sumsq2", "pending_tiles",
+                                    "last_work_count", "residual_max0", "residual_max1", "residual_max2", "pending_tiles",
                                     "wait_timeouts"};
   });
   m.def("vmm_available", &vmm_available);

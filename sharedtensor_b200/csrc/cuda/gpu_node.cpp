@@ -176,12 +176,13 @@ class GpuNode {
     d["edges"] = edges;
     py::dict dev;
     static const char* snames[] = {"rounds", "tiles_processed", "frames_sent", "frames_recv", "blocked_no_credit", "errors",
-                                   "last_work_count", "residual_sumsq0", "residual_sumsq1", "residual_sumsq2", "pending_tiles",
+                                   "last_work_count", "residual_max0", "residual_max1", "residual_max2", "pending_tiles",
                                    "wait_timeouts"};
     for (int i = 0; i < 12; i++) {
       if (i >= 7 && i <= 9) {
-        double v;
-        std::memcpy(&v, &st[i], 8);
+        uint32_t bits = uint32_t(st[i]);
+        float v;
+        std::memcpy(&v, &bits, 4);
         dev[snames[i]] = v;
       } else {
         dev[snames[i]] = st[i];

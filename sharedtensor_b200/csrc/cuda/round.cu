@@ -17,8 +17,8 @@
 // Nothing in here waits for another GPU.  The only waits are on this CTA's own TMA copies, and they are
 // bounded: on a timeout the group records an error in the status block and leaves.
 //
-// Arithmetic is written with explicit round-to-nearest multiplies and adds in the order documented in
-// ../core/codec.hpp, so that words, scales and mirrors are bit-identical to the host codec.
+// Arithmetic is written with explicit round-to-nearest operations; block statistics are maxima (order does not
+// matter), so words, scales and mirrors are bit-identical to the host codec (../core/codec.cpp).
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -93,9 +93,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 
 __device__ __forceinline__ int floor_log2_dev(float x) { return int((__float_as_uint(x) >> 23) & 0xff) - 127; }
 
-__device__ __forceinline__ int block_code_dev(float sx, uint32_t vmax_bits, int lb, int min_exp, int rel_bits) {
-  if ((__float_as_uint(sx) >> 23) == 0) return 0;
-  int kx = (floor_log2_dev(sx) - lb) >> 1;
+// exponent code of a block from its largest |residual| and the bits of its largest |value| (see block_code in
+// ../core/codec.cpp: step = 2^floor(log2(2/3 max|x|)), silent below 2^(emax - rel_bits))
+__device__ __forceinline__ int block_code_dev(float xmax, uint32_t vmax_bits, int min_exp, int rel_bits) {
+  const float scaled = __fmul_rn(xmax, 0.6666667f);
+  if ((__float_as_uint(scaled) >> 23) == 0) return 0;
+  int kx = floor_log2_dev(scaled);
   if (kx < min_exp) return 0;
   if ((vmax_bits >> 23) != 0) {
     int emax = int(vmax_bits >> 23) - 127;
@@ -104,16 +107,6 @@ __device__ __forceinline__ int block_code_dev(float sx, uint32_t vmax_bits, int 
   if (kx < -126) return 0;
   if (kx > 127) kx = 127;
   return kx + 127;
-}
-
-__device__ __forceinline__ float sumsq4(const float4& a) {
-  return __fadd_rn(__fadd_rn(__fmul_rn(a.x, a.x), __fmul_rn(a.y, a.y)), __fadd_rn(__fmul_rn(a.z, a.z), __fmul_rn(a.w, a.w)));
-}
-
-__device__ __forceinline__ int ceil_log2_dev(int64_t v) {
-  int l = 0;
-  while ((int64_t(1) << l) < v) l++;
-  return l;
 }
 
 }  // namespace
@@ -166,9 +159,9 @@ __global__ void __launch_bounds__(256) round_begin_kernel(const __grid_constant_
   if (tile == 0) {
     p.work_count[par ^ 1] = 0;  // the next round appends to the other counter
     p.status[kStPendingTiles] = 0;
-    p.status[kStResidualSumsq0] = 0;
-    p.status[kStResidualSumsq1] = 0;
-    p.status[kStResidualSumsq2] = 0;
+    p.status[kStResidualMax0] = 0;
+    p.status[kStResidualMax1] = 0;
+    p.status[kStResidualMax2] = 0;
   }
   if (tile >= p.n_tiles) return;
   uint4 cur = make_uint4(0u, 0u, 0u, 0u);
@@ -273,21 +266,15 @@ __device__ __forceinline__ void apply_frame(float4 (&d)[8], uint32_t w, uint32_t
   }
 }
 
-// sum of squares of v - k over the 32 elements, in the canonical order (per piece, then a pairwise tree; the XOR
-// swizzle permutes pieces only within each level's pairs, and addition commutes)
-__device__ __forceinline__ float residual_sumsq(const float4 (&v)[8], const float4 (&k)[8]) {
-  float px[8];
+// largest |v - k| among the 32 elements
+__device__ __forceinline__ float residual_maxabs(const float4 (&v)[8], const float4 (&k)[8]) {
+  float m = 0.f;
 #pragma unroll
   for (int q = 0; q < 8; q++) {
-    float4 x;
-    x.x = __fsub_rn(v[q].x, k[q].x);
-    x.y = __fsub_rn(v[q].y, k[q].y);
-    x.z = __fsub_rn(v[q].z, k[q].z);
-    x.w = __fsub_rn(v[q].w, k[q].w);
-    px[q] = sumsq4(x);
+    m = fmaxf(fmaxf(m, fabsf(__fsub_rn(v[q].x, k[q].x))), fabsf(__fsub_rn(v[q].y, k[q].y)));
+    m = fmaxf(fmaxf(m, fabsf(__fsub_rn(v[q].z, k[q].z))), fabsf(__fsub_rn(v[q].w, k[q].w)));
   }
-  return __fadd_rn(__fadd_rn(__fadd_rn(px[0], px[1]), __fadd_rn(px[2], px[3])),
-                   __fadd_rn(__fadd_rn(px[4], px[5]), __fadd_rn(px[6], px[7])));
+  return m;
 }
 
 // bits of the largest |v| among the 32 elements
@@ -391,8 +378,6 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
   const int first = int(blockIdx.x) * kGroups + g;
   const int my_count = count > first ? (count - first + stride - 1) / stride : 0;
   const int total_steps = my_count * arrays;
-  const int64_t tail_block = (n & ((int64_t(1) << lb) - 1)) ? (n >> lb) : int64_t(-1);
-  const int tail_lb = tail_block >= 0 ? ceil_log2_dev(n - (tail_block << lb)) : lb;
   const int tpb = lb - 5;           // log2(threads per block)
 
   if (t == 0) {
@@ -420,7 +405,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
     for (int c = 0; c < kSlots - 1 && c < total_steps; c++) issue_load(c, c / arrays == 0 ? tile_cur : tile_next);
   }
 
-  float acc_res0 = 0.f, acc_res1 = 0.f, acc_res2 = 0.f;
+  float res_max0 = 0.f, res_max1 = 0.f, res_max2 = 0.f;  // largest outstanding |residual| per link seen by this thread
   uint32_t n_rx = 0, n_tx = 0, n_blocked = 0, n_pending = 0;
   bool aborted = false;
 
@@ -529,20 +514,18 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
         n_frames = any_ring ? min(room, p.frames_per_round) : 0;
         uint32_t vmax = max_abs_bits(v);
         for (int sft = 0; sft < tpb && sft < 5; sft++) vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1 << sft));
-        int lbe = lb;
-        if (tail_block >= 0 && (ebase >> lb) == tail_block) lbe = tail_lb;
         const int passes = n_frames > 0 ? n_frames : 1;  // without ring space one pass still tells whether work is left
         for (int f = 0; f < passes; f++) {
-          float sx = residual_sumsq(v, k);
+          float xm = residual_maxabs(v, k);
           if (f == 0) {
-            if (l == 0) acc_res0 += sx; else if (l == 1) acc_res1 += sx; else acc_res2 += sx;
+            if (l == 0) res_max0 = fmaxf(res_max0, xm); else if (l == 1) res_max1 = fmaxf(res_max1, xm); else res_max2 = fmaxf(res_max2, xm);
           }
-          // blocks larger than 32 elements: butterfly over lanes (up to 1024), then over the group's warps
-          for (int sft = 0; sft < tpb && sft < 5; sft++) sx = __fadd_rn(sx, __shfl_xor_sync(0xffffffffu, sx, 1 << sft));
+          // blocks larger than 32 elements: maximum over lanes (up to 1024), then over the group's warps
+          for (int sft = 0; sft < tpb && sft < 5; sft++) xm = fmaxf(xm, __shfl_xor_sync(0xffffffffu, xm, 1 << sft));
           uint32_t vm = vmax;
           if (tpb > 5) {
             if (lane == 0) {
-              s_red[wig] = sx;
+              s_red[wig] = xm;
               s_red[4 + wig] = __uint_as_float(vmax);
             }
             group_bar(g);
@@ -550,15 +533,15 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
             const uint32_t b0 = __float_as_uint(s_red[4]), b1 = __float_as_uint(s_red[5]);
             const uint32_t b2 = __float_as_uint(s_red[6]), b3 = __float_as_uint(s_red[7]);
             if (tpb == 6) {  // 2048: warps {0,1} and {2,3}
-              sx = wig < 2 ? __fadd_rn(a0, a1) : __fadd_rn(a2, a3);
+              xm = wig < 2 ? fmaxf(a0, a1) : fmaxf(a2, a3);
               vm = wig < 2 ? max(b0, b1) : max(b2, b3);
             } else {         // 4096: the whole tile
-              sx = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
+              xm = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
               vm = max(max(b0, b1), max(b2, b3));
             }
             group_bar(g);  // s_red is reused by the next pass
           }
-          const int code = block_code_dev(sx, vm, lbe, p.min_exp, p.rel_bits);
+          const int code = block_code_dev(xm, vm, p.min_exp, p.rel_bits);
           if (code) nonsilent_mask |= 1u << f;
           if (n_frames > 0) {
             const uint32_t word = full_chunk ? sign_word_and_step<true>(v, k, uint32_t(code), sw, vmask)
@@ -674,16 +657,16 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
 
   // ---------------- statistics: one atomic per group and counter
   {
-    float a0 = acc_res0, a1 = acc_res1, a2 = acc_res2;
+    float a0 = res_max0, a1 = res_max1, a2 = res_max2;
     for (int o = 16; o > 0; o >>= 1) {
-      a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-      a1 += __shfl_xor_sync(0xffffffffu, a1, o);
-      a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+      a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, o));
+      a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, o));
+      a2 = fmaxf(a2, __shfl_xor_sync(0xffffffffu, a2, o));
     }
-    if (lane == 0) {
-      if (a0 != 0.f) atomicAdd(reinterpret_cast<double*>(p.status + kStResidualSumsq0), double(a0));
-      if (a1 != 0.f) atomicAdd(reinterpret_cast<double*>(p.status + kStResidualSumsq1), double(a1));
-      if (a2 != 0.f) atomicAdd(reinterpret_cast<double*>(p.status + kStResidualSumsq2), double(a2));
+    if (lane == 0) {  // non-negative floats order like their bit patterns
+      if (a0 != 0.f) atomicMax(reinterpret_cast<unsigned long long*>(p.status + kStResidualMax0), (unsigned long long)__float_as_uint(a0));
+      if (a1 != 0.f) atomicMax(reinterpret_cast<unsigned long long*>(p.status + kStResidualMax1), (unsigned long long)__float_as_uint(a1));
+      if (a2 != 0.f) atomicMax(reinterpret_cast<unsigned long long*>(p.status + kStResidualMax2), (unsigned long long)__float_as_uint(a2));
     }
   }
   if (t == 0) {

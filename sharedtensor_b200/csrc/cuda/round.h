@@ -82,9 +82,9 @@ enum StatusWord : int {
   kStBlockedNoCredit, // tile-links that had something to send but no ring space
   kStErrors,          // bit mask, see kErr*
   kStLastWorkCount,
-  kStResidualSumsq0,  // double bits, per link: residual energy seen by the last round (3 words)
-  kStResidualSumsq1,
-  kStResidualSumsq2,
+  kStResidualMax0,    // per link: bits of the largest |values - mirror| (fp32) the last round saw
+  kStResidualMax1,
+  kStResidualMax2,
   kStPendingTiles,    // tiles still marked pending after the last round
   kStWaitTimeouts,
   kStWords = 16

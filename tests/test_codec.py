@@ -94,7 +94,7 @@ def test_mirror_form_tracks_residual_form():
     bits_a = torch.zeros(core.sign_bytes(n), dtype=torch.uint8)
     bits_b = torch.zeros_like(bits_a)
     for it in range(40):
-        sa = core.encode_tensor(v.data_ptr(), k.data_ptr(), n, bits_a.data_ptr(), 0.0)
+        sa = core.encode_tensor(v.data_ptr(), k.data_ptr(), n, bits_a.data_ptr(), 0.0, 0)  # rule 0: the reference's
         sb = core.encode_residual_ref(resid.data_ptr(), n, bits_b.data_ptr())
         if it < 12:
             assert sa == sb
@@ -111,7 +111,7 @@ def test_tensor_stream_converges_to_fp32_floor():
     peer = torch.zeros(n)
     bits = torch.zeros(core.sign_bytes(n), dtype=torch.uint8)
     for _ in range(400):
-        s = core.encode_tensor(v.data_ptr(), k.data_ptr(), n, bits.data_ptr(), 2.0 ** -24)
+        s = core.encode_tensor(v.data_ptr(), k.data_ptr(), n, bits.data_ptr(), 2.0 ** -21)
         core.decode_tensor_add(bits.data_ptr(), s, n, peer.data_ptr(), 0)
     assert torch.equal(peer, k)
     assert ((peer - v).norm() / v.norm()) < 1e-5
@@ -151,16 +151,33 @@ def test_block_silent_when_converged():
     assert torch.equal(k, v)
 
 
-def test_block_scale_is_pow2_floor_of_rms():
+def test_block_scale_is_pow2_floor_of_two_thirds_of_the_largest_residual():
     n = 32
     v = torch.full((n,), 3.0)
     k = torch.zeros(n)
     words = torch.zeros(1, dtype=torch.int32)
     scales = torch.zeros(1, dtype=torch.uint8)
     core.encode_block(v.data_ptr(), k.data_ptr(), n, 32, -60, 22, words.data_ptr(), scales.data_ptr())
-    assert int(scales[0]) - 127 == 1  # rms 3 -> 2^1
+    assert int(scales[0]) - 127 == 1  # largest residual 3 -> 2/3 of it is 2 -> 2^1
     assert int(words[0]) == 0          # all positive -> bit 0
     assert torch.equal(k, torch.full((n,), 2.0))
+
+
+def test_bisection_shrinks_the_error_bound_every_frame():
+    """The largest outstanding residual falls to at most 2/3 with every frame, and by about half on average."""
+    n = 4096
+    torch.manual_seed(9)
+    v = torch.randn(n) * torch.exp(torch.randn(n))  # heavy-tailed
+    k = torch.zeros(n)
+    words = torch.zeros(core.block_words(n), dtype=torch.int32)
+    scales = torch.zeros(core.block_scales(n, 32), dtype=torch.uint8)
+    worst = []
+    for _ in range(14):
+        worst.append(core.encode_block(v.data_ptr(), k.data_ptr(), n, 32, -60, 22, words.data_ptr(), scales.data_ptr()))
+    for a, b in zip(worst[:10], worst[1:11]):
+        assert b <= a * (2.0 / 3.0) * (1 + 1e-6)
+    assert worst[10] <= worst[0] * 0.56 ** 10
+    assert ((v - k).norm() / v.norm()) < 1e-3
 
 
 def test_segment_sumsq():

@@ -76,7 +76,7 @@ def test_tree_shape_of_sequential_joins(free_port):
         out = torch.zeros(4)
         for n in nodes:
             n.copyToTensor(out)
-            assert torch.equal(out, torch.arange(4.0) + 1)
+            assert torch.allclose(out, torch.arange(4.0) + 1, atol=2e-3)  # ready once the stream's scale fell by 2^-12
     finally:
         for n in reversed(nodes):
             n.cfg.rejoin = False
