@@ -255,12 +255,12 @@ def run_ours(args) -> dict | None:
         return e0.elapsed_time(e1) / 1e3, rel, d2h
 
     # ---- warm-up (untimed), timed region, end-to-end region
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment before its first sample: started ahead of the (identical) warm-up steps
     if args.warmup:
         run_steps(0, args.warmup, False)
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     l0 = rep.launches()
     x0 = extra_launches
     secs, rel, _ = run_steps(args.warmup, args.steps, False)

@@ -65,8 +65,8 @@ PYBIND11_MODULE(_cuda, m) {
     ck(launch_sample_sqerr(ptr<float>(a), stride, ptr<float>(b), count, ptr<double>(out), strm(s)), "sample_sqerr");
   });
   m.def("delay", [](uint64_t ns, uintptr_t s) { ck(launch_delay(ns, strm(s)), "delay"); });
-  m.def("tensor_sumsq", [](uintptr_t v, uintptr_t k, int64_t n, uintptr_t out2, uintptr_t s) {
-    ck(launch_tensor_sumsq(ptr<float>(v), ptr<float>(k), n, ptr<double>(out2), strm(s)), "tensor_sumsq");
+  m.def("tensor_maxabs", [](uintptr_t v, uintptr_t k, int64_t n, uintptr_t out2, uintptr_t s) {
+    ck(launch_tensor_maxabs(ptr<float>(v), ptr<float>(k), n, ptr<uint32_t>(out2), strm(s)), "tensor_maxabs");
   });
   m.def("tensor_encode", [](uintptr_t v, uintptr_t k, int64_t n, float scale, uintptr_t words, uintptr_t s) {
     ck(launch_tensor_encode(ptr<float>(v), ptr<float>(k), n, scale, ptr<uint32_t>(words), strm(s)), "tensor_encode");

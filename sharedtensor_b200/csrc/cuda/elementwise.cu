@@ -389,25 +389,26 @@ int launch_snapshot_join(const float* values, float* dst_values, float* mirror, 
 // ---------------------------------------------------------------------------------------------
 // tensor-scale frames on the device (one scale for the whole tensor, 1 bit per element)
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) tensor_sumsq_kernel(const float* __restrict__ v, const float* __restrict__ k, int64_t n,
-                                                           double* __restrict__ out2) {
-  double ax = 0.0, av = 0.0;
+// out2[0] = bits of max |v - k|, out2[1] = bits of max |v| (non-negative floats order like their bit patterns)
+__global__ void __launch_bounds__(256) tensor_maxabs_kernel(const float* __restrict__ v, const float* __restrict__ k, int64_t n,
+                                                            uint32_t* __restrict__ out2) {
+  float mx = 0.f, mv = 0.f;
   for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n; i += int64_t(gridDim.x) * 256) {
-    float a = v[i], x = a - k[i];
-    ax += double(x) * double(x);
-    av += double(a) * double(a);
+    float a = v[i];
+    mx = fmaxf(mx, fabsf(a - k[i]));
+    mv = fmaxf(mv, fabsf(a));
   }
   for (int o = 16; o > 0; o >>= 1) {
-    ax += __shfl_xor_sync(0xffffffffu, ax, o);
-    av += __shfl_xor_sync(0xffffffffu, av, o);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
   }
   if ((threadIdx.x & 31) == 0) {
-    atomicAdd(out2, ax);
-    atomicAdd(out2 + 1, av);
+    atomicMax(out2, __float_as_uint(mx));
+    atomicMax(out2 + 1, __float_as_uint(mv));
   }
 }
-int launch_tensor_sumsq(const float* v, const float* k, int64_t n, double* out2, void* stream) {
-  tensor_sumsq_kernel<<<ew_blocks(n, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(v, k, n, out2);
+int launch_tensor_maxabs(const float* v, const float* k, int64_t n, uint32_t* out2, void* stream) {
+  tensor_maxabs_kernel<<<ew_blocks(n, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(v, k, n, out2);
   return int(cudaGetLastError());
 }
 // words[i/32] bit i%32 = !(v-k > 0); k steps by -/+ scale.  n is padded by the caller to a multiple of 32

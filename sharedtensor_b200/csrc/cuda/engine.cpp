@@ -128,6 +128,9 @@ GpuReplica::~GpuReplica() {
   cudaFree(work_count_);
   cudaFree(status_);
   if (status_host_) cudaFreeHost(status_host_);
+  if (tcp_words_dev_) cudaFree(tcp_words_dev_);
+  if (tcp_stat_dev_) cudaFree(tcp_stat_dev_);
+  if (tcp_pinned_) cudaFreeHost(tcp_pinned_);
   for (void* e : ev_round_) cudaEventDestroy(E(e));
   if (ev_user_) cudaEventDestroy(E(ev_user_));
   if (ev_comm_) cudaEventDestroy(E(ev_comm_));
@@ -315,6 +318,7 @@ void GpuReplica::load_values(const float* src, void* user_stream) {
   check(cudaMemcpyAsync(values(), src, size_t(n_) * 4, cudaMemcpyDeviceToDevice, S(comm_)), "cudaMemcpyAsync");
   check(launch_fill_state(tile_state_, n_tiles_, 1, comm_), "fill_state");
   launches_ += 1;
+  epoch_++;
   order_user_after(user_stream);
 }
 
@@ -323,6 +327,7 @@ void GpuReplica::add(const float* delta, void* user_stream) {
   std::lock_guard<std::mutex> lk(mu_);
   order_after_user(user_stream);
   check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
+  epoch_++;
   launches_ += 1;
   order_user_after(user_stream);
 }
@@ -332,6 +337,7 @@ void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) 
   std::lock_guard<std::mutex> lk(mu_);
   order_after_user(user_stream);
   check(launch_sub_add(values(), neu, old, n_, tile_state_, n_tiles_, 0, comm_), "sub_add kernel");
+  epoch_++;
   launches_ += 1;
   order_user_after(user_stream);
 }
@@ -341,6 +347,7 @@ void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) 
   std::lock_guard<std::mutex> lk(mu_);
   order_after_user(user_stream);
   check(launch_add_scaled_bf16(values(), g, alpha, n_, tile_state_, n_tiles_, comm_), "add_scaled_bf16 kernel");
+  epoch_++;
   launches_ += 1;
   order_user_after(user_stream);
 }
@@ -386,6 +393,64 @@ void GpuReplica::round(bool do_rx, bool do_tx) {
   check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
   check(launch_round_publish(params_, comm_), "round_publish kernel");
   launches_ += 3;
+  epoch_++;
+}
+
+float GpuReplica::tcp_encode(int link, uint32_t* words, float min_scale_abs, float min_scale_rel) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
+  const size_t n_words = size_t((n_ + 31) / 32);
+  if (!tcp_words_dev_) {
+    check(cudaMalloc(reinterpret_cast<void**>(&tcp_words_dev_), n_words * 4), "cudaMalloc tcp words");
+    check(cudaMalloc(reinterpret_cast<void**>(&tcp_stat_dev_), 8), "cudaMalloc tcp stat");
+    check(cudaMallocHost(reinterpret_cast<void**>(&tcp_pinned_), 8 + n_words * 4), "cudaMallocHost tcp staging");
+  }
+  float* k = static_cast<float*>(links_[link].mirror.ptr);
+  check(cudaMemsetAsync(tcp_stat_dev_, 0, 8, S(comm_)), "memset");
+  check(launch_tensor_maxabs(values(), k, n_, tcp_stat_dev_, comm_), "tensor_maxabs kernel");
+  check(cudaMemcpyAsync(tcp_pinned_, tcp_stat_dev_, 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  float xmax, vmax;
+  std::memcpy(&xmax, tcp_pinned_, 4);
+  std::memcpy(&vmax, tcp_pinned_ + 1, 4);
+  // bisection rule of the host codec: power-of-two floor of two thirds of the largest residual
+  float scaled = xmax * 0.6666667f, scale = 0.f;
+  uint32_t sb;
+  std::memcpy(&sb, &scaled, 4);
+  if ((sb >> 23) != 0 && (sb >> 23) != 0xff) {
+    sb &= 0x7f800000u;
+    std::memcpy(&scale, &sb, 4);
+  }
+  float min_scale = min_scale_abs;
+  if (vmax * min_scale_rel > min_scale) min_scale = vmax * min_scale_rel;
+  if (scale < min_scale) scale = 0.f;
+  check(launch_tensor_encode(values(), k, n_, scale, tcp_words_dev_, comm_), "tensor_encode kernel");
+  check(cudaMemcpyAsync(tcp_pinned_ + 2, tcp_words_dev_, n_words * 4, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  std::memcpy(words, tcp_pinned_ + 2, n_words * 4);
+  launches_ += 2;
+  return scale;
+}
+
+void GpuReplica::tcp_decode(int link, const uint32_t* words, float scale) {
+  if (scale == 0.f) return;
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
+  const size_t n_words = size_t((n_ + 31) / 32);
+  if (!tcp_words_dev_) {
+    check(cudaMalloc(reinterpret_cast<void**>(&tcp_words_dev_), n_words * 4), "cudaMalloc tcp words");
+    check(cudaMalloc(reinterpret_cast<void**>(&tcp_stat_dev_), 8), "cudaMalloc tcp stat");
+    check(cudaMallocHost(reinterpret_cast<void**>(&tcp_pinned_), 8 + n_words * 4), "cudaMallocHost tcp staging");
+  }
+  std::memcpy(tcp_pinned_ + 2, words, n_words * 4);
+  check(cudaMemcpyAsync(tcp_words_dev_, tcp_pinned_ + 2, n_words * 4, cudaMemcpyHostToDevice, S(comm_)), "cudaMemcpyAsync");
+  check(launch_tensor_decode(tcp_words_dev_, scale, n_, values(), static_cast<float*>(links_[link].mirror.ptr), tile_state_, comm_),
+        "tensor_decode kernel");
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  launches_ += 1;
+  epoch_++;
 }
 
 void GpuReplica::sync() {
@@ -458,6 +523,7 @@ void GpuReplica::engine_loop() {
     }
     r++;
     if (r >= depth) cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
+    if (status_host_[kStLastWorkCount] != 0) epoch_++;
     if (status_host_[kStLastWorkCount] == 0) {
       idle_rounds++;
       if (idle_rounds > 2 && cfg_.idle_sleep_us > 0) ::usleep(useconds_t(cfg_.idle_sleep_us));

@@ -76,6 +76,10 @@ class GpuReplica {
   void copy_mirror_from_values(int link);                 // mirror <- values (neighbour is given a snapshot)
   void push_snapshot(int link, float* remote_values);     // neighbour's values <- values, mirror <- values
   void round(bool do_rx = true, bool do_tx = true);
+  // TCP links: a link with a mirror and no ring peers; its tensor-scale frames (the reference's wire format) are
+  // made and applied on the device, host threads only move bytes.  `words` is host memory of ceil(n/32) words.
+  float tcp_encode(int link, uint32_t* words, float min_scale_abs, float min_scale_rel);  // returns the frame's scale
+  void tcp_decode(int link, const uint32_t* words, float scale);
   void sync();
 
   // ---- engine thread: free-running rounds ----
@@ -86,6 +90,7 @@ class GpuReplica {
   // ---- observation ----
   std::vector<uint64_t> status();      // StatusWord order; synchronises the comm stream
   uint64_t launches() const { return launches_.load(); }
+  uint64_t change_epoch() const { return epoch_.load(); }  // bumped whenever values may have changed
   std::string last_error() const;
 
  private:
@@ -129,6 +134,9 @@ class GpuReplica {
   int32_t* work_count_ = nullptr;
   uint64_t* status_ = nullptr;
   uint64_t* status_host_ = nullptr;    // pinned
+  uint32_t* tcp_words_dev_ = nullptr;  // ceil(n/32) words, staging of TCP frames
+  uint32_t* tcp_stat_dev_ = nullptr;   // 2 words
+  uint32_t* tcp_pinned_ = nullptr;     // pinned host staging: 2 stat words + ceil(n/32) frame words
   RoundParams params_{};
   int map_link_[kMaxLinks] = {0, 0, 0};  // dense link index of each link id
   int round_no_ = 0;
@@ -142,6 +150,7 @@ class GpuReplica {
   std::thread engine_;
   std::atomic<bool> engine_on_{false}, engine_stop_{false};
   std::atomic<uint64_t> launches_{0};
+  std::atomic<uint64_t> epoch_{1};
   std::string error_;
 };
 

@@ -23,6 +23,7 @@
 #include <chrono>
 #include <condition_variable>
 #include <cstdio>
+#include <cmath>
 #include <cstring>
 #include <deque>
 #include <memory>
@@ -169,7 +170,11 @@ class GpuNode {
       py::dict e;
       e["state"] = states[edges_[s].state];
       e["peer"] = edges_[s].state ? addr_to_string(edges_[s].peer) : std::string();
-      e["transport"] = edges_[s].state == 2 ? "p2p" : "";
+      e["transport"] = edges_[s].state == 2 ? (edges_[s].tcp ? "tcp" : "p2p") : "";
+      if (edges_[s].tcp && tcp_[s]) {
+        e["frames_sent"] = tcp_[s]->frames_sent.load();
+        e["frames_recv"] = tcp_[s]->frames_recv.load();
+      }
       e["link"] = edges_[s].link;
       edges[names[s]] = e;
     }
@@ -206,9 +211,123 @@ class GpuNode {
     sockaddr_in peer{};
     uint64_t adopted_ms = 0;
     bool upgrading = false;  // the parent side of the upgrade is at work on this edge
+    bool tcp = false;        // frames travel over the TCP connection (see TcpEdge)
     int link = -1, peer_id = -1, block = -1;
     VmmBlock remote;      // neighbour's edge block mapped here
   };
+
+  // An edge whose other end does not speak the peer-memory upgrade (a CPU node, the reference, another host):
+  // tensor-scale frames over the TCP connection, encoded and decoded on the device, bytes moved by two threads
+  // (the counterpart of the reference's synca / sync_in pair, src/sharedtensor.c:113-189).
+  struct TcpEdge {
+    int slot = 0, fd = -1, link = -1;
+    std::thread tx, rx;
+    std::atomic<bool> stop{false}, failed{false};
+    std::atomic<uint64_t> frames_sent{0}, frames_recv{0};
+  };
+
+  void start_tcp_edge(int slot, int fd, const sockaddr_in& peer) {
+    int link = rep_->add_link();
+    if (link < 0) {
+      ::close(fd);
+      return;
+    }
+    std::unique_ptr<TcpEdge> te(new TcpEdge());
+    te->slot = slot;
+    te->fd = fd;
+    te->link = link;
+    TcpEdge* raw = te.get();
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      Edge& e = edges_[slot];
+      e.state = 2;
+      e.tcp = true;
+      e.tcp_fd = fd;
+      e.peer = peer;
+      e.link = link;
+      tcp_[slot] = std::move(te);
+    }
+    raw->tx = std::thread([this, raw] { tcp_tx_loop(raw); });
+    raw->rx = std::thread([this, raw] { tcp_rx_loop(raw); });
+    std::fprintf(stderr, "[sharedtensor] edge %d to %s runs over TCP (reference wire format)\n", slot, addr_to_string(peer).c_str());
+  }
+
+  void tcp_tx_loop(TcpEdge* e) {
+    cudaSetDevice(device_);
+    const size_t n_words = size_t((n_ + 31) / 32), n_bytes = size_t((n_ + 7) / 8);
+    std::vector<uint32_t> words(n_words);
+    std::vector<uint8_t> frame(4 + n_bytes);
+    bool sent_first = false, idle_announced = false;
+    uint64_t seen = 0;
+    while (!e->stop.load()) {
+      const uint64_t ep = rep_->change_epoch();
+      if (sent_first && idle_announced && ep == seen) {
+        ::usleep(500);
+        continue;
+      }
+      seen = ep;
+      float scale = 0.f;
+      try {
+        scale = rep_->tcp_encode(e->link, words.data(), 0.f, 2.3841858e-07f);
+      } catch (const std::exception&) {
+        e->failed.store(true);
+        break;
+      }
+      const bool noop = scale == 0.f;
+      if (noop && sent_first && idle_announced) continue;  // nothing new; one no-op frame already ended the burst
+      std::memcpy(frame.data(), &scale, 4);
+      std::memcpy(frame.data() + 4, words.data(), n_bytes);
+      IoStatus st = write_full(e->fd, frame.data(), frame.size(), &e->stop);
+      if (st != IoStatus::Ok) {
+        if (st != IoStatus::Stopped) e->failed.store(true);
+        break;
+      }
+      sent_first = true;
+      idle_announced = noop;
+      if (!noop) seen = 0;  // keep draining until a pass has nothing to say
+      e->frames_sent++;
+    }
+  }
+
+  void tcp_rx_loop(TcpEdge* e) {
+    cudaSetDevice(device_);
+    const size_t n_words = size_t((n_ + 31) / 32), n_bytes = size_t((n_ + 7) / 8);
+    std::vector<uint32_t> words(n_words, 0u);
+    std::vector<uint8_t> frame(4 + n_bytes);
+    float first_scale = 0.f;
+    const uint64_t t0 = now_ms();
+    while (!e->stop.load()) {
+      IoStatus st = read_full(e->fd, frame.data(), frame.size(), &e->stop);
+      if (st != IoStatus::Ok) {
+        if (st != IoStatus::Stopped) e->failed.store(true);
+        break;
+      }
+      float scale;
+      std::memcpy(&scale, frame.data(), 4);
+      if (!(scale >= 0.f) || scale > 3.0e38f) {  // NaN, negative or infinite: the peer's state is broken
+        e->failed.store(true);
+        break;
+      }
+      std::memcpy(words.data(), frame.data() + 4, n_bytes);
+      try {
+        rep_->tcp_decode(e->link, words.data(), scale);
+      } catch (const std::exception&) {
+        e->failed.store(true);
+        break;
+      }
+      e->frames_recv++;
+      if (e->slot == kSlotUp) {
+        std::lock_guard<std::mutex> g(mu_);
+        if (!ready_) {
+          if (first_scale == 0.f && scale > 0.f) first_scale = scale;
+          if (scale == 0.f || scale <= std::ldexp(first_scale, -12) || now_ms() - t0 > 30000) {
+            ready_ = true;
+            cv_.notify_all();
+          }
+        }
+      }
+    }
+  }
 
   Hello my_hello() const {
     Hello h;
@@ -270,7 +389,22 @@ class GpuNode {
       }
     }
     master_.store(false);
-    if (!upgrade_as_child(jr, first, &err)) {
+    bool no_endpoint = false;
+    if (!upgrade_as_child(jr, first, &err, &no_endpoint)) {
+      if (no_endpoint) {
+        // the parent is a CPU node, the reference, or on another host: speak TCP frames with it.  A node that
+        // re-joins keeps only what its lost parent had not been told (like the CPU node).
+        if (!first && carry_valid_) {
+          cudaMemcpy(rep_->values(), carry_, size_t(n_) * 4, cudaMemcpyDeviceToDevice);
+          cudaFree(carry_);
+          carry_ = nullptr;
+          carry_valid_ = false;
+        }
+        start_tcp_edge(kSlotUp, jr.fd, jr.parent_addr);
+        std::fprintf(stderr, "[sharedtensor] joined %s:%d below %s after %d redirect(s), GPU %d, TCP edge\n", host_.c_str(), port_,
+                     addr_to_string(jr.parent_addr).c_str(), jr.hops, device_);
+        return true;
+      }
       std::fprintf(stderr, "[sharedtensor] peer-memory upgrade with %s failed: %s\n", addr_to_string(jr.parent_addr).c_str(),
                    err.c_str());
       ::close(jr.fd);
@@ -287,26 +421,27 @@ class GpuNode {
   }
 
   // ---- child side of the upgrade ----
-  bool upgrade_as_child(const JoinResult& jr, bool first, std::string* err) {
-    int us = unix_connect_abstract(unix_name(jr.parent_addr), opt_.upgrade_timeout_ms);
+  bool upgrade_as_child(const JoinResult& jr, bool first, std::string* err, bool* no_endpoint) {
+    int us = unix_connect_abstract(unix_name(jr.parent_addr), 300);
     if (us < 0) {
       *err = "parent has no peer-memory endpoint on this host (TCP-only parent)";
+      *no_endpoint = true;
       return false;
     }
     bool ok = false;
     int block = -1, link = -1;
     VmmBlock remote;
     do {
+      // the hello goes out first, so that the parent knows at once that this child will not speak TCP frames
+      Hello h = my_hello();
+      if (!unix_send_fd(us, -1, &h, sizeof(h))) {
+        *err = "hello send failed";
+        break;
+      }
       block = rep_->alloc_edge_block();
       link = rep_->add_link();
       if (block < 0 || link < 0) {
         *err = "out of links or edge blocks";
-        break;
-      }
-      Hello h = my_hello();
-      h.edge_bytes = rep_->edge_block(block).bytes;
-      if (!unix_send_fd(us, -1, &h, sizeof(h))) {
-        *err = "hello send failed";
         break;
       }
       Hello reply;
@@ -330,7 +465,8 @@ class GpuNode {
       }
       // A re-joining node keeps what its lost parent had not been told: u = values - mirror_up is set
       // aside now and added back on top of the new parent's snapshot.
-      bool sent = unix_send_fd(us, fd_edge, "E", 1) && unix_send_fd(us, fd_vals, "V", 1);
+      const uint64_t sz_edge = rep_->edge_block(block).bytes, sz_vals = rep_->values_block().bytes;
+      bool sent = unix_send_fd(us, fd_edge, &sz_edge, 8) && unix_send_fd(us, fd_vals, &sz_vals, 8);
       ::close(fd_edge);
       ::close(fd_vals);
       if (!sent) {
@@ -338,12 +474,12 @@ class GpuNode {
         break;
       }
       int fd_remote = -1;
-      char tag = 0;
-      if (!unix_recv_fd(us, &fd_remote, &tag, 1, opt_.upgrade_timeout_ms) || fd_remote < 0) {
+      uint64_t sz_remote = 0;
+      if (!unix_recv_fd(us, &fd_remote, &sz_remote, 8, opt_.upgrade_timeout_ms) || fd_remote < 0) {
         *err = "parent's edge block did not arrive";
         break;
       }
-      remote = vmm_import_fd(fd_remote, size_t(reply.edge_bytes), device_, &e2);
+      remote = vmm_import_fd(fd_remote, size_t(sz_remote), device_, &e2);
       ::close(fd_remote);
       if (!remote.ptr) {
         *err = "cannot map parent's edge block: " + e2;
@@ -442,17 +578,16 @@ class GpuNode {
         break;
       }
       Hello r = my_hello();
-      r.edge_bytes = rep_->edge_block(block).bytes;
       if (!unix_send_fd(us, -1, &r, sizeof(r))) break;
       int fd_edge = -1, fd_vals = -1;
-      char tag = 0;
-      if (!unix_recv_fd(us, &fd_edge, &tag, 1, opt_.upgrade_timeout_ms) || fd_edge < 0) break;
-      if (!unix_recv_fd(us, &fd_vals, &tag, 1, opt_.upgrade_timeout_ms) || fd_vals < 0) {
+      uint64_t sz_edge = 0, sz_vals = 0;
+      if (!unix_recv_fd(us, &fd_edge, &sz_edge, 8, opt_.upgrade_timeout_ms * 4) || fd_edge < 0) break;
+      if (!unix_recv_fd(us, &fd_vals, &sz_vals, 8, opt_.upgrade_timeout_ms) || fd_vals < 0) {
         ::close(fd_edge);
         break;
       }
-      remote = vmm_import_fd(fd_edge, size_t(h.edge_bytes), device_, &err);
-      child_values = vmm_import_fd(fd_vals, size_t(h.values_bytes), device_, &err);
+      remote = vmm_import_fd(fd_edge, size_t(sz_edge), device_, &err);
+      child_values = vmm_import_fd(fd_vals, size_t(sz_vals), device_, &err);
       ::close(fd_edge);
       ::close(fd_vals);
       if (!remote.ptr || !child_values.ptr) {
@@ -461,7 +596,8 @@ class GpuNode {
       }
       int my_fd = vmm_export_fd(rep_->edge_block(block), &err);
       if (my_fd < 0) break;
-      bool sent = unix_send_fd(us, my_fd, "E", 1);
+      const uint64_t my_sz = rep_->edge_block(block).bytes;
+      bool sent = unix_send_fd(us, my_fd, &my_sz, 8);
       ::close(my_fd);
       if (!sent) break;
       // state transfer: one pass over the replica, in stream order with the rounds
@@ -497,14 +633,17 @@ class GpuNode {
       {
         std::lock_guard<std::mutex> g(mu_);
         for (int s = 0; s < kNumSlots; s++) {
-          if (edges_[s].state && edges_[s].tcp_fd >= 0) {
+          if (edges_[s].state && edges_[s].tcp_fd >= 0 && !edges_[s].tcp) {
             pfds.push_back({edges_[s].tcp_fd, POLLIN, 0});
             slots.push_back(s);
           }
+          if (edges_[s].tcp && tcp_[s] && tcp_[s]->failed.load()) {
+            pfds.push_back({-1, 0, 0});
+            slots.push_back(100 + s);
+          }
           // a child that was adopted over TCP but never came in over the unix socket is a TCP-only
           // peer (CPU node, reference, other host): not served by this class
-          if (edges_[s].state == 1 && !edges_[s].upgrading &&
-              now_ms() - edges_[s].adopted_ms > uint64_t(opt_.upgrade_timeout_ms) * 2) {
+          if (edges_[s].state == 1 && !edges_[s].upgrading && now_ms() - edges_[s].adopted_ms > 600) {
             pfds.push_back({-1, 0, 0});
             slots.push_back(-(s + 1));
           }
@@ -517,19 +656,32 @@ class GpuNode {
       int pr = ::poll(pfds.data(), pfds.size(), kPollMs);
       for (size_t i = 0; i < pfds.size(); i++) {
         if (slots[i] < 0) {
+          // adopted over TCP and no peer-memory hello followed: a TCP-only child (CPU node, reference, other host)
           int s = -slots[i] - 1;
-          std::fprintf(stderr, "[sharedtensor] edge %d: peer never completed the peer-memory upgrade, dropping it\n", s);
-          drop_edge(s, true);
+          int fd;
+          sockaddr_in peer;
+          {
+            std::lock_guard<std::mutex> g(mu_);
+            if (edges_[s].state != 1 || edges_[s].upgrading) continue;
+            fd = edges_[s].tcp_fd;
+            peer = edges_[s].peer;
+            edges_[s].upgrading = true;  // claimed
+          }
+          start_tcp_edge(s, fd, peer);
           continue;
         }
-        if (pr <= 0 || !(pfds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
-        char buf[256];
-        ssize_t r = ::recv(pfds[i].fd, buf, sizeof(buf), MSG_DONTWAIT);
-        if (r > 0) continue;  // stray bytes on a liveness connection are ignored
-        if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;
         int s = slots[i];
+        if (s < 100) {
+          if (pr <= 0 || !(pfds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+          char buf[256];
+          ssize_t r = ::recv(pfds[i].fd, buf, sizeof(buf), MSG_DONTWAIT);
+          if (r > 0) continue;  // stray bytes on a liveness connection are ignored
+          if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;
+        } else {
+          s -= 100;  // a TCP edge whose thread reported a failure
+        }
         if (stop_.load()) break;
-        std::fprintf(stderr, "[sharedtensor] edge %d lost (neighbour closed its liveness connection)\n", s);
+        std::fprintf(stderr, "[sharedtensor] edge %d lost (neighbour closed its connection)\n", s);
         bool was_up = s == kSlotUp;
         if (was_up && opt_.rejoin) save_carry();
         drop_edge(s, true);
@@ -586,6 +738,17 @@ class GpuNode {
 
   void drop_edge(int slot, bool count) {
     Edge old;
+    std::unique_ptr<TcpEdge> te;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      te = std::move(tcp_[slot]);
+    }
+    if (te) {
+      te->stop.store(true);
+      if (te->fd >= 0) ::shutdown(te->fd, SHUT_RDWR);
+      if (te->tx.joinable()) te->tx.join();
+      if (te->rx.joinable()) te->rx.join();
+    }
     {
       std::lock_guard<std::mutex> g(mu_);
       old = edges_[slot];
@@ -617,6 +780,7 @@ class GpuNode {
   std::unique_ptr<TreeListener> listener_;
   int unix_fd_ = -1;
   Edge edges_[kNumSlots];
+  std::unique_ptr<TcpEdge> tcp_[kNumSlots];
   std::mutex mu_;
   std::condition_variable cv_;
   bool ready_ = false;

@@ -117,7 +117,7 @@ int launch_delay(uint64_t ns, void* stream);
 // values -> dst (peer or local) and mirror <- values in one pass; used for snapshot-on-join.
 int launch_snapshot_join(const float* values, float* dst_values, float* mirror, int64_t n_padded, void* stream);
 // Tensor-scale frames for TCP edges, encoded/decoded on the device (wire format of the reference).
-int launch_tensor_sumsq(const float* v, const float* k, int64_t n, double* out2, void* stream);  // out2[0]=sum (v-k)^2, out2[1]=sum v^2
+int launch_tensor_maxabs(const float* v, const float* k, int64_t n, uint32_t* out2, void* stream);  // bits of max|v-k|, max|v|
 int launch_tensor_encode(const float* v, float* k, int64_t n, float scale, uint32_t* words, void* stream);
 int launch_tensor_decode(const uint32_t* words, float scale, int64_t n, float* v, float* k, uint8_t* tile_state,
                          void* stream);
