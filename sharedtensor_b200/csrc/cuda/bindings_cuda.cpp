@@ -85,7 +85,6 @@ PYBIND11_MODULE(_cuda, m) {
       .def_readwrite("rel_bits", &GpuConfig::rel_bits)
       .def_readwrite("comm_ctas", &GpuConfig::comm_ctas)
       .def_readwrite("shareable", &GpuConfig::shareable)
-      .def_readwrite("atomic_values", &GpuConfig::atomic_values)
       .def_readwrite("rounds_in_flight", &GpuConfig::rounds_in_flight)
       .def_readwrite("idle_sleep_us", &GpuConfig::idle_sleep_us)
       .def_readwrite("frames_per_round", &GpuConfig::frames_per_round);

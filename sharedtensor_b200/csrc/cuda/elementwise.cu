@@ -265,9 +265,23 @@ __global__ void __launch_bounds__(256) table_partial_kernel(const float* __restr
   const int64_t begin = off[seg] + (c - first_chunk[seg]) * kTsChunk;
   const int64_t end = min(begin + kTsChunk, off[seg + 1]);
   double acc = 0.0;
-  for (int64_t i = begin + threadIdx.x; i < end; i += 256) {
-    float v = x[i];
-    acc += double(v) * double(v);
+  // 16-byte loads over the aligned middle of the chunk, scalar loads at its ragged ends
+  int64_t a0 = (begin + 3) & ~int64_t(3);
+  if (a0 > end) a0 = end;
+  const int64_t a1 = a0 + ((end - a0) & ~int64_t(3));
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (int64_t i = begin + threadIdx.x; i < a0; i += 256) acc += double(x[i]) * double(x[i]);
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (int64_t i = a0 / 4 + threadIdx.x; i < a1 / 4; i += 256) {
+      float4 v = ldg_stream(x4 + i);
+      acc += (double(v.x) * double(v.x) + double(v.y) * double(v.y)) + (double(v.z) * double(v.z) + double(v.w) * double(v.w));
+    }
+    for (int64_t i = a1 + threadIdx.x; i < end; i += 256) acc += double(x[i]) * double(x[i]);
+  } else {
+    for (int64_t i = begin + threadIdx.x; i < end; i += 256) {
+      float v = x[i];
+      acc += double(v) * double(v);
+    }
   }
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;

@@ -105,7 +105,6 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   params_.worklist = worklist_;
   params_.work_count = work_count_;
   params_.status = status_;
-  params_.atomic_values = cfg.atomic_values ? 1 : 0;
   params_.frames_per_round = cfg.frames_per_round < 1 ? 1 : (cfg.frames_per_round > 3 ? 3 : cfg.frames_per_round);
   check(cudaDeviceSynchronize(), "init");
 }

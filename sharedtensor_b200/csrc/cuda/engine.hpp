@@ -27,7 +27,6 @@ struct GpuConfig {
   int rel_bits = 22;
   int comm_ctas = 0;         // 0 = one CTA per SM
   bool shareable = true;     // allocate edge blocks and values with the VMM API (needed across processes)
-  bool atomic_values = false;
   int rounds_in_flight = 2;
   int idle_sleep_us = 200;
   int frames_per_round = 1;  // successive 1-bit frames per link and round (1..3)

@@ -5,14 +5,16 @@
 //   1. array-tiles are staged into shared memory with 1-D TMA bulk copies (cp.async.bulk, completion on an
 //      mbarrier, a three-slot ring per group so the next copy is in flight while this one is computed;
 //      every source is this GPU's own memory);
-//   2. a thread owns 32 consecutive elements (read with an XOR swizzle, so no bank conflicts): it decodes
-//      the frames that arrived (sign bit + per-block power-of-two scale) into the values and into the
-//      mirror of the link they came from                 (reference src/sharedtensor.c:106-111, 124-127);
+//   2. a thread owns 32 consecutive elements (read with an XOR swizzle, so no bank conflicts) and keeps its
+//      values in registers for the whole tile; in a link's step it decodes the frames that arrived on that
+//      link (sign bit + per-block power-of-two scale) once and adds them to the values and to the link's
+//      mirror                                             (reference src/sharedtensor.c:106-111, 124-127);
 //   3. per link it forms the residual values - mirror, the block's sum of squares, the exponent code from
 //      the float's exponent bits, its 32 sign bits as one word, and steps the mirror by -/+ 2^k
 //                                                         (reference 156-174);
-//   4. changed array-tiles go back to global memory with TMA bulk stores, and the packed words + scale
-//      bytes go straight into the neighbours' ring slots with TMA bulk stores over NVLink
+//   4. changed mirror tiles go back to global memory with TMA bulk stores, changed values with one 128-byte
+//      line per thread, and the packed words + scale bytes go straight into the neighbours' ring slots with
+//      TMA bulk stores over NVLink
 //      (reference 176-177: two socket writes).
 // Nothing in here waits for another GPU.  The only waits are on this CTA's own TMA copies, and they are
 // bounded: on a timeout the group records an error in the status block and leaves.
@@ -43,8 +45,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -116,8 +118,8 @@ __device__ __forceinline__ int block_code_dev(float xmax, uint32_t vmax_bits, in
 // ----------------------------------------------------------------------------------------------
 // After round_main: tell the neighbours what happened.  Credits for the frames this replica consumed
 // go to their senders, sequence flags for the frames it wrote go to their receivers.  round_main has
-// completed (stream order), so its peer stores are performed; the release stores below order them
-// before the flag for an observer at system scope.
+// completed (stream order), so its peer stores are performed; one system-scope fence per publishing
+// thread orders them before the flag stores that follow it.
 __global__ void __launch_bounds__(256) round_publish_kernel(const __grid_constant__ RoundParams p) {
   const int tile = blockIdx.x * blockDim.x + threadIdx.x;
   if (tile >= p.n_tiles) return;
@@ -127,12 +129,13 @@ __global__ void __launch_bounds__(256) round_publish_kernel(const __grid_constan
   const uint2 sentw = *reinterpret_cast<const uint2*>(p.sent + size_t(tile) * 8);
   const uint8_t* ps = reinterpret_cast<const uint8_t*>(&sentw);
   if ((prev.x | prev.y) == 0u && (sentw.x | sentw.y) == 0u) return;  // nothing consumed, nothing sent
+  __threadfence_system();
   for (int r = 0; r < p.n_in; r++) {
     int avail = pc[r] >> 6;
     if (avail) {
       uint32_t seq = p.in[r].rx_seq[tile] + uint32_t(avail);
       p.in[r].rx_seq[tile] = seq;
-      st_release_sys(p.in[r].credit_remote + tile, seq);
+      st_relaxed_sys(p.in[r].credit_remote + tile, seq);
     }
   }
   for (int r = 0; r < p.n_out; r++) {
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(256) round_publish_kernel(const __grid_constan
       const int slot0 = pc[8 + r] & 63;
       for (int f = 0; f < frames; f++) {
         seq++;
-        st_release_sys(p.out[r].flags_remote + size_t((slot0 + f) % p.ring_slots) * p.n_tiles + tile, seq);
+        st_relaxed_sys(p.out[r].flags_remote + size_t((slot0 + f) % p.ring_slots) * p.n_tiles + tile, seq);
       }
       p.out[r].tx_seq[tile] = seq;
     }
@@ -208,11 +211,6 @@ __device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, u
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ void bulk_s2g_add_f32(void* dst_gmem, const void* src_smem, uint32_t bytes) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_gmem),
-               "r"(smem_u32(src_smem)), "r"(bytes)
-               : "memory");
-}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -244,24 +242,25 @@ __device__ __forceinline__ float signed_scale(uint32_t scale_bits, uint32_t w, i
 // ---- per-thread arithmetic on 32 consecutive elements held as eight float4 pieces; piece q holds elements
 // 4*(q^sw) .. +3.  VMASK: bit i set = element i of the 32 exists (all ones except in a tensor's last chunk).
 
-// d += frame: element i moves by +/- 2^(code-127) according to bit i of w
+// a += frame and b += frame with one decode (values and the mirror of the link the frame came from)
 template <bool FULL>
-__device__ __forceinline__ void apply_frame(float4 (&d)[8], uint32_t w, uint32_t sb, int sw, uint32_t vmask) {
+__device__ __forceinline__ void apply_frame2(float4 (&a)[8], float4 (&b)[8], uint32_t w, uint32_t sb, int sw, uint32_t vmask) {
 #pragma unroll
   for (int q = 0; q < 8; q++) {
     const int sh = 4 * (q ^ sw);
     const uint32_t wq = w >> sh;
+    const float f0 = signed_scale(sb, wq, 0), f1 = signed_scale(sb, wq, 1), f2 = signed_scale(sb, wq, 2), f3 = signed_scale(sb, wq, 3);
     if (FULL) {
-      d[q].x = __fadd_rn(d[q].x, signed_scale(sb, wq, 0));
-      d[q].y = __fadd_rn(d[q].y, signed_scale(sb, wq, 1));
-      d[q].z = __fadd_rn(d[q].z, signed_scale(sb, wq, 2));
-      d[q].w = __fadd_rn(d[q].w, signed_scale(sb, wq, 3));
+      a[q].x = __fadd_rn(a[q].x, f0); b[q].x = __fadd_rn(b[q].x, f0);
+      a[q].y = __fadd_rn(a[q].y, f1); b[q].y = __fadd_rn(b[q].y, f1);
+      a[q].z = __fadd_rn(a[q].z, f2); b[q].z = __fadd_rn(b[q].z, f2);
+      a[q].w = __fadd_rn(a[q].w, f3); b[q].w = __fadd_rn(b[q].w, f3);
     } else {
       const uint32_t vq = vmask >> sh;
-      if (vq & 1u) d[q].x = __fadd_rn(d[q].x, signed_scale(sb, wq, 0));
-      if (vq & 2u) d[q].y = __fadd_rn(d[q].y, signed_scale(sb, wq, 1));
-      if (vq & 4u) d[q].z = __fadd_rn(d[q].z, signed_scale(sb, wq, 2));
-      if (vq & 8u) d[q].w = __fadd_rn(d[q].w, signed_scale(sb, wq, 3));
+      if (vq & 1u) { a[q].x = __fadd_rn(a[q].x, f0); b[q].x = __fadd_rn(b[q].x, f0); }
+      if (vq & 2u) { a[q].y = __fadd_rn(a[q].y, f1); b[q].y = __fadd_rn(b[q].y, f1); }
+      if (vq & 4u) { a[q].z = __fadd_rn(a[q].z, f2); b[q].z = __fadd_rn(b[q].z, f2); }
+      if (vq & 8u) { a[q].w = __fadd_rn(a[q].w, f3); b[q].w = __fadd_rn(b[q].w, f3); }
     }
   }
 }
@@ -350,7 +349,7 @@ int round_main_smem_bytes(int, int, int payload_bytes, int* stages_out) {
   return group_layout(payload_bytes, kMaxGroups).total;
 }
 
-template <bool ATOMIC, int kGroups>
+template <int kGroups>
 __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(const __grid_constant__ RoundParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const GroupSmem lay = group_layout(p.payload_bytes, kGroups);
@@ -393,8 +392,13 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
   int tile_cur = my_count > 0 ? p.worklist[first] : 0;
   int tile_next = my_count > 1 ? p.worklist[first + stride] : 0;
   uint4 cw_cur = my_count > 0 ? *reinterpret_cast<const uint4*>(p.ctrl + size_t(tile_cur) * 16) : make_uint4(0u, 0u, 0u, 0u);
+  // Mirrors are visited in link order on even rounds and in reverse order on odd rounds: a frame is applied to the
+  // values in its own link's step, so links visited earlier in the same tile forward it one round later, and
+  // alternating the order shares that delay out.
+  const bool reverse = (p.round & 1) != 0;
+  auto link_of = [&](int a) -> int { return reverse ? L - a : a - 1; };
   auto src_of = [&](int tile, int a) -> const float* {
-    return (a == 0 ? p.values : p.mirror[a - 1]) + size_t(tile) * kTile;
+    return (a == 0 ? p.values : p.mirror[link_of(a)]) + size_t(tile) * kTile;
   };
   auto issue_load = [&](int c, int tile) {
     const int s = c % kSlots;
@@ -426,19 +430,21 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
     uint32_t sent_lo = 0, sent_hi = 0;
 
     float4 v[8];  // piece q holds elements 4*(q^sw) .. +3 of this thread's 32
+    bool v_changed = false;
     for (int a = 0; a < arrays && !aborted; a++) {
       const int c = i * arrays + a;
       const int s = c % kSlots;
       float4* slot4 = reinterpret_cast<float4*>(slots + size_t(s) * kTileBytes) + t * 8;
-      const int l = a - 1;
+      const int l = a == 0 ? -1 : link_of(a);
 
-      // Frames that concern this step: all in-rings for the values, the link's own in-rings for a mirror
-      // (decoded a second time; they are a few hundred bytes per tile and come from L1/L2).  They are fetched
-      // three at a time so that their load latencies overlap, the first batch before the wait on the slot.
+      // Frames that concern this step: none for the values, the link's own in-rings for a mirror; they are
+      // decoded once and added to the mirror and to the values, which stay in registers for the whole tile.
+      // (A few hundred bytes per tile, from L1/L2.)  They are fetched three at a time so that their load
+      // latencies overlap, the first batch before the wait on the slot.
       int it_r = -1, it_f = 0, it_avail = 0;
       uint32_t it_ib = 0;
       auto next_frame = [&]() -> const uint8_t* {
-        if (!rx_any) return nullptr;
+        if (!rx_any || a == 0) return nullptr;
         while (true) {
           if (it_r >= 0 && it_f < it_avail) {
             const int slot_no = (int(it_ib & 63u) + it_f) % p.ring_slots;
@@ -448,7 +454,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
           it_r++;
           if (it_r >= p.n_in) return nullptr;
           it_ib = in_byte(it_r);
-          it_avail = (a > 0 && p.in[it_r].link != l) ? 0 : int(it_ib >> 6);
+          it_avail = p.in[it_r].link != l ? 0 : int(it_ib >> 6);
           it_f = 0;
         }
       };
@@ -477,15 +483,12 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
 
       bool changed = false;
       auto apply_one = [&](uint32_t w, uint32_t code) {
-        if (a == 0 && t == 0) n_rx++;
+        if (t == 0) n_rx++;
         if (!code) return;
         changed = true;
+        v_changed = true;
         const uint32_t sb = code << 23;  // bits of 2^(code-127)
-        if (a == 0) {
-          if (full_chunk) apply_frame<true>(v, w, sb, sw, vmask); else apply_frame<false>(v, w, sb, sw, vmask);
-        } else {
-          if (full_chunk) apply_frame<true>(k, w, sb, sw, vmask); else apply_frame<false>(k, w, sb, sw, vmask);
-        }
+        if (full_chunk) apply_frame2<true>(v, k, w, sb, sw, vmask); else apply_frame2<false>(v, k, w, sb, sw, vmask);
       };
       while (fp0) {
         const uint32_t w0 = fw0, c0 = fc0, w1 = fw1, c1 = fc1, w2 = fw2, c2 = fc2;
@@ -554,27 +557,10 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
         }
       }
 
-      // ---------------- write the array-tile back into its slot if this thread changed it
-      if (changed) {
-        if (a == 0) {
-          if (ATOMIC) {
-            // the slot becomes the difference, added to global memory by the copy engine
+      // ---------------- a changed mirror goes back through its slot (the values are written at the end of the tile)
+      if (changed && a > 0) {
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
-              float4 o = slot4[q ^ sw];
-              slot4[q ^ sw] = make_float4(v[q].x - o.x, v[q].y - o.y, v[q].z - o.z, v[q].w - o.w);
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 8; q++) slot4[q ^ sw] = v[q];
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < 8; q++) slot4[q ^ sw] = k[q];
-        }
-      } else if (a == 0 && ATOMIC && rx_any) {
-#pragma unroll
-        for (int q = 0; q < 8; q++) slot4[q ^ sw] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < 8; q++) slot4[q ^ sw] = k[q];
       }
       fence_async_smem();
       {
@@ -595,12 +581,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
 
       if (t == 0) {
         void* gdst = const_cast<float*>(src_of(tile, a));
-        if (any_changed) {
-          if (a == 0 && ATOMIC)
-            bulk_s2g_add_f32(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
-          else
-            bulk_s2g(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
-        }
+        if (any_changed && a > 0) bulk_s2g(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
         if (a > 0 && n_frames > 0 && ns_bits) {
           int sent_here = 0;
           for (int f = 0; f < n_frames; f++) {
@@ -632,6 +613,12 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
       }
     }
     if (aborted) break;
+    if (v_changed) {
+      // this thread's 32 values are one 128-byte line of global memory
+      float4* gv = reinterpret_cast<float4*>(p.values + size_t(tile) * kTile) + t * 8;
+#pragma unroll
+      for (int q = 0; q < 8; q++) gv[q ^ sw] = v[q];
+    }
     if (t == 0) {
       *reinterpret_cast<uint2*>(p.sent + size_t(tile) * 8) = make_uint2(sent_lo, sent_hi);
       p.tile_state[tile] = uint8_t(pend_tile ? 1 : 0);
@@ -696,30 +683,29 @@ int launch_round_publish(const RoundParams& p, void* stream) {
   return int(cudaGetLastError());
 }
 
-template <bool ATOMIC, int G>
+template <int G>
 static int launch_main_t(const RoundParams& p, int ctas, cudaStream_t stream) {
   const int smem = group_layout(p.payload_bytes, G).total;
   static int configured_for = -1;  // per instantiation
   if (configured_for < smem) {
-    cudaError_t e = cudaFuncSetAttribute(round_main_kernel<ATOMIC, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(round_main_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
     configured_for = smem;
   }
-  round_main_kernel<ATOMIC, G><<<ctas, G * kGroupThreads, smem, stream>>>(p);
+  round_main_kernel<G><<<ctas, G * kGroupThreads, smem, stream>>>(p);
   return int(cudaGetLastError());
 }
 
 int launch_round_main(const RoundParams& p, int ctas, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (p.n_links < 1 || p.n_links > kMaxLinks) return int(cudaErrorInvalidValue);
-  // 4 groups of 128 threads (128 registers each) or 3 groups (168 registers each, no spills)
+  // 3 groups of 128 threads (168 registers each, the default: no spills) or 4 groups (128 registers each)
   static const int groups = [] {
     const char* e = getenv("SHAREDTENSOR_ROUND_GROUPS");
-    int g = e ? atoi(e) : 4;
-    return g == 3 ? 3 : 4;
+    int g = e ? atoi(e) : 3;
+    return g == 4 ? 4 : 3;
   }();
-  if (groups == 3) return p.atomic_values ? launch_main_t<true, 3>(p, ctas, stream) : launch_main_t<false, 3>(p, ctas, stream);
-  return p.atomic_values ? launch_main_t<true, 4>(p, ctas, stream) : launch_main_t<false, 4>(p, ctas, stream);
+  return groups == 3 ? launch_main_t<3>(p, ctas, stream) : launch_main_t<4>(p, ctas, stream);
 }
 
 }  // namespace st

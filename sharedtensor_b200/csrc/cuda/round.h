@@ -69,7 +69,6 @@ struct RoundParams {
   uint64_t* status;              // see StatusWord
   int32_t round;
   int32_t do_rx, do_tx;          // receiver-only / sender-only rounds
-  int32_t atomic_values;         // values are updated with red.add (a concurrent add kernel may run)
   int32_t frames_per_round;      // 1..3 successive 1-bit frames per link, tile and round
 };
 

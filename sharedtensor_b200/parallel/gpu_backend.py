@@ -22,7 +22,6 @@ def _gpu_config(cfg: Config):
     g.rel_bits = cfg.rel_bits
     g.comm_ctas = cfg.comm_ctas
     g.shareable = True
-    g.atomic_values = False
     g.rounds_in_flight = cfg.rounds_in_flight
     g.idle_sleep_us = cfg.idle_sleep_us
     g.frames_per_round = cfg.frames_per_round

@@ -25,13 +25,12 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _replica(cu, n, block=32, slots=4, shareable=True, atomic=False, rel_bits=22, frames=1):
+def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, frames=1):
     cfg = cu.GpuConfig()
     cfg.frames_per_round = frames
     cfg.block = block
     cfg.ring_slots = slots
     cfg.shareable = shareable
-    cfg.atomic_values = atomic
     cfg.rel_bits = rel_bits
     return cu.GpuReplica(0, n, cfg)
 
@@ -366,24 +365,6 @@ def test_mesh_group_no_forwarding(cu):
         torch.cuda.synchronize()
         rel = ((out - expect).norm() / expect.norm()).item()
         assert rel < 1e-5, rel
-
-
-def test_atomic_values_mode_matches_within_rounding(cu):
-    n = 4 * 4096
-    torch.manual_seed(2)
-    A, B = _replica(cu, n, atomic=True), _replica(cu, n, atomic=True)
-    connect_local(A, B)
-    init = torch.randn(n, device="cuda")
-    A.load_values(init.data_ptr(), _stream())
-    for _ in range(110):
-        A.round()
-        B.round()
-    A.sync()
-    B.sync()
-    out = torch.empty(n, device="cuda")
-    B.snapshot(out.data_ptr(), _stream())
-    torch.cuda.synchronize()
-    assert ((out - init).norm() / init.norm()).item() < 1e-5
 
 
 def test_engine_thread_free_running(cu):
