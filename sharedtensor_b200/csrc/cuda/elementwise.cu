@@ -107,22 +107,29 @@ __global__ void __launch_bounds__(kEwThreads) add_vec(float4* __restrict__ value
   int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * kEwThreads;
   for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
-  for (; i + stride < n4; i += 2 * stride) {
-    float4 d0 = ldg_stream(a + i), d1 = ldg_stream(a + i + stride);
+  // four independent 16-byte streams per thread and iteration
+  for (; i + 3 * stride < n4; i += 4 * stride) {
+    float4 d[4], v[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) d[u] = ldg_stream(a + i + u * stride);
     if (SUB) {
-      float4 o0 = ldg_stream(b + i), o1 = ldg_stream(b + i + stride);
-      d0.x -= o0.x; d0.y -= o0.y; d0.z -= o0.z; d0.w -= o0.w;
-      d1.x -= o1.x; d1.y -= o1.y; d1.z -= o1.z; d1.w -= o1.w;
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        float4 o = ldg_stream(b + i + u * stride);
+        d[u].x -= o.x; d[u].y -= o.y; d[u].z -= o.z; d[u].w -= o.w;
+      }
     }
     if (ATOMIC) {
-      red_add_v4(reinterpret_cast<float*>(values + i), d0);
-      red_add_v4(reinterpret_cast<float*>(values + i + stride), d1);
+#pragma unroll
+      for (int u = 0; u < 4; u++) red_add_v4(reinterpret_cast<float*>(values + i + u * stride), d[u]);
     } else {
-      float4 v0 = values[i], v1 = values[i + stride];
-      v0.x += d0.x; v0.y += d0.y; v0.z += d0.z; v0.w += d0.w;
-      v1.x += d1.x; v1.y += d1.y; v1.z += d1.z; v1.w += d1.w;
-      values[i] = v0;
-      values[i + stride] = v1;
+#pragma unroll
+      for (int u = 0; u < 4; u++) v[u] = values[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        v[u].x += d[u].x; v[u].y += d[u].y; v[u].z += d[u].z; v[u].w += d[u].w;
+        values[i + u * stride] = v[u];
+      }
     }
   }
   for (; i < n4; i += stride) {
@@ -162,7 +169,7 @@ static int launch_add_t(float* values, const float* a, const float* b, int64_t n
   bool al = aligned16(values) && aligned16(a) && (!SUB || aligned16(b));
   int64_t n4 = al ? n / 4 : 0;
   if (n4) {
-    int blocks = ew_blocks(n4 / 2 + 1);
+    int blocks = ew_blocks(n4 / 4 + 1);
     if (atomic)
       add_vec<SUB, true><<<blocks, kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), reinterpret_cast<const float4*>(a),
                                                        reinterpret_cast<const float4*>(b), n4, tile_state, n_tiles);

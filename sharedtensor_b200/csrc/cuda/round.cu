@@ -223,14 +223,15 @@ __device__ __forceinline__ void group_bar(int group) {
 constexpr uint32_t kFlagChanged = 1, kFlagFailed = 2, kFlagNonsilent0 = 4;  // nonsilent: one bit per pass, 4 << f
 constexpr int kMaxFrames = 3;       // 1-bit frames per link, tile and round
 
+// frame words and scale bytes were written by a neighbour GPU: read them from L2, never from this SM's L1
 __device__ __forceinline__ uint32_t ld_u32_ca(const void* p) {
   uint32_t v;
-  asm volatile("ld.global.ca.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
 __device__ __forceinline__ uint32_t ld_u8_ca(const void* p) {
   uint32_t v;
-  asm volatile("ld.global.ca.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
 
