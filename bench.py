@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--probes", type=int, default=24, help="single-update latency probes after the timed region")
     ap.add_argument("--topology", default="tree", choices=["tree", "mesh"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the comparison run on the other topology")
     ap.add_argument("--ref-time-cap", type=float, default=120.0, help="wall-clock cap of the reference arm's wait, seconds")
     return ap.parse_args()
 
@@ -183,127 +184,142 @@ def run_ours(args) -> dict | None:
         h.copy_(pool[i % POOL])
     staging = torch.empty(n, device=dev)
 
-    # ---- the tree: ranks join one after the other so that the shape is the reference's (left, right, redirect ...)
-    port = int(os.environ.get("MASTER_PORT", "29500")) + 17
-    st = None
-    if args.topology == "mesh":
-        st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev), topology="mesh",
-                                        group_rank=rank, group_size=world)
-        barrier()
-    else:
-        for r in range(world):
-            if r == rank:
-                st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev))
+    def measure(topology: str, with_e2e: bool, port: int) -> dict:
+        nonlocal expect_s
+        expect_s = init[::SAMPLE_STRIDE].clone()
+        # ---- the tree: ranks join one after the other so that the shape is the reference's (left, right, redirect ...)
+        st = None
+        if topology == "mesh":
+            st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev), topology="mesh",
+                                            group_rank=rank, group_size=world)
             barrier()
-    assert st is not None
-    del init
-    rep = st._b.rep
-    err_buf = torch.zeros(2, dtype=torch.float64, device=dev)
-    err_host = torch.zeros(2, dtype=torch.float64).pin_memory()
-    extra_launches = 0
+        else:
+            for r in range(world):
+                if r == rank:
+                    st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.empty(n, device=dev))
+                barrier()
+        assert st is not None
+        rep = st._b.rep
+        err_buf = torch.zeros(2, dtype=torch.float64, device=dev)
+        err_host = torch.zeros(2, dtype=torch.float64).pin_memory()
+        extra_launches = 0
 
-    def sampled_err2() -> float:
-        nonlocal extra_launches
-        err_buf.zero_()
-        cu.sample_sqerr(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, err_buf.data_ptr(), stream)
-        err_host.copy_(err_buf, non_blocking=True)
-        torch.cuda.synchronize()
-        extra_launches += 2
-        return float(err_host[0])
+        def sampled_err2() -> float:
+            nonlocal extra_launches
+            err_buf.zero_()
+            cu.sample_sqerr(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, err_buf.data_ptr(), stream)
+            err_host.copy_(err_buf, non_blocking=True)
+            torch.cuda.synchronize()
+            extra_launches += 2
+            return float(err_host[0])
 
-    def add_expected(r: int, p: int, times: int = 1):
-        expect_s.add_(pool_s[(r, p)], alpha=float(times))
+        def add_expected(r: int, p: int, times: int = 1):
+            expect_s.add_(pool_s[(r, p)], alpha=float(times))
 
-    def cadence_ns() -> int:
-        u = float(torch.rand(1, generator=rng_cad))
-        return int((CADENCE_MS[0] + u * (CADENCE_MS[1] - CADENCE_MS[0])) * 1e6)
+        def cadence_ns() -> int:
+            u = float(torch.rand(1, generator=rng_cad))
+            return int((CADENCE_MS[0] + u * (CADENCE_MS[1] - CADENCE_MS[0])) * 1e6)
 
-    def run_steps(k0: int, steps: int, e2e: bool, pool_mod: int = POOL) -> tuple[float, float, int]:
-        """Issues `steps` updates on this rank (all ranks do the same), waits until the replica holds everybody's;
-        returns (seconds to local convergence, final relative error, bytes read back)."""
-        nonlocal extra_launches
-        # what everybody is about to add
-        upd2 = 0.0
-        total = torch.zeros_like(expect_s)
-        for r in range(world):
+        def run_steps(k0: int, steps: int, e2e: bool, pool_mod: int = POOL) -> tuple[float, float, int]:
+            """Issues `steps` updates on this rank (all ranks do the same), waits until the replica holds everybody's;
+            returns (seconds to local convergence, final relative error, bytes read back)."""
+            nonlocal extra_launches
+            # what everybody is about to add
+            upd2 = 0.0
+            total = torch.zeros_like(expect_s)
+            for r in range(world):
+                for j in range(steps):
+                    total.add_(pool_s[(r, (k0 + j) % pool_mod)])
+            expect_s.add_(total)
+            upd2 = float((total.double() ** 2).sum())
+            del total
+            d2h = 0
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
             for j in range(steps):
-                total.add_(pool_s[(r, (k0 + j) % pool_mod)])
-        expect_s.add_(total)
-        upd2 = float((total.double() ** 2).sum())
-        del total
-        d2h = 0
+                p = (k0 + j) % pool_mod
+                cu.delay(cadence_ns(), stream)
+                extra_launches += 1
+                if e2e:
+                    staging.copy_(pinned[p], non_blocking=True)   # this step's input: pinned host -> device
+                    st.addFromTensor(staging)
+                    err_buf.zero_()
+                    cu.sample_sqerr(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, err_buf.data_ptr(), stream)
+                    err_host.copy_(err_buf, non_blocking=True)                   # this step's result: device -> host
+                    torch.cuda.synchronize()
+                    extra_launches += 2
+                    d2h += 16
+                else:
+                    st.addFromTensor(pool[p])
+            deadline = time.time() + 60.0
+            rel = float("inf")
+            while time.time() < deadline:
+                e2 = sampled_err2()
+                rel = (e2 / upd2) ** 0.5 if upd2 > 0 else 0.0
+                if rel <= TOL:
+                    break
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / 1e3, rel, d2h
+
+        # ---- warm-up (untimed), timed region, end-to-end region
+        if args.warmup:
+            run_steps(0, args.warmup, False)
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for j in range(steps):
-            p = (k0 + j) % pool_mod
-            cu.delay(cadence_ns(), stream)
-            extra_launches += 1
-            if e2e:
-                staging.copy_(pinned[p], non_blocking=True)   # this step's input: pinned host -> device
-                st.addFromTensor(staging)
-                err_buf.zero_()
-                cu.sample_sqerr(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, err_buf.data_ptr(), stream)
-                err_host.copy_(err_buf, non_blocking=True)                   # this step's result: device -> host
-                torch.cuda.synchronize()
-                extra_launches += 2
-                d2h += 16
-            else:
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        l0 = rep.launches()
+        x0 = extra_launches
+        secs, rel, _ = run_steps(args.warmup, args.steps, False)
+        launches = int(allsum(float(rep.launches() - l0 + extra_launches - x0)))
+        secs = allmax(secs)
+        rel = allmax(rel)
+        clocks = sampler.stop() if rank == 0 else {}
+        e2e = None
+        if with_e2e:
+            k_e2e = max(3, min(args.steps, 10))
+            if pinned:
+                for i, h in enumerate(pinned):
+                    h.copy_(pool[i % POOL])
+            s2, rel2, d2h = run_steps(args.warmup + args.steps, k_e2e, True, pool_mod=len(pinned))
+            s2 = allmax(s2)
+            e2e = {"value": world * k_e2e / s2, "unit": "updates/s", "steps": k_e2e, "h2d_bytes_per_step": 4 * n,
+                   "d2h_bytes_per_step": d2h // k_e2e, "final_rel_err": allmax(rel2)}
+
+        # ---- single-update convergence latency: one rank adds, everybody measures until its replica has it
+        lat = []
+        for i in range(args.probes if world > 1 else 0):
+            origin, p = i % world, i % POOL
+            add_expected(origin, p)
+            upd2 = float((pool_s[(origin, p)].double() ** 2).sum())
+            barrier()
+            t0 = time.perf_counter()
+            if rank == origin:
                 st.addFromTensor(pool[p])
-        deadline = time.time() + 60.0
-        rel = float("inf")
-        while time.time() < deadline:
-            e2 = sampled_err2()
-            rel = (e2 / upd2) ** 0.5 if upd2 > 0 else 0.0
-            if rel <= TOL:
-                break
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / 1e3, rel, d2h
-
-    # ---- warm-up (untimed), timed region, end-to-end region
-    if args.warmup:
-        run_steps(0, args.warmup, False)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    l0 = rep.launches()
-    x0 = extra_launches
-    secs, rel, _ = run_steps(args.warmup, args.steps, False)
-    launches = int(allsum(float(rep.launches() - l0 + extra_launches - x0)))
-    secs = allmax(secs)
-    rel = allmax(rel)
-    clocks = sampler.stop() if rank == 0 else {}
-    e2e = None
-    if not args.no_e2e:
-        k_e2e = max(3, min(args.steps, 10))
-        if pinned:
-            for i, h in enumerate(pinned):
-                h.copy_(pool[i % POOL])
-        s2, rel2, d2h = run_steps(args.warmup + args.steps, k_e2e, True, pool_mod=len(pinned))
-        s2 = allmax(s2)
-        e2e = {"value": world * k_e2e / s2, "unit": "updates/s", "steps": k_e2e, "h2d_bytes_per_step": 4 * n,
-               "d2h_bytes_per_step": d2h // k_e2e, "final_rel_err": allmax(rel2)}
-
-    # ---- single-update convergence latency: one rank adds, everybody measures until its replica has it
-    lat = []
-    for i in range(args.probes if world > 1 else 0):
-        origin, p = i % world, i % POOL
-        add_expected(origin, p)
-        upd2 = float((pool_s[(origin, p)].double() ** 2).sum())
+            while True:
+                e2 = sampled_err2()
+                if (e2 / upd2) ** 0.5 <= TOL or time.perf_counter() - t0 > 5.0:
+                    break
+            lat.append(allmax(time.perf_counter() - t0))
+        stats = st.stats()
         barrier()
-        t0 = time.perf_counter()
-        if rank == origin:
-            st.addFromTensor(pool[p])
-        while True:
-            e2 = sampled_err2()
-            if (e2 / upd2) ** 0.5 <= TOL or time.perf_counter() - t0 > 5.0:
-                break
-        lat.append(allmax(time.perf_counter() - t0))
-    stats = st.stats()
-    barrier()
-    st.close()
+        st.close()
+        barrier()
+        return {"secs": secs, "rel": rel, "launches": launches, "clocks": clocks, "e2e": e2e, "lat": lat, "stats": stats}
+    base_port = int(os.environ.get("MASTER_PORT", "29500")) + 17
+    main = measure(args.topology, not args.no_e2e, base_port)
+    # the other topology of the same GPUs, for comparison (a mesh group is one hop wide, a tree up to five)
+    other = None
+    if world > 1 and not args.no_extra:
+        other_name = "mesh" if args.topology == "tree" else "tree"
+        o = measure(other_name, False, base_port + 40)
+        ol = sorted(x * 1e3 for x in o["lat"])
+        other = {"topology": other_name, "value": world * args.steps / o["secs"], "ms_per_step": o["secs"] * 1e3 / args.steps,
+                 "final_rel_err": o["rel"], "latency_ms": {"p50": ol[len(ol) // 2] if ol else None,
+                                                           "p99": ol[min(len(ol) - 1, int(0.99 * len(ol)))] if ol else None}}
+    secs, rel, launches, clocks, e2e, lat, stats = (main[k] for k in ("secs", "rel", "launches", "clocks", "e2e", "lat", "stats"))
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -326,6 +342,8 @@ def run_ours(args) -> dict | None:
     }
     if e2e:
         out["e2e"] = e2e
+    if other:
+        out["other_topology"] = other
     return out
 
 

@@ -43,7 +43,9 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     cu = _native.cuda()
-    dist.init_process_group("gloo")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
     nccl = dist.new_group(backend="nccl") if world > 1 else None
     stream = torch.cuda.current_stream().cuda_stream
     base_port = int(os.environ.get("MASTER_PORT", "29500")) + 100

@@ -42,7 +42,9 @@ def main():
     rank, local, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("gloo")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
     nccl = dist.new_group(backend="nccl") if (world > 1 and args.mode == "sync") else None
     torch.manual_seed(0)  # every rank builds the same initial model
     if args.model == "char_rnn":
@@ -68,17 +70,7 @@ def main():
         trainer = AsyncTrainer(model, shared, lr=lr, param_dtype=dtype)
         del probe
     else:
-        class _Sync(SyncTrainer):
-            def push(self_inner):
-                if self_inner.world > 1:
-                    dist.all_reduce(self_inner.gflat, group=nccl)
-                if self_inner.master is not None:
-                    self_inner.master.add_(self_inner.gflat.float(), alpha=-self_inner.lr / self_inner.world)
-                    self_inner.flat.copy_(self_inner.master)
-                else:
-                    self_inner.flat.add_(self_inner.gflat, alpha=-self_inner.lr / self_inner.world)
-
-        trainer = _Sync(model, lr=lr, param_dtype=dtype)
+        trainer = SyncTrainer(model, lr=lr, param_dtype=dtype, group=nccl)
     trainer.run(batches, steps=args.warmup, log_every=1000)
     trainer.log = type(trainer.log)()
     torch.cuda.synchronize()

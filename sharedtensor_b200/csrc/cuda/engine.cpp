@@ -126,6 +126,7 @@ GpuReplica::~GpuReplica() {
   cudaFree(worklist_);
   cudaFree(work_count_);
   cudaFree(status_);
+  if (graph_exec_) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
   if (status_host_) cudaFreeHost(status_host_);
   if (tcp_words_dev_) cudaFree(tcp_words_dev_);
   if (tcp_stat_dev_) cudaFree(tcp_stat_dev_);
@@ -258,6 +259,11 @@ void GpuReplica::publish_pending() {
 }
 
 void GpuReplica::rebuild_params() {
+  if (graph_exec_) {
+    cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
+    graph_exec_ = nullptr;
+  }
+  graph_warm_ = false;
   int dense = 0;
   for (int i = 0; i < kMaxLinks; i++) {
     map_link_[i] = -1;
@@ -501,13 +507,50 @@ void GpuReplica::engine_loop() {
     try {
       std::lock_guard<std::mutex> lk(mu_);
       if (params_.n_in + params_.n_out > 0) {
-        params_.round = round_no_++;
         params_.do_rx = 1;
         params_.do_tx = 1;
-        check(launch_round_begin(params_, comm_), "round_begin kernel");
-        check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
-        check(launch_round_publish(params_, comm_), "round_publish kernel");
-        launches_ += 3;
+        bool by_graph = false;
+        if (cfg_.use_graph && graph_warm_ && (round_no_ & 1) == 0) {
+          // Two rounds (even and odd parity) replayed as one CUDA graph: one launch instead of six, which is what
+          // bounds the round rate of small tensors.  The graph is rebuilt whenever the ring set changes.
+          if (!graph_exec_) {
+            cudaGraph_t graph = nullptr;
+            cudaError_t ce = cudaStreamBeginCapture(S(comm_), cudaStreamCaptureModeThreadLocal);
+            if (ce == cudaSuccess) {
+              for (int rr = 0; rr < 2; rr++) {
+                params_.round = rr;
+                launch_round_begin(params_, comm_);
+                launch_round_main(params_, ctas_, comm_);
+                launch_round_publish(params_, comm_);
+              }
+              ce = cudaStreamEndCapture(S(comm_), &graph);
+            }
+            if (ce == cudaSuccess && graph) {
+              cudaGraphExec_t exec = nullptr;
+              ce = cudaGraphInstantiate(&exec, graph, 0);
+              cudaGraphDestroy(graph);
+              if (ce == cudaSuccess) graph_exec_ = exec;
+            }
+            if (!graph_exec_) {
+              cudaGetLastError();
+              cfg_.use_graph = false;  // capture is not available here: plain launches from now on
+            }
+          }
+          if (graph_exec_) {
+            check(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec_), S(comm_)), "cudaGraphLaunch");
+            round_no_ += 2;
+            launches_ += 6;
+            by_graph = true;
+          }
+        }
+        if (!by_graph) {
+          params_.round = round_no_++;
+          check(launch_round_begin(params_, comm_), "round_begin kernel");
+          check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
+          check(launch_round_publish(params_, comm_), "round_publish kernel");
+          launches_ += 3;
+          graph_warm_ = true;  // the kernels' attributes are set: later rounds may be captured
+        }
         // the work count of this round tells the thread whether anything is moving
         cudaMemcpyAsync(status_host_ + kStLastWorkCount, status_ + kStLastWorkCount, 8, cudaMemcpyDeviceToHost, S(comm_));
         cudaEventRecord(E(ev_round_[r % depth]), S(comm_));

@@ -30,6 +30,7 @@ struct GpuConfig {
   int rounds_in_flight = 2;
   int idle_sleep_us = 200;
   int frames_per_round = 1;  // successive 1-bit frames per link and round (1..3)
+  bool use_graph = true;     // the engine thread replays pairs of rounds as a CUDA graph
 };
 
 struct EdgeBlockLayout {
@@ -139,6 +140,8 @@ class GpuReplica {
   RoundParams params_{};
   int map_link_[kMaxLinks] = {0, 0, 0};  // dense link index of each link id
   int round_no_ = 0;
+  void* graph_exec_ = nullptr;         // cudaGraphExec_t: two rounds (even, odd parity) of the current ring set
+  bool graph_warm_ = false;            // one plain round has run since the ring set last changed
   int ctas_ = 148;
   void* comm_ = nullptr;               // cudaStream_t
   void* ev_user_ = nullptr;            // cudaEvent_t: user stream -> comm

@@ -25,6 +25,7 @@ def _gpu_config(cfg: Config):
     g.rounds_in_flight = cfg.rounds_in_flight
     g.idle_sleep_us = cfg.idle_sleep_us
     g.frames_per_round = cfg.frames_per_round
+    g.use_graph = cfg.use_graph
     return g
 
 

@@ -122,12 +122,13 @@ class AsyncTrainer(_Base):
 class SyncTrainer(_Base):
     """Synchronous data parallelism: gradients are averaged over the process group every step (NCCL on GPUs)."""
 
-    def __init__(self, model, lr: float, param_dtype: torch.dtype = torch.float32, align: int = 32):
+    def __init__(self, model, lr: float, param_dtype: torch.dtype = torch.float32, align: int = 32, group=None):
         super().__init__(model, lr, align=align, param_dtype=param_dtype)
         self.master = self.flat.float().clone() if param_dtype != torch.float32 else None
-        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         if self.world > 1:  # every rank starts from rank 0's weights
-            dist.broadcast(self.flat, 0)
+            dist.broadcast(self.flat, 0, group=group)
             if self.master is not None:
                 self.master.copy_(self.flat)
 
@@ -136,7 +137,7 @@ class SyncTrainer(_Base):
 
     def push(self) -> None:
         if self.world > 1:
-            dist.all_reduce(self.gflat)
+            dist.all_reduce(self.gflat, group=self.group)
         if self.master is not None:
             self.master.add_(self.gflat.float(), alpha=-self.lr / self.world)
             self.flat.copy_(self.master)

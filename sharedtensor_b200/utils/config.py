@@ -37,6 +37,7 @@ class Config:
     comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
     rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
     idle_sleep_us: int = 200         # engine pause when a round moved nothing
+    use_graph: bool = True           # engine thread replays pairs of rounds as one CUDA graph
     poll_deadline_us: int = 1000     # upper bound of every device-side wait
     use_multimem: bool = False       # NVLS store fan-out for mesh groups when the host exposes it
     # --- TCP edges ------------------------------------------------------------------------------
