@@ -37,6 +37,8 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--lr", type=float, default=None)
+    ap.add_argument("--comm-ctas", type=int, default=32, help="SMs the sync rounds may use (async mode)")
+    ap.add_argument("--round-interval-us", type=int, default=500, help="pause between sync rounds (async mode)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, local, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -64,7 +66,8 @@ def main():
         port = int(os.environ.get("MASTER_PORT", "29500")) + 31
         for r in range(world):
             if r == rank:
-                shared = sharedtensor.createOrFetch("127.0.0.1", port, probe if rank == 0 else torch.empty_like(probe))
+                shared = sharedtensor.createOrFetch("127.0.0.1", port, probe if rank == 0 else torch.empty_like(probe),
+                                                     comm_ctas=args.comm_ctas, round_interval_us=args.round_interval_us)
             torch.cuda.synchronize()
             dist.barrier()
         trainer = AsyncTrainer(model, shared, lr=lr, param_dtype=dtype)

@@ -87,6 +87,7 @@ PYBIND11_MODULE(_cuda, m) {
       .def_readwrite("shareable", &GpuConfig::shareable)
       .def_readwrite("rounds_in_flight", &GpuConfig::rounds_in_flight)
       .def_readwrite("idle_sleep_us", &GpuConfig::idle_sleep_us)
+      .def_readwrite("round_interval_us", &GpuConfig::round_interval_us)
       .def_readwrite("frames_per_round", &GpuConfig::frames_per_round)
       .def_readwrite("use_graph", &GpuConfig::use_graph);
 

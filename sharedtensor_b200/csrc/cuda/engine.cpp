@@ -37,7 +37,8 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   if (n <= 0) throw std::invalid_argument("shared tensor needs at least one element");
   if (cfg.block < 32 || cfg.block > 4096 || (cfg.block & (cfg.block - 1)))
     throw std::invalid_argument("block must be a power of two in 32..4096");
-  if (cfg.ring_slots < 2 || cfg.ring_slots > 64) throw std::invalid_argument("ring_slots must be in 2..64");
+  if (cfg.ring_slots < 2 || cfg.ring_slots > 64 || (cfg.ring_slots & (cfg.ring_slots - 1)))
+    throw std::invalid_argument("ring_slots must be a power of two in 2..64");
   DeviceGuard g(device_);
   n_tiles_ = int((n + kTile - 1) / kTile);
   n_padded_ = int64_t(n_tiles_) * kTile;
@@ -567,10 +568,19 @@ void GpuReplica::engine_loop() {
     if (r >= depth) cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
     if (status_host_[kStLastWorkCount] != 0) epoch_++;
     if (status_host_[kStLastWorkCount] == 0) {
+      // nothing moved: back off from 10 us up to idle_sleep_us, so that a fresh update is picked up quickly after a
+      // burst and an idle replica costs next to nothing
       idle_rounds++;
-      if (idle_rounds > 2 && cfg_.idle_sleep_us > 0) ::usleep(useconds_t(cfg_.idle_sleep_us));
+      if (idle_rounds > 2 && cfg_.idle_sleep_us > 0) {
+        uint64_t shift = idle_rounds - 3 > 6 ? 6 : idle_rounds - 3;
+        uint64_t us = 10ull << shift;
+        if (us > uint64_t(cfg_.idle_sleep_us)) us = uint64_t(cfg_.idle_sleep_us);
+        ::usleep(useconds_t(us));
+      }
     } else {
       idle_rounds = 0;
+      // pacing: a training job can cap how often rounds run, leaving the GPU to its own kernels in between
+      if (cfg_.round_interval_us > 0) ::usleep(useconds_t(cfg_.round_interval_us));
     }
   }
   cudaStreamSynchronize(S(comm_));

@@ -28,7 +28,8 @@ struct GpuConfig {
   int comm_ctas = 0;         // 0 = one CTA per SM
   bool shareable = true;     // allocate edge blocks and values with the VMM API (needed across processes)
   int rounds_in_flight = 2;
-  int idle_sleep_us = 200;
+  int idle_sleep_us = 200;   // longest pause of the engine thread between rounds while nothing moves
+  int round_interval_us = 0; // pause after every busy round (0 = run rounds back to back)
   int frames_per_round = 1;  // successive 1-bit frames per link and round (1..3)
   bool use_graph = true;     // the engine thread replays pairs of rounds as a CUDA graph
 };

@@ -448,7 +448,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
         if (!rx_any || a == 0) return nullptr;
         while (true) {
           if (it_r >= 0 && it_f < it_avail) {
-            const int slot_no = (int(it_ib & 63u) + it_f) % p.ring_slots;
+            const int slot_no = (int(it_ib & 63u) + it_f) & (p.ring_slots - 1);  // ring_slots is a power of two
             it_f++;
             return p.in[it_r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
           }
@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
             const uint8_t* ob = outbuf + size_t((c & 1) * kMaxFrames + f) * pb_pad;
             for (int r = 0; r < p.n_out; r++) {
               if (p.out[r].link != l) continue;
-              const int slot_no = (int(out_byte(r) & 63u) + sent_here) % p.ring_slots;
+              const int slot_no = (int(out_byte(r) & 63u) + sent_here) & (p.ring_slots - 1);
               bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + tile) * pb, ob, uint32_t(pb));
               n_tx++;
             }

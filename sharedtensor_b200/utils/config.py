@@ -36,7 +36,8 @@ class Config:
     engine: str = "thread"           # thread: free-running rounds on a comm stream | manual: caller drives step()
     comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
     rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
-    idle_sleep_us: int = 200         # engine pause when a round moved nothing
+    idle_sleep_us: int = 200         # longest engine pause while nothing moves (backs off from 10 us)
+    round_interval_us: int = 0       # pause after every busy round: caps the round rate (a rate limit for GPU edges)
     use_graph: bool = True           # engine thread replays pairs of rounds as one CUDA graph
     poll_deadline_us: int = 1000     # upper bound of every device-side wait
     use_multimem: bool = False       # NVLS store fan-out for mesh groups when the host exposes it
@@ -86,8 +87,8 @@ class Config:
             raise ValueError(f"engine must be thread or manual, got {self.engine!r}")
         if self.ready_mode not in ("first_frame", "converged"):
             raise ValueError(f"ready_mode must be first_frame or converged, got {self.ready_mode!r}")
-        if not 2 <= self.ring_slots <= 64:
-            raise ValueError("ring_slots must be in 2..64")
+        if not 2 <= self.ring_slots <= 64 or self.ring_slots & (self.ring_slots - 1):
+            raise ValueError("ring_slots must be a power of two in 2..64")
         if self.rel_bits < 1 or self.rel_bits > 60:
             raise ValueError("rel_bits must be in 1..60")
         if not 1 <= self.frames_per_round <= 3:
