@@ -94,6 +94,11 @@ class SharedTensor:
         s["config"] = self.cfg.asdict()
         return s
 
+    def trace(self) -> list:
+        """Per-round records kept on the device (GPU replicas): when each of the last 64 rounds ended on the GPU's
+        clock, how many tiles it had to look at and how many frames had been sent by then."""
+        return self._b.trace() if hasattr(self._b, "trace") else []
+
     def state_dict(self) -> dict:
         """Values plus per-edge mirrors, as CPU tensors (see ``utils.checkpoint``)."""
         return self._b.state_dict()

@@ -31,6 +31,8 @@ PYBIND11_MODULE(_cuda, m) {
   m.attr("MAX_LINKS") = kMaxLinks;
   m.attr("MAX_RINGS") = kMaxRings;
   m.attr("STATUS_WORDS") = int(kStWords);
+  m.attr("TRACE_ENTRIES") = int(kTraceEntries);
+  m.attr("TRACE_WORDS") = int(kTraceWords);
   m.def("status_names", [] {
     return std::vector<std::string>{"rounds", "tiles_processed", "frames_sent", "frames_recv", "blocked_no_credit", "errors",
                                     "last_work_count", "residual_max0", "residual_max1", "residual_max2", "pending_tiles",

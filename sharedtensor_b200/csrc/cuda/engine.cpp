@@ -63,14 +63,14 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   check(cudaMalloc(reinterpret_cast<void**>(&tile_state_), size_t(n_tiles_)), "cudaMalloc tile_state");
   check(cudaMalloc(reinterpret_cast<void**>(&worklist_), size_t(n_tiles_) * 4), "cudaMalloc worklist");
   check(cudaMalloc(reinterpret_cast<void**>(&work_count_), 2 * 4), "cudaMalloc work_count");
-  check(cudaMalloc(reinterpret_cast<void**>(&status_), kStWords * 8), "cudaMalloc status");
-  check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), kStWords * 8), "cudaMallocHost status");
+  check(cudaMalloc(reinterpret_cast<void**>(&status_), kStTotalWords * 8), "cudaMalloc status");
+  check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), kStTotalWords * 8), "cudaMallocHost status");
   check(cudaMemset(ctrl_, 0, size_t(n_tiles_) * 16), "memset");
   check(cudaMemset(sent_, 0, size_t(n_tiles_) * 8), "memset");
   check(cudaMemset(tile_state_, 1, size_t(n_tiles_)), "memset");
   check(cudaMemset(work_count_, 0, 8), "memset");
-  check(cudaMemset(status_, 0, kStWords * 8), "memset");
-  std::memset(status_host_, 0, kStWords * 8);
+  check(cudaMemset(status_, 0, kStTotalWords * 8), "memset");
+  std::memset(status_host_, 0, kStTotalWords * 8);
 
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
@@ -467,10 +467,10 @@ void GpuReplica::sync() {
 std::vector<uint64_t> GpuReplica::status() {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> lk(mu_);
-  std::vector<uint64_t> out(kStWords);
-  check(cudaMemcpyAsync(status_host_, status_, kStWords * 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
+  std::vector<uint64_t> out(kStTotalWords);
+  check(cudaMemcpyAsync(status_host_, status_, kStTotalWords * 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
   check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
-  std::memcpy(out.data(), status_host_, kStWords * 8);
+  std::memcpy(out.data(), status_host_, kStTotalWords * 8);
   return out;
 }
 

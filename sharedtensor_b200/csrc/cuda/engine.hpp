@@ -89,7 +89,7 @@ class GpuReplica {
   bool engine_running() const { return engine_on_.load(); }
 
   // ---- observation ----
-  std::vector<uint64_t> status();      // StatusWord order; synchronises the comm stream
+  std::vector<uint64_t> status();      // StatusWord order, then the trace ring; synchronises the comm stream
   uint64_t launches() const { return launches_.load(); }
   uint64_t change_epoch() const { return epoch_.load(); }  // bumped whenever values may have changed
   std::string last_error() const;

@@ -664,8 +664,13 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
     if (n_blocked) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStBlockedNoCredit), (unsigned long long)n_blocked);
     if (n_pending) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStPendingTiles), (unsigned long long)n_pending);
     if (blockIdx.x == 0 && g == 0) {
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStRounds), 1ull);
+      const unsigned long long r = atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStRounds), 1ull);
       p.status[kStLastWorkCount] = uint64_t(count);
+      uint64_t* rec = p.status + kStWords + (r % kTraceEntries) * kTraceWords;  // trace ring, read by stats()
+      rec[0] = globaltimer_ns();
+      rec[1] = r;
+      rec[2] = uint64_t(count);
+      rec[3] = p.status[kStFramesSent];
     }
   }
 }

@@ -86,7 +86,11 @@ enum StatusWord : int {
   kStResidualMax2,
   kStPendingTiles,    // tiles still marked pending after the last round
   kStWaitTimeouts,
-  kStWords = 16
+  kStWords = 16,
+  // after the counters: a ring of kTraceEntries records {globaltimer ns, round, listed tiles, frames sent so far}
+  kTraceEntries = 64,
+  kTraceWords = 4,
+  kStTotalWords = kStWords + kTraceEntries * kTraceWords
 };
 constexpr uint64_t kErrBarrierTimeout = 1, kErrBadCtrl = 2;
 

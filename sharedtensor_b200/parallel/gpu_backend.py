@@ -101,6 +101,15 @@ class GpuBackend:
         s["backend"] = "gpu/p2p"
         return s
 
+    def trace(self) -> list[dict]:
+        """The last rounds as recorded on the device: GPU clock (ns), round number, tiles listed, frames sent so far."""
+        cu = _native.cuda()
+        st = self.rep.status()
+        base, ne, nw = cu.STATUS_WORDS, cu.TRACE_ENTRIES, cu.TRACE_WORDS
+        recs = [st[base + i * nw: base + (i + 1) * nw] for i in range(ne)]
+        recs = [{"gpu_time_ns": r[0], "round": r[1], "tiles": r[2], "frames_sent": r[3]} for r in recs if r[0]]
+        return sorted(recs, key=lambda r: r["round"])
+
     def is_master(self) -> bool:
         return self.node.is_master()
 

@@ -404,6 +404,23 @@ def test_engine_thread_free_running(cu):
     assert ok and ok2
 
 
+def test_trace_ring_records_rounds(cu):
+    n = 2 * 4096
+    A, B = _replica(cu, n), _replica(cu, n)
+    connect_local(A, B)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    for _ in range(5):
+        A.round()
+        B.round()
+    st = A.status()
+    assert len(st) == cu.STATUS_WORDS + cu.TRACE_ENTRIES * cu.TRACE_WORDS
+    recs = [st[cu.STATUS_WORDS + i * cu.TRACE_WORDS: cu.STATUS_WORDS + (i + 1) * cu.TRACE_WORDS] for i in range(5)]
+    assert [r[1] for r in recs] == [0, 1, 2, 3, 4], "round numbers"
+    assert all(r[0] > 0 for r in recs) and recs[4][0] > recs[0][0], "GPU clock stamps increase"
+    assert recs[0][2] == A.tiles()
+
+
 def test_vmm_blocks_when_available(cu):
     rep = _replica(cu, 4096, shareable=True)
     b = rep.alloc_edge_block()
