@@ -1,6 +1,6 @@
 // Sync-round kernels for sm_100a: round_begin, round_main and round_publish (see round.h for the protocol).
 //
-// round_main is the fused hot path.  A CTA is four independent groups of 128 threads; a group works
+// round_main is the fused hot path.  A CTA is three independent groups of 128 threads; a group works
 // through its share of the listed tiles, one 16 KB array-tile (values, then each link's mirror) at a time:
 //   1. array-tiles are staged into shared memory with 1-D TMA bulk copies (cp.async.bulk, completion on an
 //      mbarrier, a three-slot ring per group so the next copy is in flight while this one is computed;
@@ -12,8 +12,7 @@
 //   3. per link it forms the residual values - mirror, the block's sum of squares, the exponent code from
 //      the float's exponent bits, its 32 sign bits as one word, and steps the mirror by -/+ 2^k
 //                                                         (reference 156-174);
-//   4. changed mirror tiles go back to global memory with TMA bulk stores, changed values with one 128-byte
-//      line per thread, and the packed words + scale bytes go straight into the neighbours' ring slots with
+//   4. changed mirror tiles and the tile's values go back to global memory with TMA bulk stores, and the packed words + scale bytes go straight into the neighbours' ring slots with
 //      TMA bulk stores over NVLink
 //      (reference 176-177: two socket writes).
 // Nothing in here waits for another GPU.  The only waits are on this CTA's own TMA copies, and they are
@@ -24,7 +23,6 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
-#include <cstdlib>
 
 #include "round.h"
 
@@ -32,9 +30,9 @@ namespace st {
 
 namespace {
 
-constexpr int kMaxGroups = 4;       // independent 128-thread groups per CTA (3 or 4, chosen at launch)
+
 constexpr int kGroupThreads = 128;  // one thread per 32 consecutive elements of a tile
-constexpr int kSlots = 3;           // array-tile slots per group
+__host__ __device__ constexpr int slots_for(int) { return 3; }  // array-tile slots per group
 constexpr int kTileBytes = kTile * 4;
 
 // ----------------------------------------------------------------------------------------------
@@ -320,6 +318,7 @@ __device__ __forceinline__ uint32_t sign_word_and_step(const float4 (&v)[8], flo
 
 struct GroupSmem {
   int off_slots;    // [kGroups][kSlots][kTileBytes]
+  int off_vstage;   // [kGroups][kTileBytes]   values of the tile on their way back to global memory
   int off_out;      // [kGroups][2][3 frames][payload_bytes]
   int off_bar;      // uint64_t[kGroups][kSlots]
   int off_red;      // float[kGroups][2][4]   cross-warp partials for blocks of 2048/4096
@@ -330,7 +329,10 @@ __host__ __device__ inline GroupSmem group_layout(int payload_bytes, int kGroups
   GroupSmem m;
   int off = 0;
   m.off_slots = off;
+  const int kSlots = slots_for(kGroups);
   off += kGroups * kSlots * kTileBytes;
+  m.off_vstage = off;
+  off += kGroups * kTileBytes;
   m.off_out = off;
   off += kGroups * 2 * 3 * ((payload_bytes + 127) & ~127);
   m.off_bar = off;
@@ -346,13 +348,14 @@ __host__ __device__ inline GroupSmem group_layout(int payload_bytes, int kGroups
 }  // namespace
 
 int round_main_smem_bytes(int, int, int payload_bytes, int* stages_out) {
-  if (stages_out) *stages_out = kSlots;
-  return group_layout(payload_bytes, kMaxGroups).total;
+  if (stages_out) *stages_out = slots_for(3);
+  return group_layout(payload_bytes, 3).total;
 }
 
 template <int kGroups>
 __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(const __grid_constant__ RoundParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kSlots = slots_for(kGroups);
   const GroupSmem lay = group_layout(p.payload_bytes, kGroups);
   const int tid = threadIdx.x;
   const int g = tid >> 7;           // group
@@ -361,6 +364,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
   const int wig = (tid >> 5) & 3;   // warp in group
   const int sw = t & 7;             // XOR swizzle of this thread's eight 16-byte pieces
   uint8_t* slots = smem + lay.off_slots + size_t(g) * kSlots * kTileBytes;
+  float4* vstage4 = reinterpret_cast<float4*>(smem + lay.off_vstage + size_t(g) * kTileBytes) + t * 8;
   const int pb_pad = (p.payload_bytes + 127) & ~127;
   uint8_t* outbuf = smem + lay.off_out + size_t(g) * 2 * kMaxFrames * pb_pad;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + g * kSlots;
@@ -431,7 +435,6 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
     uint32_t sent_lo = 0, sent_hi = 0;
 
     float4 v[8];  // piece q holds elements 4*(q^sw) .. +3 of this thread's 32
-    bool v_changed = false;
     for (int a = 0; a < arrays && !aborted; a++) {
       const int c = i * arrays + a;
       const int s = c % kSlots;
@@ -487,7 +490,6 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
         if (t == 0) n_rx++;
         if (!code) return;
         changed = true;
-        v_changed = true;
         const uint32_t sb = code << 23;  // bits of 2^(code-127)
         if (full_chunk) apply_frame2<true>(v, k, w, sb, sw, vmask); else apply_frame2<false>(v, k, w, sb, sw, vmask);
       };
@@ -563,6 +565,12 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
 #pragma unroll
         for (int q = 0; q < 8; q++) slot4[q ^ sw] = k[q];
       }
+      // the tile's values leave through a staging buffer after the last mirror (if any frame arrived for the tile)
+      const bool store_values = rx_any && a == arrays - 1;
+      if (store_values) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) vstage4[q ^ sw] = v[q];
+      }
       fence_async_smem();
       {
         const uint32_t mine = (changed ? kFlagChanged : 0u) | (nonsilent_mask * kFlagNonsilent0) | (wait_failed ? kFlagFailed : 0u);
@@ -583,6 +591,7 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
       if (t == 0) {
         void* gdst = const_cast<float*>(src_of(tile, a));
         if (any_changed && a > 0) bulk_s2g(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
+        if (store_values) bulk_s2g(p.values + size_t(tile) * kTile, smem + lay.off_vstage + size_t(g) * kTileBytes, kTileBytes);
         if (a > 0 && n_frames > 0 && ns_bits) {
           int sent_here = 0;
           for (int f = 0; f < n_frames; f++) {
@@ -614,12 +623,6 @@ __global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(
       }
     }
     if (aborted) break;
-    if (v_changed) {
-      // this thread's 32 values are one 128-byte line of global memory
-      float4* gv = reinterpret_cast<float4*>(p.values + size_t(tile) * kTile) + t * 8;
-#pragma unroll
-      for (int q = 0; q < 8; q++) gv[q ^ sw] = v[q];
-    }
     if (t == 0) {
       *reinterpret_cast<uint2*>(p.sent + size_t(tile) * 8) = make_uint2(sent_lo, sent_hi);
       p.tile_state[tile] = uint8_t(pend_tile ? 1 : 0);
@@ -705,13 +708,8 @@ static int launch_main_t(const RoundParams& p, int ctas, cudaStream_t stream) {
 int launch_round_main(const RoundParams& p, int ctas, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (p.n_links < 1 || p.n_links > kMaxLinks) return int(cudaErrorInvalidValue);
-  // 3 groups of 128 threads (168 registers each, the default: no spills) or 4 groups (128 registers each)
-  static const int groups = [] {
-    const char* e = getenv("SHAREDTENSOR_ROUND_GROUPS");
-    int g = e ? atoi(e) : 3;
-    return g == 4 ? 4 : 3;
-  }();
-  return groups == 3 ? launch_main_t<3>(p, ctas, stream) : launch_main_t<4>(p, ctas, stream);
+  // 3 groups of 128 threads: 168 registers per thread (no spills) and 3 x (3 slots + staging) x 16 KB of shared memory
+  return launch_main_t<3>(p, ctas, stream);
 }
 
 }  // namespace st
