@@ -40,7 +40,7 @@ class Config:
     round_interval_us: int = 0       # pause after every busy round: caps the round rate (a rate limit for GPU edges)
     use_graph: bool = True           # engine thread replays pairs of rounds as one CUDA graph
     poll_deadline_us: int = 1000     # upper bound of every device-side wait
-    use_multimem: bool = False       # NVLS store fan-out for mesh groups when the host exposes it
+    use_multimem: bool = False       # reserved: NVLS store fan-out is not built (plain peer stores only)
     # --- TCP edges ------------------------------------------------------------------------------
     max_frames_per_s: float = 0.0    # rate cap per edge (README.md:31 of the reference lists this as a TODO)
     idle_keepalive_ms: int = 0
@@ -91,6 +91,8 @@ class Config:
             raise ValueError("ring_slots must be a power of two in 2..64")
         if self.rel_bits < 1 or self.rel_bits > 60:
             raise ValueError("rel_bits must be in 1..60")
+        if self.use_multimem:
+            raise ValueError("use_multimem: the NVLS store path is not built; leave it False")
         if not 1 <= self.frames_per_round <= 3:
             raise ValueError("frames_per_round must be in 1..3")
         if self.rounds_in_flight < 1:

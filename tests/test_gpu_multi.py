@@ -31,8 +31,11 @@ def _run(world, port, n, scenario):
 
 
 def _need(k):
-    if torch.cuda.device_count() < k:
-        pytest.skip(f"needs {k} GPUs")
+    """Ranks are spread over the GPUs that exist (rank % device_count).  Sharing a GPU is safe because no kernel of
+    this framework ever waits for a neighbour; a box with one GPU still exercises the join, the fd exchange, the
+    mapping of another process's memory and the rings."""
+    if torch.cuda.device_count() < 1:
+        pytest.skip("needs a GPU")
 
 
 @pytest.mark.parametrize("world", [2, 4])
