@@ -27,7 +27,8 @@ import torch.distributed as dist  # noqa: E402
 
 import sharedtensor  # noqa: E402
 from sharedtensor_b200.models import GPT2, CharRNN, GPT2Config, flatten_parameters  # noqa: E402
-from sharedtensor_b200.parallel.trainers import AsyncTrainer, SyncTrainer, random_token_batches  # noqa: E402
+from sharedtensor_b200.parallel.trainers import (AsyncTrainer, SyncTrainer, random_token_batches,  # noqa: E402
+                                                 structured_token_batches)
 
 
 def main():
@@ -37,6 +38,8 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--lr", type=float, default=None)
+    ap.add_argument("--data", default="random", choices=["random", "structured"],
+                    help="random: uniform tokens (the benchmark configs); structured: a learnable arithmetic sequence")
     ap.add_argument("--comm-ctas", type=int, default=32, help="SMs the sync rounds may use (async mode)")
     ap.add_argument("--round-interval-us", type=int, default=500, help="pause between sync rounds (async mode)")
     ap.add_argument("--out", default="")
@@ -58,7 +61,8 @@ def main():
         vocab, batch, seq, dtype, lr = cfg.vocab, 8, cfg.ctx, torch.bfloat16, 1e-3
     if args.lr is not None:
         lr = args.lr
-    batches = random_token_batches(vocab, batch, seq, dev, seed=1000 + rank)
+    make = random_token_batches if args.data == "random" else structured_token_batches
+    batches = make(vocab, batch, seq, dev, seed=1000 + rank)
     shared = None
     if args.mode == "async":
         # fp32 masters, one arena; parameters start on scale-block boundaries (table layout)
@@ -95,7 +99,7 @@ def main():
                "tokens_per_s": float(tot[0]), "tokens_per_s_per_gpu": float(tot[0]) / world,
                "exposed_sync_frac_max": float(mx[1]), "seconds_max": float(mx[2]), "lr": lr, "dtype": str(dtype).replace("torch.", ""),
                "loss_curve": [[round(w, 4), round(l, 5)] for w, l in zip(log.wall, log.loss)], "device_status": stats,
-               "data": "synthetic uniform-random tokens", "parameters": trainer.flat.numel()}
+               "data": "synthetic uniform-random tokens" if args.data == "random" else "synthetic arithmetic token sequences", "parameters": trainer.flat.numel()}
         print(json.dumps(out), flush=True)
         if args.out:
             Path(args.out).write_text(json.dumps(out, indent=1))

@@ -151,3 +151,16 @@ def random_token_batches(vocab: int, batch: int, seq: int, device, seed: int):
     while True:
         x = torch.randint(0, vocab, (batch, seq + 1), generator=g, device=device)
         yield x[:, :-1].contiguous(), x[:, 1:].contiguous()
+
+
+def structured_token_batches(vocab: int, batch: int, seq: int, device, seed: int, period: int = 7):
+    """Learnable synthetic data: token t+1 = (token t + step) mod vocab with a per-sequence step in 1..period, so a
+    model has to look at the previous two tokens.  Used to compare async and sync loss curves on something that
+    can actually be learnt (uniform-random tokens cannot)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    ar = torch.arange(seq + 1, device=device)
+    while True:
+        start = torch.randint(0, vocab, (batch, 1), generator=g, device=device)
+        step = torch.randint(1, period + 1, (batch, 1), generator=g, device=device)
+        x = (start + step * ar) % vocab
+        yield x[:, :-1].contiguous(), x[:, 1:].contiguous()

@@ -51,3 +51,39 @@ def test_gpt2_tiny_forward_backward_and_parameter_count():
     full = GPT2Config()
     n = (full.vocab + full.ctx) * full.d_model + full.n_layer * (12 * full.d_model ** 2 + 13 * full.d_model) + 2 * full.d_model
     assert n == 124_439_808
+
+
+def test_two_async_replicas_learn_together(free_port):
+    """Two replicas train on different shards of a learnable task through one shared tensor; both losses fall and
+    the replicas end up with the same parameters."""
+    import threading
+
+    from sharedtensor_b200.models import flatten_parameters
+    from sharedtensor_b200.parallel.trainers import structured_token_batches
+
+    torch.manual_seed(1)
+    models = [CharRNN(vocab=13, hidden=24, layers=1) for _ in range(2)]
+    models[1].load_state_dict(models[0].state_dict())
+    init, _ = flatten_parameters(models[0], align=32)
+    shared = [sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone()) for _ in range(2)]
+    logs = [None, None]
+
+    def work(i):
+        tr = AsyncTrainer(models[i], shared[i], lr=0.3)
+        data = structured_token_batches(13, 8, 10, torch.device("cpu"), seed=10 + i, period=1)
+        logs[i] = tr.run(data, steps=80, log_every=79)
+
+    try:
+        ts = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        for lg in logs:
+            assert lg.loss[-1] < 0.8 * lg.loss[0]
+        assert all(s.flush(10.0) for s in shared)
+        a, b = torch.empty_like(init), torch.empty_like(init)
+        shared[0].copyToTensor(a)
+        shared[1].copyToTensor(b)
+        assert float((a - b).norm() / a.norm()) < 1e-3
+    finally:
+        for s in reversed(shared):
+            s.close()
