@@ -42,6 +42,11 @@ def main():
                     help="random: uniform tokens (the benchmark configs); structured: a learnable arithmetic sequence")
     ap.add_argument("--comm-ctas", type=int, default=32, help="SMs the sync rounds may use (async mode)")
     ap.add_argument("--round-interval-us", type=int, default=500, help="pause between sync rounds (async mode)")
+    ap.add_argument("--rel-bits", type=int, default=22,
+                    help="async mode: a block stops sending once its residual is below 2^-rel_bits of its largest value")
+    ap.add_argument("--topology", default="tree", choices=["tree", "mesh"])
+    ap.add_argument("--rounds-per-step", type=int, default=0,
+                    help="async mode: > 0 = no engine thread, the trainer queues this many sync rounds behind every update")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, local, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -68,13 +73,19 @@ def main():
         # fp32 masters, one arena; parameters start on scale-block boundaries (table layout)
         probe, _ = flatten_parameters(model, align=32, dtype=torch.float32)
         port = int(os.environ.get("MASTER_PORT", "29500")) + 31
+        topo = {"topology": "mesh", "group_rank": rank, "group_size": world} if args.topology == "mesh" else {}
         for r in range(world):
-            if r == rank:
+            if r == rank or args.topology == "mesh":
+                if shared is not None:
+                    continue
                 shared = sharedtensor.createOrFetch("127.0.0.1", port, probe if rank == 0 else torch.empty_like(probe),
-                                                     comm_ctas=args.comm_ctas, round_interval_us=args.round_interval_us)
+                                                     comm_ctas=args.comm_ctas, round_interval_us=args.round_interval_us,
+                                                     rel_bits=args.rel_bits, **topo,
+                                                     **({"engine": "manual"} if args.rounds_per_step > 0 else {}))
             torch.cuda.synchronize()
-            dist.barrier()
-        trainer = AsyncTrainer(model, shared, lr=lr, param_dtype=dtype)
+            if args.topology == "tree":
+                dist.barrier()
+        trainer = AsyncTrainer(model, shared, lr=lr, param_dtype=dtype, rounds_per_step=args.rounds_per_step)
         del probe
     else:
         trainer = SyncTrainer(model, lr=lr, param_dtype=dtype, group=nccl)
@@ -98,7 +109,9 @@ def main():
         out = {"model": args.model, "mode": args.mode, "n_gpus": world, "steps": args.steps,
                "tokens_per_s": float(tot[0]), "tokens_per_s_per_gpu": float(tot[0]) / world,
                "exposed_sync_frac_max": float(mx[1]), "seconds_max": float(mx[2]), "lr": lr, "dtype": str(dtype).replace("torch.", ""),
-               "loss_curve": [[round(w, 4), round(l, 5)] for w, l in zip(log.wall, log.loss)], "device_status": stats,
+               "loss_curve": [[round(w, 4), round(l, 5)] for w, l in zip(log.wall, log.loss)], "device_status": stats, "rel_bits": args.rel_bits, "topology": args.topology,
+               "comm_ctas": args.comm_ctas, "round_interval_us": args.round_interval_us,
+               "rounds_per_step": args.rounds_per_step,
                "data": "synthetic uniform-random tokens" if args.data == "random" else "synthetic arithmetic token sequences", "parameters": trainer.flat.numel()}
         print(json.dumps(out), flush=True)
         if args.out:

@@ -1,7 +1,10 @@
 #include "engine.hpp"
 
 #include <cuda_runtime_api.h>
+#include <sys/prctl.h>
 #include <unistd.h>
+
+#include <chrono>
 
 #include <cstring>
 #include <stdexcept>
@@ -319,43 +322,55 @@ void GpuReplica::order_user_after(void* user_stream) {
 
 void GpuReplica::load_values(const float* src, void* user_stream) {
   DeviceGuard g(device_);
-  std::lock_guard<std::mutex> lk(mu_);
-  order_after_user(user_stream);
-  check(cudaMemcpyAsync(values(), src, size_t(n_) * 4, cudaMemcpyDeviceToDevice, S(comm_)), "cudaMemcpyAsync");
-  check(launch_fill_state(tile_state_, n_tiles_, 1, comm_), "fill_state");
-  launches_ += 1;
-  epoch_++;
-  order_user_after(user_stream);
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    order_after_user(user_stream);
+    check(cudaMemcpyAsync(values(), src, size_t(n_) * 4, cudaMemcpyDeviceToDevice, S(comm_)), "cudaMemcpyAsync");
+    check(launch_fill_state(tile_state_, n_tiles_, 1, comm_), "fill_state");
+    launches_ += 1;
+    epoch_++;
+    order_user_after(user_stream);
+  }
+  local_update();
 }
 
 void GpuReplica::add(const float* delta, void* user_stream) {
   DeviceGuard g(device_);
-  std::lock_guard<std::mutex> lk(mu_);
-  order_after_user(user_stream);
-  check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
-  epoch_++;
-  launches_ += 1;
-  order_user_after(user_stream);
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    order_after_user(user_stream);
+    check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
+    epoch_++;
+    launches_ += 1;
+    order_user_after(user_stream);
+  }
+  local_update();
 }
 
 void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) {
   DeviceGuard g(device_);
-  std::lock_guard<std::mutex> lk(mu_);
-  order_after_user(user_stream);
-  check(launch_sub_add(values(), neu, old, n_, tile_state_, n_tiles_, 0, comm_), "sub_add kernel");
-  epoch_++;
-  launches_ += 1;
-  order_user_after(user_stream);
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    order_after_user(user_stream);
+    check(launch_sub_add(values(), neu, old, n_, tile_state_, n_tiles_, 0, comm_), "sub_add kernel");
+    epoch_++;
+    launches_ += 1;
+    order_user_after(user_stream);
+  }
+  local_update();
 }
 
 void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) {
   DeviceGuard gd(device_);
-  std::lock_guard<std::mutex> lk(mu_);
-  order_after_user(user_stream);
-  check(launch_add_scaled_bf16(values(), g, alpha, n_, tile_state_, n_tiles_, comm_), "add_scaled_bf16 kernel");
-  epoch_++;
-  launches_ += 1;
-  order_user_after(user_stream);
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    order_after_user(user_stream);
+    check(launch_add_scaled_bf16(values(), g, alpha, n_, tile_state_, n_tiles_, comm_), "add_scaled_bf16 kernel");
+    epoch_++;
+    launches_ += 1;
+    order_user_after(user_stream);
+  }
+  local_update();
 }
 
 void GpuReplica::snapshot(float* out, void* user_stream) {
@@ -442,21 +457,25 @@ float GpuReplica::tcp_encode(int link, uint32_t* words, float min_scale_abs, flo
 void GpuReplica::tcp_decode(int link, const uint32_t* words, float scale) {
   if (scale == 0.f) return;
   DeviceGuard g(device_);
-  std::lock_guard<std::mutex> lk(mu_);
-  if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
-  const size_t n_words = size_t((n_ + 31) / 32);
-  if (!tcp_words_dev_) {
-    check(cudaMalloc(reinterpret_cast<void**>(&tcp_words_dev_), n_words * 4), "cudaMalloc tcp words");
-    check(cudaMalloc(reinterpret_cast<void**>(&tcp_stat_dev_), 8), "cudaMalloc tcp stat");
-    check(cudaMallocHost(reinterpret_cast<void**>(&tcp_pinned_), 8 + n_words * 4), "cudaMallocHost tcp staging");
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
+    const size_t n_words = size_t((n_ + 31) / 32);
+    if (!tcp_words_dev_) {
+      check(cudaMalloc(reinterpret_cast<void**>(&tcp_words_dev_), n_words * 4), "cudaMalloc tcp words");
+      check(cudaMalloc(reinterpret_cast<void**>(&tcp_stat_dev_), 8), "cudaMalloc tcp stat");
+      check(cudaMallocHost(reinterpret_cast<void**>(&tcp_pinned_), 8 + n_words * 4), "cudaMallocHost tcp staging");
+    }
+    std::memcpy(tcp_pinned_ + 2, words, n_words * 4);
+    check(cudaMemcpyAsync(tcp_words_dev_, tcp_pinned_ + 2, n_words * 4, cudaMemcpyHostToDevice, S(comm_)), "cudaMemcpyAsync");
+    check(launch_tensor_decode(tcp_words_dev_, scale, n_, values(), static_cast<float*>(links_[link].mirror.ptr), tile_state_,
+                               comm_),
+          "tensor_decode kernel");
+    check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+    launches_ += 1;
+    epoch_++;
   }
-  std::memcpy(tcp_pinned_ + 2, words, n_words * 4);
-  check(cudaMemcpyAsync(tcp_words_dev_, tcp_pinned_ + 2, n_words * 4, cudaMemcpyHostToDevice, S(comm_)), "cudaMemcpyAsync");
-  check(launch_tensor_decode(tcp_words_dev_, scale, n_, values(), static_cast<float*>(links_[link].mirror.ptr), tile_state_, comm_),
-        "tensor_decode kernel");
-  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
-  launches_ += 1;
-  epoch_++;
+  local_update();  // the frame has to travel on over the other links
 }
 
 void GpuReplica::sync() {
@@ -498,8 +517,41 @@ void GpuReplica::stop_engine() {
   engine_on_.store(false);
 }
 
+bool GpuReplica::wake(bool from_neighbour) {
+  (void)from_neighbour;
+  const bool was_idle = idle_.exchange(false);
+  {
+    std::lock_guard<std::mutex> g(wake_mu_);
+    wake_pending_ = true;
+  }
+  wake_cv_.notify_all();
+  return was_idle;
+}
+
+void GpuReplica::set_doorbell(std::function<void()> fn) {
+  std::lock_guard<std::mutex> g(wake_mu_);
+  doorbell_ = std::move(fn);
+}
+
+void GpuReplica::local_update() {
+  if (!wake(false)) return;
+  std::function<void()> fn;
+  {
+    std::lock_guard<std::mutex> g(wake_mu_);
+    fn = doorbell_;
+  }
+  if (fn) fn();
+}
+
+void GpuReplica::idle_pause(uint64_t us) {
+  std::unique_lock<std::mutex> lk(wake_mu_);
+  if (!wake_pending_) wake_cv_.wait_for(lk, std::chrono::microseconds(us), [this] { return wake_pending_ || engine_stop_.load(); });
+  wake_pending_ = false;
+}
+
 void GpuReplica::engine_loop() {
   cudaSetDevice(device_);
+  ::prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);  // 1 us instead of the default 50 us: the idle pauses start at 10 us
   const size_t depth = ev_round_.size();
   uint64_t r = 0;
   uint64_t idle_rounds = 0;
@@ -575,9 +627,12 @@ void GpuReplica::engine_loop() {
         uint64_t shift = idle_rounds - 3 > 6 ? 6 : idle_rounds - 3;
         uint64_t us = 10ull << shift;
         if (us > uint64_t(cfg_.idle_sleep_us)) us = uint64_t(cfg_.idle_sleep_us);
-        ::usleep(useconds_t(us));
+        idle_.store(true);
+        idle_pause(us);  // a local update or a neighbour's doorbell ends it early
+        if (!idle_.load()) idle_rounds = 0;
       }
     } else {
+      idle_.store(false);
       idle_rounds = 0;
       // pacing: a training job can cap how often rounds run, leaving the GPU to its own kernels in between
       if (cfg_.round_interval_us > 0) ::usleep(useconds_t(cfg_.round_interval_us));

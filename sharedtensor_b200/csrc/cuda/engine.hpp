@@ -10,6 +10,7 @@
 #include <atomic>
 #include <condition_variable>
 #include <cstdint>
+#include <functional>
 #include <mutex>
 #include <string>
 #include <thread>
@@ -69,6 +70,8 @@ class GpuReplica {
 
   // ---- data path ----
   void load_values(const float* src, void* user_stream);
+  // Updates run on the comm stream (a round must never see a half-applied update), after the work already queued
+  // on `user_stream`; the user stream then waits for the update, so a snapshot that follows sees it.
   void add(const float* delta, void* user_stream);
   void sub_add(const float* neu, const float* old, void* user_stream);
   void add_scaled_bf16(const void* g_bf16, float alpha, void* user_stream);  // values += alpha * g
@@ -87,6 +90,12 @@ class GpuReplica {
   void start_engine();
   void stop_engine();
   bool engine_running() const { return engine_on_.load(); }
+  // Ends the engine thread's idle pause at once.  `from_neighbour` marks a doorbell that came over a socket; the
+  // return value says whether the engine had been idle (the caller then passes the doorbell on).
+  bool wake(bool from_neighbour = false);
+  // Called (from the thread that made the update) when a local update finds the engine idle: the node rings its
+  // neighbours so that their engines are polling by the time the first frames arrive.
+  void set_doorbell(std::function<void()> fn);
 
   // ---- observation ----
   std::vector<uint64_t> status();      // StatusWord order, then the trace ring; synchronises the comm stream
@@ -152,6 +161,13 @@ class GpuReplica {
   std::mutex engine_mu_;               // serialises start_engine / stop_engine
   std::thread engine_;
   std::atomic<bool> engine_on_{false}, engine_stop_{false};
+  std::atomic<bool> idle_{false};      // the engine has seen several rounds without work and pauses between rounds
+  std::mutex wake_mu_;
+  std::condition_variable wake_cv_;
+  bool wake_pending_ = false;          // under wake_mu_
+  std::function<void()> doorbell_;     // under wake_mu_
+  void local_update();                 // wake + doorbell if the engine was idle
+  void idle_pause(uint64_t us);
   std::atomic<uint64_t> launches_{0};
   std::atomic<uint64_t> epoch_{1};
   std::string error_;

@@ -78,6 +78,7 @@ class GpuNode {
   GpuNode(int device, int64_t n, const GpuConfig& gcfg, const GpuNodeOptions& opt)
       : rep_(new GpuReplica(device, n, gcfg)), gcfg_(gcfg), opt_(opt), device_(device), n_(n) {
     for (int s = 0; s < kNumSlots; s++) edges_[s].slot = s;
+    rep_->set_doorbell([this] { ring_neighbours(-1); });
   }
   ~GpuNode() { close(); }
 
@@ -132,6 +133,7 @@ class GpuNode {
     if (closed_.exchange(true)) return;
     stop_.store(true);
     cv_.notify_all();
+    if (rep_) rep_->set_doorbell(nullptr);
     if (rep_) rep_->stop_engine();
     if (listener_) listener_->stop();
     if (unix_fd_ >= 0) ::shutdown(unix_fd_, SHUT_RDWR);
@@ -625,6 +627,18 @@ class GpuNode {
     }
   }
 
+  // One byte on the otherwise silent TCP connection of every peer-memory edge except `except_slot`.  A GPU cannot
+  // interrupt a host thread, so an engine that pauses between rounds would find the first frames of a burst only
+  // at its next poll; the doorbell travels ahead of the frames and ends the pause.
+  void ring_neighbours(int except_slot) {
+    std::lock_guard<std::mutex> g(mu_);
+    for (int s = 0; s < kNumSlots; s++) {
+      const Edge& e = edges_[s];
+      if (s == except_slot || e.state != 2 || e.tcp || e.tcp_fd < 0 || e.peer_id < 0) continue;
+      (void)!::send(e.tcp_fd, "W", 1, MSG_DONTWAIT | MSG_NOSIGNAL);
+    }
+  }
+
   // ---- liveness ----
   void watch_loop() {
     while (!stop_.load()) {
@@ -675,7 +689,12 @@ class GpuNode {
           if (pr <= 0 || !(pfds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
           char buf[256];
           ssize_t r = ::recv(pfds[i].fd, buf, sizeof(buf), MSG_DONTWAIT);
-          if (r > 0) continue;  // stray bytes on a liveness connection are ignored
+          if (r > 0) {
+            // a doorbell: the neighbour is about to send frames.  Poll at full rate, and pass the doorbell on if
+            // this engine had been pausing (the rest of the tree then is, too).
+            if (rep_->wake(true)) ring_neighbours(s);
+            continue;
+          }
           if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;
         } else {
           s -= 100;  // a TCP edge whose thread reported a failure
@@ -820,6 +839,7 @@ class GpuMeshNode {
     if (world < 1 || world > kMaxRings + 1 || rank < 0 || rank >= world)
       throw std::invalid_argument("mesh group needs 1..9 members and a rank inside it");
     peers_.resize(size_t(world));
+    rep_->set_doorbell([this] { ring_members(); });
   }
   ~GpuMeshNode() { close(); }
   GpuReplica& replica() { return *rep_; }
@@ -877,6 +897,7 @@ class GpuMeshNode {
   void close() {
     if (closed_.exchange(true)) return;
     stop_.store(true);
+    if (rep_) rep_->set_doorbell(nullptr);
     if (rep_) rep_->stop_engine();
     if (watch_.joinable()) watch_.join();
     for (int j = 0; j < world_; j++) drop_peer(j);
@@ -962,7 +983,11 @@ class GpuMeshNode {
         if (!(pfds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
         char buf[64];
         ssize_t r = ::recv(pfds[i].fd, buf, sizeof(buf), MSG_DONTWAIT);
-        if (r > 0 || (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR))) continue;
+        if (r > 0) {
+          rep_->wake(true);  // a doorbell: that member is about to send frames (one hop: nothing to pass on)
+          continue;
+        }
+        if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;
         if (stop_.load()) break;
         std::fprintf(stderr, "[sharedtensor] mesh member %d is gone, dropping its rings\n", who[i]);
         drop_peer(who[i]);
@@ -970,6 +995,12 @@ class GpuMeshNode {
         dropped_++;
       }
     }
+  }
+
+  void ring_members() {
+    std::lock_guard<std::mutex> g(mu_);
+    for (auto& p : peers_)
+      if (p.fd >= 0 && p.peer_id >= 0) (void)!::send(p.fd, "W", 1, MSG_DONTWAIT | MSG_NOSIGNAL);
   }
 
   void drop_peer(int j) {

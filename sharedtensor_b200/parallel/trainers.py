@@ -99,9 +99,15 @@ class AsyncTrainer(_Base):
     """SGD on a shared tensor: ``w <- shared`` (one snapshot kernel), backward, ``shared += -lr * g`` (one add kernel).
     With bf16 parameters the shared tensor holds fp32 masters: the snapshot casts, the add consumes bf16 gradients."""
 
-    def __init__(self, model, shared, lr: float, param_dtype: torch.dtype = torch.float32, align: int = 32):
+    def __init__(self, model, shared, lr: float, param_dtype: torch.dtype = torch.float32, align: int = 32,
+                 rounds_per_step: int = 0):
+        """``rounds_per_step`` > 0 is for a shared tensor created with ``engine="manual"``: the trainer then queues
+        that many sync rounds behind every update (on the comm stream, overlapping the next forward pass) instead of
+        leaving the rounds to a free-running engine thread.  One round per step is enough to keep up: what a round
+        could not send stays in the residual and goes out with the next one."""
         super().__init__(model, lr, align=align, param_dtype=param_dtype)
         self.shared = shared
+        self.rounds_per_step = rounds_per_step
         if shared.numel != self.flat.numel():
             raise ValueError("Not the right size!")
 
@@ -117,6 +123,8 @@ class AsyncTrainer(_Base):
         else:
             self.gflat.mul_(-self.lr)
             self.shared.addFromTensor(self.gflat)
+        if self.rounds_per_step > 0:
+            self.shared.step(self.rounds_per_step)
 
 
 class SyncTrainer(_Base):

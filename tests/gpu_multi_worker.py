@@ -1,6 +1,7 @@
 """Child process of test_gpu_multi.py: one GPU replica per process, joined through the TCP tree and upgraded
 to peer-memory edges.  Prints one JSON line with what it observed."""
 import json
+import os
 import sys
 import time
 from pathlib import Path
@@ -12,7 +13,20 @@ import torch  # noqa: E402
 import sharedtensor  # noqa: E402
 
 
+def _touch_and_wait(sync_dir, name, wanted, timeout=100.0):
+    """File rendezvous between the worker processes: start-up time (first CUDA context on a fresh machine) varies by
+    seconds, so ordering by sleeps alone is not enough."""
+    (Path(sync_dir) / name).touch()
+    deadline = time.time() + timeout
+    while time.time() < deadline:
+        if all((Path(sync_dir) / w).exists() for w in wanted):
+            return
+        time.sleep(0.01)
+    raise RuntimeError(f"rendezvous timed out waiting for {wanted}")
+
+
 def main():
+    sync_dir = os.environ["ST_TEST_SYNC_DIR"]
     rank, world, port, n, scenario = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
     torch.cuda.set_device(rank % torch.cuda.device_count())
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -23,8 +37,10 @@ def main():
         st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), topology="mesh",
                                         group_rank=rank, group_size=world)
     else:
-        time.sleep(0.4 * rank)  # join in rank order
+        # the founder first, then the others in rank order (the tree's shape follows the join order)
+        _touch_and_wait(sync_dir, f"up_{rank}", [f"joined_{r}" for r in range(rank)])
         st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), rejoin_backoff_ms=100)
+        (Path(sync_dir) / f"joined_{rank}").touch()
     out = torch.empty(n, device=dev)
     st.copyToTensor(out)
     torch.cuda.synchronize()
@@ -34,7 +50,7 @@ def main():
     for r in range(world):
         g.manual_seed(77 + r)
         deltas.append(torch.randn(n, generator=g, device=dev) * 1e-2)
-    time.sleep(0.5 * (world - rank))  # everybody is in
+    _touch_and_wait(sync_dir, f"in_{rank}", [f"in_{r}" for r in range(world)])  # everybody is in
     st.addFromTensor(deltas[rank])
     expect = init + sum(deltas)
     if scenario == "kill_leaf" and rank == world - 1:
@@ -43,8 +59,6 @@ def main():
         time.sleep(0.5)
         res["exiting"] = True
         print(json.dumps(res), flush=True)
-        import os
-
         os._exit(0)
     deadline = time.time() + 30
     rel = None
@@ -79,7 +93,9 @@ def main():
     res["errors"] = s["device"]["errors"]
     res["frames_sent"] = s["device"]["frames_sent"]
     print(json.dumps(res), flush=True)
-    time.sleep(1.0 + 0.3 * rank)  # leaves first
+    alive = world - 1 if scenario == "kill_leaf" else world
+    _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(alive)])  # nobody leaves before all have looked
+    time.sleep(0.2 + 0.3 * (world - rank))  # leaves first
     st.close()
 
 

@@ -2,8 +2,10 @@
 join, convergence to the sum, and a rank that leaves (host-side failure: it exits between steps)."""
 import json
 import os
+import shutil
 import subprocess
 import sys
+import tempfile
 from pathlib import Path
 
 import pytest
@@ -14,19 +16,26 @@ HERE = Path(__file__).resolve().parent
 
 
 def _run(world, port, n, scenario):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    sync_dir = tempfile.mkdtemp(prefix="st_multi_")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ST_TEST_SYNC_DIR=sync_dir)
     procs = [subprocess.Popen([sys.executable, str(HERE / "gpu_multi_worker.py"), str(r), str(world), str(port), str(n), scenario],
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env) for r in range(world)]
-    results = []
+    outs = []
     for p in procs:
         try:
-            out, err = p.communicate(timeout=180)
+            out, err = p.communicate(timeout=150)
         except subprocess.TimeoutExpired:
             p.kill()
             out, err = p.communicate()
+        outs.append((p.returncode, out, err))
+    results = []
+    for rc, out, err in outs:
         lines = [ln for ln in out.splitlines() if ln.startswith("{")]
-        assert lines, f"worker produced no result; rc={p.returncode}\n{err[-2000:]}"
+        if not lines:
+            report = "\n".join(f"--- rank {i}: rc={o[0]}\n{o[2][-1500:]}" for i, o in enumerate(outs))
+            raise AssertionError(f"a worker produced no result\n{report}")
         results.append(json.loads(lines[-1]))
+    shutil.rmtree(sync_dir, ignore_errors=True)
     return results
 
 
