@@ -40,13 +40,15 @@ def main():
     ap.add_argument("--lr", type=float, default=None)
     ap.add_argument("--data", default="random", choices=["random", "structured"],
                     help="random: uniform tokens (the benchmark configs); structured: a learnable arithmetic sequence")
-    ap.add_argument("--comm-ctas", type=int, default=32, help="SMs the sync rounds may use (async mode)")
-    ap.add_argument("--round-interval-us", type=int, default=500, help="pause between sync rounds (async mode)")
-    ap.add_argument("--rel-bits", type=int, default=22,
+    ap.add_argument("--comm-ctas", type=int, default=148, help="SMs the sync rounds may use (async mode)")
+    ap.add_argument("--round-interval-us", type=int, default=0,
+                    help="engine-thread mode (--rounds-per-step 0): pause after every busy sync round")
+    ap.add_argument("--rel-bits", type=int, default=14,
                     help="async mode: a block stops sending once its residual is below 2^-rel_bits of its largest value")
     ap.add_argument("--topology", default="tree", choices=["tree", "mesh"])
-    ap.add_argument("--rounds-per-step", type=int, default=0,
-                    help="async mode: > 0 = no engine thread, the trainer queues this many sync rounds behind every update")
+    ap.add_argument("--rounds-per-step", type=int, default=1,
+                    help="async mode: > 0 = no engine thread, the trainer queues this many sync rounds behind every update; "
+                         "0 = free-running engine thread")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, local, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

@@ -5,6 +5,8 @@ engine thread).  Nothing here touches the data path.
 """
 from __future__ import annotations
 
+import struct
+
 import torch
 
 from .. import _native
@@ -164,6 +166,9 @@ class GpuMeshBackend(GpuBackend):
         names = _native.cuda().status_names()
         st = self.rep.status()
         dev = {k: v for k, v in zip(names, st)}
+        for k in dev:  # the residual maxima are kept as float bit patterns (they are updated with an integer max)
+            if k.startswith("residual_max"):
+                dev[k] = struct.unpack("<f", struct.pack("<I", dev[k] & 0xFFFFFFFF))[0]
         return {"backend": "gpu/p2p-mesh", "master": self.rank == 0, "ready": True, "n": self.n, "rank": self.rank,
                 "group_size": self.world, "members_alive": self.node.members_alive(), "dropped": self.node.dropped(),
                 "launches": self.rep.launches(), "device": dev, "edges": {}}
