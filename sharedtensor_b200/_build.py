@@ -22,9 +22,9 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 
-CORE_SOURCES = ["core/codec.cpp", "core/tree.cpp", "core/node.cpp", "core/bindings.cpp"]
+CORE_SOURCES = ["core/codec.cpp", "core/codec_fast.cpp", "core/tree.cpp", "core/node.cpp", "core/bindings.cpp"]
 CUDA_SOURCES_CU = ["cuda/elementwise.cu", "cuda/round.cu", "cuda/noalloc.cu"]
-CUDA_SOURCES_CPP = ["core/codec.cpp", "core/tree.cpp", "cuda/vmm.cpp", "cuda/engine.cpp", "cuda/gpu_node.cpp",
+CUDA_SOURCES_CPP = ["core/codec.cpp", "core/codec_fast.cpp", "core/tree.cpp", "cuda/vmm.cpp", "cuda/engine.cpp", "cuda/gpu_node.cpp",
                     "cuda/bindings_cuda.cpp"]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

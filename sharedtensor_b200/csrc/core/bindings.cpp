@@ -55,6 +55,23 @@ void bind_core(py::module_& m) {
   m.def("decode_tensor_add", [](uintptr_t bits, float scale, size_t n, uintptr_t dst, uintptr_t dst2) {
     decode_tensor_add(ptr<uint8_t>(bits), scale, n, ptr<float>(dst), dst2 ? ptr<float>(dst2) : nullptr);
   });
+  m.def("encode_tensor_fast", [](uintptr_t v, uintptr_t k, size_t n, uintptr_t bits, float min_abs, float min_rel) {
+    return encode_tensor_fast(ptr<float>(v), ptr<float>(k), n, ptr<uint8_t>(bits), min_abs, min_rel);
+  });
+  m.def("decode_tensor_add_fast", [](uintptr_t bits, float scale, size_t n, uintptr_t dst, uintptr_t dst2) {
+    decode_tensor_add_fast(ptr<uint8_t>(bits), scale, n, ptr<float>(dst), dst2 ? ptr<float>(dst2) : nullptr);
+  });
+  m.def("encode_block_fast", [](uintptr_t v, uintptr_t k, size_t n, int block, int min_exp, int rel_bits, uintptr_t words,
+                                uintptr_t scales) {
+    BlockGate g;
+    g.min_exp = min_exp;
+    g.rel_bits = rel_bits;
+    return encode_block_fast(ptr<float>(v), ptr<float>(k), n, block, g, ptr<uint32_t>(words), ptr<uint8_t>(scales));
+  });
+  m.def("decode_block_add_fast", [](uintptr_t words, uintptr_t scales, size_t n, int block, uintptr_t dst, uintptr_t dst2) {
+    decode_block_add_fast(ptr<uint32_t>(words), ptr<uint8_t>(scales), n, block, ptr<float>(dst),
+                          dst2 ? ptr<float>(dst2) : nullptr);
+  });
   m.def("encode_block", [](uintptr_t v, uintptr_t k, size_t n, int block, int min_exp, int rel_bits, uintptr_t words,
                            uintptr_t scales) {
     BlockGate g;

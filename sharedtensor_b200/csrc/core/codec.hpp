@@ -82,6 +82,15 @@ float encode_tensor(const float* v, float* k, size_t n, uint8_t* bits, float min
 // Decoder: dst[i] += (bit ? -scale : +scale).  `dst2` may be null; if not it gets the same step.
 void decode_tensor_add(const uint8_t* bits, float scale, size_t n, float* dst, float* dst2);
 
+// Fast paths (codec_fast.cpp): AVX2 where the CPU has it, several threads for large tensors; bit-for-bit the
+// results of the plain functions above.  encode_tensor_fast is rule 1 (bisection) with the smallest useful
+// scale given as max(min_scale_abs, min_scale_rel * max|v|), found in the same pass as the largest residual.
+float encode_tensor_fast(const float* v, float* k, size_t n, uint8_t* bits, float min_scale_abs, float min_scale_rel);
+void decode_tensor_add_fast(const uint8_t* bits, float scale, size_t n, float* dst, float* dst2);
+void add_fast(float* values, const float* delta, size_t n);
+void sub_add_fast(float* values, const float* neu, const float* old, size_t n);
+void copy_fast(float* dst, const float* src, size_t n);
+
 // ---------------------------------------------------------------------------------------------
 // Block-scale (GPU format; CPU oracle)
 // ---------------------------------------------------------------------------------------------
@@ -98,6 +107,10 @@ double encode_block(const float* v, float* k, size_t n, int block, const BlockGa
 // Applies one block-scale frame to dst (and dst2 if non-null).
 void decode_block_add(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst,
                       float* dst2);
+// The same two, cut into block-aligned pieces over several threads for large tensors.
+double encode_block_fast(const float* v, float* k, size_t n, int block, const BlockGate& gate, uint32_t* words,
+                         uint8_t* scales);
+void decode_block_add_fast(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst, float* dst2);
 
 // Per-segment sum of squares over a flat arena (table sync; README.md:41 of the reference lists
 // per-tensor magnitudes as a TODO).  offsets has n_seg+1 entries.

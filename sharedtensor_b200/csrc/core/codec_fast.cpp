@@ -1,0 +1,255 @@
+// Fast host paths of the tensor-scale codec and of the element-wise replica updates: AVX2 where the CPU has it
+// (checked at run time), several threads for large tensors.  Every function here produces bit-for-bit what its
+// plain counterpart in codec.cpp produces — same per-element operations, order-independent reductions (maxima) —
+// and the tests hold them to that.  The reference does all of this in scalar loops on the calling thread
+// (src/sharedtensor.c:156-174 encode, 106-111 decode, 448-453 add).
+#include <immintrin.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "codec.hpp"
+
+namespace st {
+
+namespace {
+
+int max_threads() {
+  static const int v = [] {
+    int hw = int(std::thread::hardware_concurrency());
+    if (hw < 1) hw = 1;
+    int t = hw > 8 ? 8 : hw;
+    if (const char* e = std::getenv("SHAREDTENSOR_CPU_THREADS")) {
+      int x = std::atoi(e);
+      if (x >= 1 && x <= 64) t = x;
+    }
+    return t;
+  }();
+  return v;
+}
+
+bool have_avx2() {
+  static const bool v = __builtin_cpu_supports("avx2");
+  return v;
+}
+
+// Runs fn(begin, end) over [0, n) cut into at most max_threads() pieces whose boundaries are multiples of `align`.
+template <class F>
+void parallel_chunks(size_t n, size_t align, F fn) {
+  constexpr size_t kGrain = size_t(1) << 19;  // below this a second thread costs more than it saves
+  size_t t = std::min<size_t>(size_t(max_threads()), n / kGrain);
+  if (t <= 1) {
+    fn(size_t(0), n, 0);
+    return;
+  }
+  size_t chunk = (n + t - 1) / t;
+  chunk = (chunk + align - 1) / align * align;
+  std::vector<std::thread> th;
+  th.reserve(t - 1);
+  int idx = 1;
+  for (size_t b = chunk; b < n; b += chunk, idx++) {
+    size_t e = std::min(n, b + chunk);
+    th.emplace_back([=] { fn(b, e, idx); });
+  }
+  fn(size_t(0), std::min(n, chunk), 0);
+  for (auto& x : th) x.join();
+}
+
+// ---- maxima of |v| and |v - k| ------------------------------------------------------------------
+void maxabs2_scalar(const float* v, const float* k, size_t b, size_t e, float* vmax, float* xmax) {
+  float a = 0.0f, x = 0.0f;
+  for (size_t i = b; i < e; i++) {
+    float av = std::fabs(v[i]);
+    if (av > a) a = av;
+    float ax = std::fabs(v[i] - k[i]);
+    if (ax > x) x = ax;
+  }
+  *vmax = a;
+  *xmax = x;
+}
+
+__attribute__((target("avx2"))) void maxabs2_avx2(const float* v, const float* k, size_t b, size_t e, float* vmax,
+                                                  float* xmax) {
+  const __m256 absmask = _mm256_castsi256_ps(_mm256_set1_epi32(0x7fffffff));
+  __m256 a = _mm256_setzero_ps(), x = _mm256_setzero_ps();
+  size_t i = b;
+  for (; i + 8 <= e; i += 8) {
+    __m256 vv = _mm256_loadu_ps(v + i);
+    __m256 kk = _mm256_loadu_ps(k + i);
+    // max_ps(new, acc) returns acc when new is NaN: the same as the scalar "if (new > acc)"
+    a = _mm256_max_ps(_mm256_and_ps(vv, absmask), a);
+    x = _mm256_max_ps(_mm256_and_ps(_mm256_sub_ps(vv, kk), absmask), x);
+  }
+  float ta[8], tx[8];
+  _mm256_storeu_ps(ta, a);
+  _mm256_storeu_ps(tx, x);
+  float ra = 0.0f, rx = 0.0f;
+  for (int j = 0; j < 8; j++) {
+    if (ta[j] > ra) ra = ta[j];
+    if (tx[j] > rx) rx = tx[j];
+  }
+  float sa, sx;
+  maxabs2_scalar(v, k, i, e, &sa, &sx);
+  *vmax = sa > ra ? sa : ra;
+  *xmax = sx > rx ? sx : rx;
+}
+
+// ---- sign bits and mirror step ------------------------------------------------------------------
+// [b, e) with b a multiple of 8; writes bits[b/8 ...]
+void sign_step_scalar(const float* v, float* k, size_t b, size_t e, uint8_t* bits, float scale) {
+  for (size_t i = b; i < e; i += 8) {
+    unsigned byte = 0;
+    size_t lim = std::min(e, i + 8);
+    for (size_t j = i; j < lim; j++) {
+      float x = v[j] - k[j];
+      if (x > 0.0f) {
+        k[j] += scale;
+      } else {
+        byte |= 1u << (j - i);
+        k[j] -= scale;
+      }
+    }
+    bits[i >> 3] = uint8_t(byte);
+  }
+}
+
+__attribute__((target("avx2"))) void sign_step_avx2(const float* v, float* k, size_t b, size_t e, uint8_t* bits,
+                                                    float scale) {
+  const __m256 zero = _mm256_setzero_ps();
+  const __m256 pos = _mm256_set1_ps(scale), neg = _mm256_set1_ps(-scale);
+  size_t i = b;
+  for (; i + 8 <= e; i += 8) {
+    __m256 vv = _mm256_loadu_ps(v + i);
+    __m256 kk = _mm256_loadu_ps(k + i);
+    __m256 gt = _mm256_cmp_ps(_mm256_sub_ps(vv, kk), zero, _CMP_GT_OQ);  // x > 0, false for NaN like the scalar test
+    bits[i >> 3] = uint8_t(~unsigned(_mm256_movemask_ps(gt)) & 0xffu);
+    _mm256_storeu_ps(k + i, _mm256_add_ps(kk, _mm256_blendv_ps(neg, pos, gt)));
+  }
+  if (i < e) sign_step_scalar(v, k, i, e, bits, scale);
+}
+
+// scale-0 frame: bits only, the mirror does not move
+void sign_only(const float* v, const float* k, size_t b, size_t e, uint8_t* bits) {
+  for (size_t i = b; i < e; i += 8) {
+    unsigned byte = 0;
+    size_t lim = std::min(e, i + 8);
+    for (size_t j = i; j < lim; j++)
+      if (!(v[j] - k[j] > 0.0f)) byte |= 1u << (j - i);
+    bits[i >> 3] = uint8_t(byte);
+  }
+}
+
+// ---- decode ---------------------------------------------------------------------------------------
+void decode_scalar(const uint8_t* bits, float scale, size_t b, size_t e, float* dst, float* dst2) {
+  const float step[2] = {scale, -scale};
+  for (size_t i = b; i < e; i++) {
+    float f = step[(bits[i >> 3] >> (i & 7)) & 1];
+    dst[i] += f;
+    if (dst2) dst2[i] += f;
+  }
+}
+
+__attribute__((target("avx2"))) void decode_avx2(const uint8_t* bits, float scale, size_t b, size_t e, float* dst,
+                                                 float* dst2) {
+  const __m256i lane_bit = _mm256_setr_epi32(1, 2, 4, 8, 16, 32, 64, 128);
+  const __m256 pos = _mm256_set1_ps(scale), neg = _mm256_set1_ps(-scale);
+  size_t i = b;  // b is a multiple of 8
+  for (; i + 8 <= e; i += 8) {
+    __m256i byte = _mm256_set1_epi32(int(bits[i >> 3]));
+    __m256 isneg = _mm256_castsi256_ps(_mm256_cmpeq_epi32(_mm256_and_si256(byte, lane_bit), lane_bit));
+    __m256 f = _mm256_blendv_ps(pos, neg, isneg);
+    _mm256_storeu_ps(dst + i, _mm256_add_ps(_mm256_loadu_ps(dst + i), f));
+    if (dst2) _mm256_storeu_ps(dst2 + i, _mm256_add_ps(_mm256_loadu_ps(dst2 + i), f));
+  }
+  if (i < e) decode_scalar(bits, scale, i, e, dst, dst2);
+}
+
+float pow2_floor_f(float s) {
+  if (!(s > 0.0f) || std::isinf(s)) return 0.0f;
+  int e;
+  std::frexp(double(s), &e);
+  return float(std::ldexp(1.0, e - 1));
+}
+
+}  // namespace
+
+float encode_tensor_fast(const float* v, float* k, size_t n, uint8_t* bits, float min_scale_abs, float min_scale_rel) {
+  const bool avx = have_avx2();
+  float vmaxs[64], xmaxs[64];
+  for (int i = 0; i < 64; i++) vmaxs[i] = xmaxs[i] = 0.0f;
+  parallel_chunks(n, 8, [&](size_t b, size_t e, int idx) {
+    if (avx) maxabs2_avx2(v, k, b, e, &vmaxs[idx], &xmaxs[idx]);
+    else maxabs2_scalar(v, k, b, e, &vmaxs[idx], &xmaxs[idx]);
+  });
+  float vmax = 0.0f, xmax = 0.0f;
+  for (int i = 0; i < 64; i++) {
+    if (vmaxs[i] > vmax) vmax = vmaxs[i];
+    if (xmaxs[i] > xmax) xmax = xmaxs[i];
+  }
+  float min_scale = min_scale_abs;
+  if (min_scale_rel > 0.0f) {
+    float rel = vmax * min_scale_rel;
+    if (rel > min_scale) min_scale = rel;
+  }
+  float scale = pow2_floor_f(xmax * 0.6666667f);
+  if (scale < min_scale) scale = 0.0f;
+  if (scale == 0.0f) {
+    parallel_chunks(n, 8, [&](size_t b, size_t e, int) { sign_only(v, k, b, e, bits); });
+    return 0.0f;
+  }
+  parallel_chunks(n, 8, [&](size_t b, size_t e, int) {
+    if (avx) sign_step_avx2(v, k, b, e, bits, scale);
+    else sign_step_scalar(v, k, b, e, bits, scale);
+  });
+  return scale;
+}
+
+void decode_tensor_add_fast(const uint8_t* bits, float scale, size_t n, float* dst, float* dst2) {
+  if (scale == 0.0f) return;
+  const bool avx = have_avx2();
+  parallel_chunks(n, 8, [&](size_t b, size_t e, int) {
+    if (avx) decode_avx2(bits, scale, b, e, dst, dst2);
+    else decode_scalar(bits, scale, b, e, dst, dst2);
+  });
+}
+
+void add_fast(float* values, const float* delta, size_t n) {
+  parallel_chunks(n, 16, [&](size_t b, size_t e, int) {
+    for (size_t i = b; i < e; i++) values[i] += delta[i];
+  });
+}
+
+void sub_add_fast(float* values, const float* neu, const float* old, size_t n) {
+  parallel_chunks(n, 16, [&](size_t b, size_t e, int) {
+    for (size_t i = b; i < e; i++) values[i] += neu[i] - old[i];
+  });
+}
+
+void copy_fast(float* dst, const float* src, size_t n) {
+  parallel_chunks(n, 16, [&](size_t b, size_t e, int) { std::memcpy(dst + b, src + b, (e - b) * sizeof(float)); });
+}
+
+double encode_block_fast(const float* v, float* k, size_t n, int block, const BlockGate& gate, uint32_t* words,
+                         uint8_t* scales) {
+  double worst[64];
+  for (int i = 0; i < 64; i++) worst[i] = 0.0;
+  parallel_chunks(n, size_t(block), [&](size_t b, size_t e, int idx) {
+    worst[idx] = encode_block(v + b, k + b, e - b, block, gate, words + b / 32, scales + b / size_t(block));
+  });
+  double w = 0.0;
+  for (int i = 0; i < 64; i++)
+    if (worst[i] > w) w = worst[i];
+  return w;
+}
+
+void decode_block_add_fast(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst, float* dst2) {
+  parallel_chunks(n, size_t(block), [&](size_t b, size_t e, int) {
+    decode_block_add(words + b / 32, scales + b / size_t(block), e - b, block, dst + b, dst2 ? dst2 + b : nullptr);
+  });
+}
+
+}  // namespace st

@@ -176,17 +176,22 @@ void CpuNode::tx_loop(Edge* e) {
       if (B == 0) {
         // smallest step worth sending, relative to the replica's largest element: a step of at least
         // 2^-22 of it is a whole number of ulps of every element, so it can never round away
-        float min_scale = cfg_.min_scale_abs;
-        if (cfg_.min_scale_rel > 0.0f) {
-          float vmax = 0.0f;
-          for (size_t i = 0; i < n; i++) {
-            float a = std::fabs(values_[i]);
-            if (a > vmax) vmax = a;
+        float scale;
+        if (cfg_.tcp_rule == 1) {
+          scale = encode_tensor_fast(values_.data(), e->mirror.data(), n, frame.data() + 4, cfg_.min_scale_abs, cfg_.min_scale_rel);
+        } else {
+          float min_scale = cfg_.min_scale_abs;
+          if (cfg_.min_scale_rel > 0.0f) {
+            float vmax = 0.0f;
+            for (size_t i = 0; i < n; i++) {
+              float a = std::fabs(values_[i]);
+              if (a > vmax) vmax = a;
+            }
+            float rel = vmax * cfg_.min_scale_rel;
+            if (rel > min_scale) min_scale = rel;
           }
-          float rel = vmax * cfg_.min_scale_rel;
-          if (rel > min_scale) min_scale = rel;
+          scale = encode_tensor(values_.data(), e->mirror.data(), n, frame.data() + 4, min_scale, cfg_.tcp_rule);
         }
-        float scale = encode_tensor(values_.data(), e->mirror.data(), n, frame.data() + 4, min_scale, cfg_.tcp_rule);
         std::memcpy(frame.data(), &scale, 4);
         noop = scale == 0.0f;
         e->st.last_scale_sent = scale;
@@ -198,7 +203,7 @@ void CpuNode::tx_loop(Edge* e) {
         // words need 4-byte alignment: ns may be odd, so encode into an aligned scratch
         static thread_local std::vector<uint32_t> wtmp;
         wtmp.assign(block_words(n), 0u);
-        double ss = encode_block(values_.data(), e->mirror.data(), n, B, cfg_.gate, wtmp.data(), scales);
+        double ss = encode_block_fast(values_.data(), e->mirror.data(), n, B, cfg_.gate, wtmp.data(), scales);
         std::memcpy(words, wtmp.data(), 4 * wtmp.size());
         noop = true;
         int maxc = 0;
@@ -269,13 +274,13 @@ void CpuNode::rx_loop(Edge* e) {
         edge_failed(e, "malformed frame (scale)", IoStatus::Error);
         break;
       }
-      decode_tensor_add(frame.data() + 4, scale, n, values_.data(), e->mirror.data());
+      decode_tensor_add_fast(frame.data() + 4, scale, n, values_.data(), e->mirror.data());
       level = scale;
     } else {
       size_t ns = block_scales(n, B);
       wtmp.resize(block_words(n));
       std::memcpy(wtmp.data(), frame.data() + ns, 4 * wtmp.size());
-      decode_block_add(wtmp.data(), frame.data(), n, B, values_.data(), e->mirror.data());
+      decode_block_add_fast(wtmp.data(), frame.data(), n, B, values_.data(), e->mirror.data());
       int maxc = 0;
       for (size_t i = 0; i < ns; i++)
         if (frame[i] > maxc) maxc = frame[i];
@@ -374,7 +379,7 @@ void CpuNode::add(const float* delta, int64_t n) {
   if (closed_.load()) throw std::runtime_error("shared tensor is closed");
   {
     std::lock_guard<std::mutex> g(mu_);
-    for (int64_t i = 0; i < n_; i++) values_[size_t(i)] += delta[i];
+    add_fast(values_.data(), delta, size_t(n_));
     for (int s = 0; s < kNumSlots; s++) edges_[s].dirty++;
     adds_++;
   }
@@ -386,7 +391,7 @@ void CpuNode::sub_add(const float* neu, const float* old, int64_t n) {
   if (closed_.load()) throw std::runtime_error("shared tensor is closed");
   {
     std::lock_guard<std::mutex> g(mu_);
-    for (int64_t i = 0; i < n_; i++) values_[size_t(i)] += neu[i] - old[i];
+    sub_add_fast(values_.data(), neu, old, size_t(n_));
     for (int s = 0; s < kNumSlots; s++) edges_[s].dirty++;
     adds_++;
   }
@@ -396,7 +401,7 @@ void CpuNode::sub_add(const float* neu, const float* old, int64_t n) {
 void CpuNode::copy_to(float* out, int64_t n) {
   if (n != n_) throw std::invalid_argument("Not the right size!");
   std::lock_guard<std::mutex> g(mu_);
-  std::memcpy(out, values_.data(), size_t(n_) * sizeof(float));
+  copy_fast(out, values_.data(), size_t(n_));
   copies_++;
 }
 

@@ -567,27 +567,12 @@ void GpuReplica::engine_loop() {
           // Two rounds (even and odd parity) replayed as one CUDA graph: one launch instead of six, which is what
           // bounds the round rate of small tensors.  The graph is rebuilt whenever the ring set changes.
           if (!graph_exec_) {
-            cudaGraph_t graph = nullptr;
-            cudaError_t ce = cudaStreamBeginCapture(S(comm_), cudaStreamCaptureModeThreadLocal);
-            if (ce == cudaSuccess) {
-              for (int rr = 0; rr < 2; rr++) {
-                params_.round = rr;
-                launch_round_begin(params_, comm_);
-                launch_round_main(params_, ctas_, comm_);
-                launch_round_publish(params_, comm_);
-              }
-              ce = cudaStreamEndCapture(S(comm_), &graph);
-            }
-            if (ce == cudaSuccess && graph) {
-              cudaGraphExec_t exec = nullptr;
-              ce = cudaGraphInstantiate(&exec, graph, 0);
-              cudaGraphDestroy(graph);
-              if (ce == cudaSuccess) graph_exec_ = exec;
-            }
-            if (!graph_exec_) {
-              cudaGetLastError();
-              cfg_.use_graph = false;  // capture is not available here: plain launches from now on
-            }
+            RoundParams two[2] = {params_, params_};
+            two[0].round = 0;
+            two[1].round = 1;
+            void* exec = nullptr;
+            if (build_round_graph(two, 2, ctas_, &exec) == 0) graph_exec_ = exec;
+            else cfg_.use_graph = false;  // no graphs here: plain launches from now on
           }
           if (graph_exec_) {
             check(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec_), S(comm_)), "cudaGraphLaunch");
@@ -602,7 +587,7 @@ void GpuReplica::engine_loop() {
           check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
           check(launch_round_publish(params_, comm_), "round_publish kernel");
           launches_ += 3;
-          graph_warm_ = true;  // the kernels' attributes are set: later rounds may be captured
+          graph_warm_ = true;  // the kernels' attributes are set: later rounds may be replayed from a graph
         }
         // the work count of this round tells the thread whether anything is moving
         cudaMemcpyAsync(status_host_ + kStLastWorkCount, status_ + kStLastWorkCount, 8, cudaMemcpyDeviceToHost, S(comm_));

@@ -705,6 +705,58 @@ static int launch_main_t(const RoundParams& p, int ctas, cudaStream_t stream) {
   return int(cudaGetLastError());
 }
 
+// The rounds `rounds[0..count)` as one executable graph: begin -> main -> publish of each, chained.  The graph is
+// built node by node, not by stream capture: while any stream of a device is capturing, a device-wide
+// synchronisation from any other thread (a user's cudaDeviceSynchronize) fails, and the engine thread builds its
+// graph at times the user cannot know.
+int build_round_graph(const RoundParams* rounds, int count, int ctas, void** exec_out) {
+  *exec_out = nullptr;
+  constexpr int G = 3;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaGraphCreate(&graph, 0);
+  if (e != cudaSuccess) return int(e);
+  cudaGraphNode_t prev = nullptr;
+  for (int i = 0; i < count && e == cudaSuccess; i++) {
+    RoundParams p = rounds[i];
+    if (p.n_links < 1 || p.n_links > kMaxLinks) {
+      e = cudaErrorInvalidValue;
+      break;
+    }
+    const int smem = group_layout(p.payload_bytes, G).total;
+    e = cudaFuncSetAttribute(round_main_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) break;
+    void* args[1] = {&p};  // copied into the node when it is added
+    const unsigned tile_blocks = unsigned((p.n_tiles + 255) / 256);
+    struct {
+      void* fn;
+      unsigned grid, block, smem;
+    } k[3] = {{reinterpret_cast<void*>(round_begin_kernel), tile_blocks, 256u, 0u},
+              {reinterpret_cast<void*>(round_main_kernel<G>), unsigned(ctas), unsigned(G * kGroupThreads), unsigned(smem)},
+              {reinterpret_cast<void*>(round_publish_kernel), tile_blocks, 256u, 0u}};
+    for (int j = 0; j < 3 && e == cudaSuccess; j++) {
+      cudaKernelNodeParams np = {};
+      np.func = k[j].fn;
+      np.gridDim = dim3(k[j].grid);
+      np.blockDim = dim3(k[j].block);
+      np.sharedMemBytes = k[j].smem;
+      np.kernelParams = args;
+      np.extra = nullptr;
+      cudaGraphNode_t node = nullptr;
+      e = cudaGraphAddKernelNode(&node, graph, prev ? &prev : nullptr, prev ? 1 : 0, &np);
+      prev = node;
+    }
+  }
+  cudaGraphExec_t exec = nullptr;
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return int(e);
+  }
+  *exec_out = exec;
+  return 0;
+}
+
 int launch_round_main(const RoundParams& p, int ctas, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (p.n_links < 1 || p.n_links > kMaxLinks) return int(cudaErrorInvalidValue);

@@ -98,6 +98,8 @@ constexpr uint64_t kErrBarrierTimeout = 1, kErrBadCtrl = 2;
 int launch_round_begin(const RoundParams& p, void* stream);
 int launch_round_publish(const RoundParams& p, void* stream);
 int launch_round_main(const RoundParams& p, int ctas, void* stream);
+// `count` rounds chained into one executable graph (a cudaGraphExec_t), built without stream capture.
+int build_round_graph(const RoundParams* rounds, int count, int ctas, void** exec_out);
 int round_main_smem_bytes(int n_links, int n_in, int payload_bytes, int* stages_out);
 
 // Element-wise kernels (copyToTensor / addFromTensor / pushUpdate; src/sharedtensor.c:435-446, 334-344).

@@ -60,7 +60,7 @@ def main():
     out = ROOT / "sharedtensor_b200" / "build" / "sanitize"
     out.mkdir(parents=True, exist_ok=True)
     so = out / f"_core_{kind}.so"
-    src = [ROOT / "sharedtensor_b200" / "csrc" / "core" / f for f in ("codec.cpp", "tree.cpp", "node.cpp", "bindings.cpp")]
+    src = [ROOT / "sharedtensor_b200" / "csrc" / "core" / f for f in ("codec.cpp", "codec_fast.cpp", "tree.cpp", "node.cpp", "bindings.cpp")]
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-fPIC", "-shared", f"-fsanitize={kind}", "-fno-omit-frame-pointer", "-ffp-contract=off",
            "-pthread", f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{ROOT / 'sharedtensor_b200' / 'csrc'}",
            *map(str, src), "-o", str(so)]

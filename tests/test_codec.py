@@ -184,3 +184,54 @@ def test_segment_sumsq():
     x = torch.arange(10, dtype=torch.float32)
     out = core.segment_sumsq(x.data_ptr(), [0, 3, 3, 10])
     assert out == [5.0, 0.0, float((x[3:] ** 2).sum())]
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 1000, 65537, 2_100_003])
+def test_fast_paths_are_bit_identical_to_the_plain_codec(n):
+    """The AVX2 / multi-threaded host paths (the sizes cover the scalar tail, one thread and several threads) give
+    exactly the bits, the scale and the mirror of the plain loops, NaNs and exact zeros included."""
+    P = lambda t: t.data_ptr()  # noqa: E731
+    g = torch.Generator().manual_seed(n)
+    v = torch.randn(n, generator=g)
+    k = torch.randn(n, generator=g) * 0.5
+    if n > 100:
+        v[5] = float("nan")
+        v[17] = 0.0
+        k[17] = 0.0
+    k1, k2 = k.clone(), k.clone()
+    b1 = torch.zeros((n + 7) // 8, dtype=torch.uint8)
+    b2 = torch.full_like(b1, 0xAA)
+    vmax = float(torch.nan_to_num(v.abs(), nan=0.0).max())
+    s1 = core.encode_tensor(P(v), P(k1), n, P(b1), vmax * 2.0 ** -22, 1)
+    s2 = core.encode_tensor_fast(P(v), P(k2), n, P(b2), 0.0, 2.0 ** -22)
+    assert s1 == s2 and s1 > 0
+    assert torch.equal(b1, b2)
+    assert torch.equal(torch.nan_to_num(k1, nan=7.0), torch.nan_to_num(k2, nan=7.0))
+    # a frame below the cut-off: bits only, the mirror stays
+    k3 = k.clone()
+    assert core.encode_tensor_fast(P(v), P(k3), n, P(b2), 1e9, 0.0) == 0.0
+    assert torch.equal(torch.nan_to_num(k3, nan=7.0), torch.nan_to_num(k, nan=7.0))
+    k4 = k.clone()
+    core.encode_tensor(P(v), P(k4), n, P(b1), 1e9, 1)
+    assert torch.equal(b1, b2)
+    # decode
+    d1 = torch.randn(n, generator=g)
+    d2, m1, m2 = d1.clone(), torch.zeros(n), torch.zeros(n)
+    core.decode_tensor_add(P(b1), 0.25, n, P(d1), P(m1))
+    core.decode_tensor_add_fast(P(b1), 0.25, n, P(d2), P(m2))
+    assert torch.equal(d1, d2) and torch.equal(m1, m2)
+    # block format, cut into block-aligned pieces
+    v = torch.randn(n, generator=g)
+    k1, k2 = k.clone(), k.clone()
+    B = 64
+    w1 = torch.zeros((n + 31) // 32, dtype=torch.int32)
+    w2 = torch.zeros_like(w1)
+    c1 = torch.zeros((n + B - 1) // B, dtype=torch.uint8)
+    c2 = torch.zeros_like(c1)
+    r1 = core.encode_block(P(v), P(k1), n, B, -100, 22, P(w1), P(c1))
+    r2 = core.encode_block_fast(P(v), P(k2), n, B, -100, 22, P(w2), P(c2))
+    assert r1 == r2 and torch.equal(w1, w2) and torch.equal(c1, c2) and torch.equal(k1, k2)
+    a1, a2 = torch.zeros(n), torch.zeros(n)
+    core.decode_block_add(P(w1), P(c1), n, B, P(a1), 0)
+    core.decode_block_add_fast(P(w1), P(c1), n, B, P(a2), 0)
+    assert torch.equal(a1, a2)
