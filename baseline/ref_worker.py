@@ -14,6 +14,7 @@ import ctypes
 import json
 import os
 import resource
+import select
 import subprocess
 import sys
 import time
@@ -101,14 +102,11 @@ def _serve() -> None:
 class RefWorker:
     """Client handle of one reference replica process."""
 
-    def __init__(self, n: int, threads: int = 2):
+    def __init__(self, n: int, threads: int = 2, call_timeout: float = 600.0):
+        self.call_timeout = call_timeout
         need = n // 8 + (64 << 20)
         soft, hard = resource.getrlimit(resource.RLIMIT_STACK)
         want = need if hard == resource.RLIM_INFINITY else min(need, hard)
-
-        def _limits():
-            if soft != resource.RLIM_INFINITY and soft < want:
-                resource.setrlimit(resource.RLIMIT_STACK, (want, hard))
 
         # The reference adds into four malloc()ed arrays it never clears (src/sharedtensor.c:367-370).
         # glibc's perturb tunable set to 255 makes malloc hand out zero-filled blocks (the thread
@@ -116,13 +114,24 @@ class RefWorker:
         # start state its author assumed.
         env = dict(os.environ, REF_WORKER_THREADS=str(threads),
                    GLIBC_TUNABLES="glibc.malloc.tcache_count=0:glibc.malloc.perturb=255")
-        self.proc = subprocess.Popen([sys.executable, str(Path(__file__).resolve()), "--serve"], stdin=subprocess.PIPE,
-                                     stdout=subprocess.PIPE, text=True, preexec_fn=_limits, env=env)
+        # The stack limit has to be raised before the worker starts (its frame buffers are stack arrays of n/8
+        # bytes, src/sharedtensor.c:118, 144, and glibc sizes thread stacks from the limit at program start).
+        # A shell does it: a preexec_fn would run Python between fork and exec in a parent that has threads.
+        cmd = [sys.executable, str(Path(__file__).resolve()), "--serve"]
+        if soft != resource.RLIM_INFINITY and soft < want:
+            cmd = ["bash", "-c", f'ulimit -s {want // 1024} 2>/dev/null; exec "$0" "$@"'] + cmd
+        self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
 
-    def call(self, **req) -> dict:
+    def call(self, timeout: float | None = None, **req) -> dict:
+        """One request, one reply line.  The reference can block for good (a joiner whose tree holds only zeros,
+        src/sharedtensor.c:385): after `timeout` seconds without a reply the call raises instead of waiting on."""
         assert self.proc.stdin and self.proc.stdout
         self.proc.stdin.write(json.dumps(req) + "\n")
         self.proc.stdin.flush()
+        timeout = self.call_timeout if timeout is None else timeout
+        ready, _, _ = select.select([self.proc.stdout], [], [], timeout)
+        if not ready:
+            raise RuntimeError(f"reference worker did not answer {req.get('op')!r} within {timeout:.0f} s")
         line = self.proc.stdout.readline()
         if not line:
             raise RuntimeError(f"reference worker died (exit code {self.proc.poll()})")

@@ -131,6 +131,9 @@ def run_ours(args) -> dict | None:
     rank, local_rank, world = env_rank()
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N>1")
+    # host threads and pinned buffers on the socket next to this rank's GPU (matters once 8 ranks copy at once)
+    from sharedtensor_b200.utils.affinity import bind_to_gpu
+    cpus = bind_to_gpu(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     cu = _native.cuda()
@@ -358,6 +361,7 @@ def run_ours(args) -> dict | None:
                    "delta": "N(0,1e-3) fp32", "cadence_ms": list(CADENCE_MS), "scale_block": 32,
                    "applied_when": f"rel-L2 of outstanding update <= {TOL} on every replica",
                    "l2": "inputs larger than L2 (400 MB per array)",
+                   "host_cpus_bound": len(cpus),
                    "e2e_pipeline": "host->device copy of step j+1 overlaps step j (two staging buffers, copy stream); "
                                    "the host waits for and reads every step's result"},
         "final_rel_err": rel, "gpu_launches": launches, "clocks": clocks,

@@ -534,10 +534,16 @@ void GpuReplica::set_doorbell(std::function<void()> fn) {
 }
 
 void GpuReplica::local_update() {
-  if (!wake(false)) return;
+  const bool was_idle = wake(false);
+  // Ring the neighbours when this engine had been pausing (theirs then are, too) or when there is no engine thread
+  // here at all (rounds driven by the caller): at most one doorbell per 200 us.
+  if (!was_idle && engine_on_.load()) return;
+  const auto now = std::chrono::steady_clock::now();
   std::function<void()> fn;
   {
     std::lock_guard<std::mutex> g(wake_mu_);
+    if (now - last_ring_ < std::chrono::microseconds(200)) return;
+    last_ring_ = now;
     fn = doorbell_;
   }
   if (fn) fn();
@@ -609,7 +615,7 @@ void GpuReplica::engine_loop() {
       // burst and an idle replica costs next to nothing
       idle_rounds++;
       if (idle_rounds > 2 && cfg_.idle_sleep_us > 0) {
-        uint64_t shift = idle_rounds - 3 > 6 ? 6 : idle_rounds - 3;
+        uint64_t shift = idle_rounds - 3 > 10 ? 10 : idle_rounds - 3;
         uint64_t us = 10ull << shift;
         if (us > uint64_t(cfg_.idle_sleep_us)) us = uint64_t(cfg_.idle_sleep_us);
         idle_.store(true);

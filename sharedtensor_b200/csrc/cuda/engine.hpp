@@ -8,6 +8,7 @@
 // tearing is impossible, per-tensor tearing is allowed, as in the reference, src/sharedtensor.c:442-444).
 #pragma once
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdint>
 #include <functional>
@@ -29,7 +30,7 @@ struct GpuConfig {
   int comm_ctas = 0;         // 0 = one CTA per SM
   bool shareable = true;     // allocate edge blocks and values with the VMM API (needed across processes)
   int rounds_in_flight = 2;
-  int idle_sleep_us = 200;   // longest pause of the engine thread between rounds while nothing moves
+  int idle_sleep_us = 1000;  // longest pause of the engine thread between rounds while nothing moves
   int round_interval_us = 0; // pause after every busy round (0 = run rounds back to back)
   int frames_per_round = 1;  // successive 1-bit frames per link and round (1..3)
   bool use_graph = true;     // the engine thread replays pairs of rounds as a CUDA graph
@@ -166,6 +167,7 @@ class GpuReplica {
   std::condition_variable wake_cv_;
   bool wake_pending_ = false;          // under wake_mu_
   std::function<void()> doorbell_;     // under wake_mu_
+  std::chrono::steady_clock::time_point last_ring_{};  // under wake_mu_
   void local_update();                 // wake + doorbell if the engine was idle
   void idle_pause(uint64_t us);
   std::atomic<uint64_t> launches_{0};

@@ -36,7 +36,7 @@ class Config:
     engine: str = "thread"           # thread: free-running rounds on a comm stream | manual: caller drives step()
     comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
     rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
-    idle_sleep_us: int = 200         # longest engine pause while nothing moves (backs off from 10 us)
+    idle_sleep_us: int = 1000        # longest engine pause while nothing moves (backs off from 10 us; doorbells end it)
     round_interval_us: int = 0       # pause after every busy round: caps the round rate (a rate limit for GPU edges)
     use_graph: bool = True           # engine thread replays pairs of rounds as one CUDA graph
     poll_deadline_us: int = 1000     # upper bound of every device-side wait

@@ -24,3 +24,13 @@ def test_save_refound_and_restore(tmp_path, free_port):
         assert torch.equal(out, v)
     finally:
         b.close()
+
+
+def test_cpu_affinity_helper_is_a_no_op_without_a_gpu():
+    import os
+
+    from sharedtensor_b200.utils.affinity import bind_to_gpu
+
+    before = os.sched_getaffinity(0)
+    assert bind_to_gpu(0) == sorted(before)     # no NVML device here: nothing to intersect with
+    assert os.sched_getaffinity(0) == before

@@ -84,7 +84,7 @@ def test_gpu_child_below_reference_master(free_port):
     n = 240
     torch.manual_seed(2)
     init = torch.randn(n)
-    ref = RefWorker(n)
+    ref = RefWorker(n, call_timeout=60.0)
     g = None
     try:
         ref.call(op="create", host="127.0.0.1", port=free_port, n=n, values=init.tolist())

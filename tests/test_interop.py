@@ -34,7 +34,7 @@ def test_our_node_below_reference_master(free_port):
     n = 240
     torch.manual_seed(0)
     init = torch.randn(n)
-    ref = RefWorker(n)
+    ref = RefWorker(n, call_timeout=60.0)
     ours = None
     try:
         ref.call(op="create", host="127.0.0.1", port=free_port, n=n, values=init.tolist())
@@ -64,10 +64,15 @@ def test_reference_nodes_below_our_master_with_redirect(free_port):
     torch.manual_seed(1)
     init = torch.randn(n)
     ours = sharedtensor.createOrFetch("127.0.0.1", free_port, init)
-    refs = [RefWorker(n) for _ in range(3)]
+    refs = [RefWorker(n, call_timeout=60.0) for _ in range(3)]
     try:
+        # One phase at a time: the reference updates its arrays from several threads without any synchronisation
+        # (src/sharedtensor.c:106-111 against 166-174), so a joiner that arrives while its reference parent is
+        # still receiving its own state can lose increments for good.  Every replica is checked before the next
+        # process joins or speaks.
         for r in refs:
             r.call(op="create", host="127.0.0.1", port=free_port, n=n)
+            assert _poll(lambda r=r: _close_to(r.call(op="copy")["values"], init, 2e-4)), "state transfer to a reference joiner"
         st = ours.stats()
         assert st["edges"]["left"]["state"] == "connected" and st["edges"]["right"]["state"] == "connected"
         assert st["redirects"] == 1
