@@ -1,6 +1,6 @@
 """Builds the unmodified reference into ``baseline/_ref/libsharedtensor_ref.so``.
 
-``pip install /root/reference`` cannot work (the reference is a Lua rock with neither setup.py nor
+Installing the reference with pip cannot work (it is a Lua rock with neither setup.py nor
 pyproject.toml), so the one C file is copied verbatim into ``baseline/_ref/`` and compiled together
 with ``ref_host.c``, which stands in for the Lua interpreter.  The copy is made where the reference
 checkout is mounted; on a machine that only has the repository snapshot the already copied file and
@@ -8,6 +8,7 @@ the already built library are used as they are.
 """
 from __future__ import annotations
 
+import os
 import shutil
 import subprocess
 import sys
@@ -15,7 +16,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REF_DIR = HERE / "_ref"
-REF_SRC = Path("/root/reference/src/sharedtensor.c")
+# where the reference checkout is mounted (override with SHAREDTENSOR_REFERENCE_DIR)
+REF_SRC = Path(os.environ.get("SHAREDTENSOR_REFERENCE_DIR", "/root/reference")) / "src" / "sharedtensor.c"
 LIB = REF_DIR / "libsharedtensor_ref.so"
 
 

@@ -2,7 +2,7 @@
 """Sync bandwidth / latency sweep over tensor sizes (1 Ki .. 1 Gi fp32 elements, powers of 4).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29500 \
-        benchmarks/sync_sweep.py [--max-log4 15] [--out gpurun_out/sweep.json]
+        benchmarks/sync_sweep.py [--max-log4 15] [--out sweep.json]
 
 For every size and the N ranks of one box it measures, with deltas ~ N(0,1):
   * the compressed path of this framework: device time of one sync round under load (max over ranks), the

@@ -2,7 +2,7 @@
 """Async data-parallel training on a shared tensor vs. synchronous all-reduce training.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29500 \
-        benchmarks/train.py --model char_rnn|gpt2 --mode async|sync --steps 200 [--out gpurun_out/train.json]
+        benchmarks/train.py --model char_rnn|gpt2 --mode async|sync --steps 200 [--out train.json]
 
 char_rnn: 2-layer LSTM, hidden 512, vocabulary 65, sequence 50, batch 64 per GPU, fp32, SGD lr 2e-3, all
           parameters in one shared tensor.

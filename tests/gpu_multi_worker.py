@@ -25,11 +25,48 @@ def _touch_and_wait(sync_dir, name, wanted, timeout=100.0):
     raise RuntimeError(f"rendezvous timed out waiting for {wanted}")
 
 
+def train(rank, world, port, sync_dir, dev):
+    """Async trainers whose sync rounds are queued by the trainer itself (engine="manual", one round per step)."""
+    from sharedtensor_b200.models import CharRNN, flatten_parameters
+    from sharedtensor_b200.parallel.trainers import AsyncTrainer, structured_token_batches
+
+    torch.manual_seed(5)
+    model = CharRNN(vocab=13, hidden=24, layers=1).to(dev)
+    init, _ = flatten_parameters(model, align=32)
+    _touch_and_wait(sync_dir, f"up_{rank}", [f"joined_{r}" for r in range(rank)])
+    st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros_like(init), engine="manual", rel_bits=14)
+    (Path(sync_dir) / f"joined_{rank}").touch()
+    _touch_and_wait(sync_dir, f"in_{rank}", [f"in_{r}" for r in range(world)])
+    tr = AsyncTrainer(model, st, lr=0.3, rounds_per_step=1)
+    log = tr.run(structured_token_batches(13, 8, 10, dev, seed=10 + rank, period=1), steps=120, log_every=119)
+    _touch_and_wait(sync_dir, f"trained_{rank}", [f"trained_{r}" for r in range(world)])
+    # nobody has an engine thread: everybody keeps queueing rounds until all replicas have gone quiet
+    deadline = time.time() + 20
+    while time.time() < deadline:
+        if st.flush(0.05):
+            (Path(sync_dir) / f"quiet_{rank}").touch()
+        if all((Path(sync_dir) / f"quiet_{r}").exists() for r in range(world)):
+            break
+    for _ in range(20):
+        st.step(1)
+    out = torch.empty_like(init)
+    st.copyToTensor(out)
+    torch.cuda.synchronize()
+    s = st.stats()
+    print(json.dumps({"rank": rank, "loss_first": log.loss[0], "loss_last": log.loss[-1], "checksum": float(out.double().sum()),
+                      "norm": float(out.double().norm()), "errors": s["device"]["errors"], "rounds": s["device"]["rounds"]}), flush=True)
+    _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(world)])
+    time.sleep(0.2 + 0.3 * (world - rank))
+    st.close()
+
+
 def main():
     sync_dir = os.environ["ST_TEST_SYNC_DIR"]
     rank, world, port, n, scenario = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
     torch.cuda.set_device(rank % torch.cuda.device_count())
     dev = torch.device("cuda", torch.cuda.current_device())
+    if scenario == "train":
+        return train(rank, world, port, sync_dir, dev)
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
     init = torch.randn(n, generator=g, device=dev)

@@ -79,3 +79,15 @@ def test_rank_leaves_between_steps(free_port):
         assert r["rel_after_loss"] < 5e-5, r
     assert res[0]["edge_failures"] == 1, "the master lost its right child and noticed it on the host"
     assert res[0]["edges"]["right"] == "free"
+
+
+def test_trainers_that_queue_their_own_rounds(free_port):
+    """T8 on GPUs: two async trainers, no engine thread, one sync round queued behind every update; the loss falls
+    on both and the replicas end up equal."""
+    _need(2)
+    res = _run(2, free_port, 0, "train")
+    for r in res:
+        assert r["errors"] == 0
+        assert r["loss_last"] < 0.8 * r["loss_first"], r
+        assert r["rounds"] >= 120
+    assert abs(res[0]["checksum"] - res[1]["checksum"]) <= 1e-3 * res[0]["norm"], res
