@@ -30,6 +30,8 @@ def main():
     ap.add_argument("--links", type=int, default=1)
     ap.add_argument("--frames", type=int, default=3)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--hub-mode", default="both", choices=["both", "rx", "tx"],
+                    help="what the timed hub round does: receive and send, receive only, send only")
     args = ap.parse_args()
     cu = _native.cuda()
     n = args.elements
@@ -79,7 +81,7 @@ def main():
             leaf.add(d.data_ptr(), leaf.comm_stream())
             leaf.round()
             leaf.sync()
-        timed("round(hub)", lambda: hub.round(), ext)
+        timed("round(hub)", lambda: hub.round(args.hub_mode != "tx", args.hub_mode != "rx"), ext)
     med = {k: sorted(v)[len(v) // 2] for k, v in times.items()}
     alg = {"add": 12 * n, "sub_add": 16 * n, "snapshot_f32": 8 * n, "snapshot_bf16": 6 * n, "add_scaled_bf16": 10 * n,
            "table_scales": 4 * n, "round(hub)": (8 + 8 * args.links) * n}
