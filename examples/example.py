@@ -5,10 +5,13 @@ iteration and prints what it sees.  Pass ``cuda`` as the first argument to keep 
 """
 import sys
 import time
+from pathlib import Path
 
 import torch
 
-import sharedtensor
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))  # run from a checkout without installing
+
+import sharedtensor  # noqa: E402
 
 device = "cuda" if len(sys.argv) > 1 and sys.argv[1] == "cuda" else "cpu"
 x = torch.arange(1, 5, dtype=torch.float32, device=device)
