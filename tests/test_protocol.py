@@ -1,4 +1,5 @@
 """T2: the tree-join wire protocol, byte for byte (reference src/sharedtensor.c:192-242, 244-332)."""
+import math
 import socket
 import struct
 import time
@@ -115,3 +116,53 @@ def test_size_mismatch_is_an_error(free_port):
         assert torch.equal(out, torch.ones(4, 5, 6, 2))
     finally:
         st.close()
+
+
+def test_frames_of_the_reference_binary_decode_with_our_codec(free_port):
+    """T0/T2 against the real thing: a raw socket joins an unmodified reference master, gets the one byte 'Y', and the
+    frames the reference then streams (4-byte scale + ceil(n/8) sign bytes, src/sharedtensor.c:156-177), decoded by
+    our codec into a zeroed buffer, add up to the reference's values."""
+    import sys
+    from pathlib import Path
+
+    import pytest
+
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "baseline"))
+    import build_ref
+    from ref_worker import RefWorker
+
+    from sharedtensor_b200 import _native
+
+    if build_ref.build() is None:
+        pytest.skip("reference source not available")
+    core = _native.core()
+    n = 240
+    torch.manual_seed(3)
+    init = torch.randn(n)
+    ref = RefWorker(n, call_timeout=60.0)
+    try:
+        ref.call(op="create", host="127.0.0.1", port=free_port, n=n, values=init.tolist())
+        c = _connect(free_port)
+        assert _recv_exact(c, 1) == b"Y"
+        got = torch.zeros(n)
+        nbytes = (n + 7) // 8
+        prev_scale = None
+        err = float("inf")
+        for i in range(4000):
+            frame = _recv_exact(c, 4 + nbytes)
+            scale = struct.unpack("<f", frame[:4])[0]
+            assert scale >= 0.0 and scale == scale
+            if scale > 0.0:  # every scale is a power of two, and the stream's scales never grow
+                m, _ = math.frexp(scale)
+                assert m == 0.5
+                assert prev_scale is None or scale <= prev_scale
+                prev_scale = scale
+            bits = torch.frombuffer(bytearray(frame[4:]), dtype=torch.uint8)
+            core.decode_tensor_add(bits.data_ptr(), scale, n, got.data_ptr(), 0)
+            err = (got - init).abs().max().item()
+            if err <= 1e-3:
+                break
+        assert err <= 1e-3, f"after {i + 1} frames the decoded stream is still {err} away"
+        c.close()
+    finally:
+        ref.kill()
