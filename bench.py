@@ -45,11 +45,19 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--elements", type=int, default=N_ELEMENTS)
     ap.add_argument("--probes", type=int, default=24, help="single-update latency probes after the timed region")
-    ap.add_argument("--topology", default="tree", choices=["tree", "mesh"])
+    ap.add_argument("--topology", default="auto", choices=["auto", "tree", "mesh"],
+                    help="auto: the fixed fully connected group when the ranks are known up front (N > 1 under "
+                         "torch.distributed.run), else the join tree; the other one is measured too and reported under "
+                         "other_topology")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the comparison run on the other topology")
     ap.add_argument("--ref-time-cap", type=float, default=120.0, help="wall-clock cap of the reference arm's wait, seconds")
     return ap.parse_args()
+
+
+def resolve_topology(args, world: int) -> None:
+    if args.topology == "auto":
+        args.topology = "mesh" if world > 1 else "tree"
 
 
 def env_rank():
@@ -131,6 +139,7 @@ def run_ours(args) -> dict | None:
     rank, local_rank, world = env_rank()
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N>1")
+    resolve_topology(args, world)
     # host threads and pinned buffers on the socket next to this rank's GPU (matters once 8 ranks copy at once)
     from sharedtensor_b200.utils.affinity import bind_to_gpu
     cpus = bind_to_gpu(local_rank)
