@@ -20,6 +20,9 @@ sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 import sharedtensor  # noqa: E402
 
 
+SAMPLE = 64
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--elements", type=float, default=1e8)
@@ -48,19 +51,21 @@ def main() -> None:
         b.flush(args.timeout)
         a.copyToTensor(expect)
         total = torch.zeros(n)
+        for j in range(steps):  # what is about to be added, summed before the clock starts
+            total += deltas[j % 2]
+        # the check looks at every 64th element (like bench.py's device-side check): a full-tensor norm per poll
+        # would take longer than a frame and keep the replica's lock busy
+        es, outstanding = (expect + total)[::SAMPLE].clone(), float(total[::SAMPLE].norm())
         t0 = time.perf_counter()
         for j in range(steps):
             a.addFromTensor(deltas[j % 2])
-            total += deltas[j % 2]
-        expect.add_(total)
-        outstanding = float(total.norm())
         rel = float("inf")
         while time.perf_counter() - t0 < args.timeout:
             b.copyToTensor(out)
-            rel = float((out - expect).norm()) / outstanding
+            rel = float((out[::SAMPLE] - es).norm()) / outstanding
             if rel <= args.tol:
                 break
-            time.sleep(0.002)
+            time.sleep(0.01)
         return time.perf_counter() - t0, rel
 
     run(args.warmup)
@@ -69,7 +74,7 @@ def main() -> None:
     print(json.dumps({"metric": "applied_updates_per_s", "impl": "ours, CPU node, loopback TCP", "value": args.steps / secs,
                       "elements": n, "steps": args.steps, "seconds": secs, "final_rel_err": rel, "converged": rel <= args.tol,
                       "late_join_state_transfer_s": join_s, "frames_sent": st["frames_sent"], "bytes_sent": st["bytes_sent"],
-                      "tol": args.tol}))
+                      "tol": args.tol, "checked": f"every {SAMPLE}th element"}))
     b.close()
     a.close()
 
