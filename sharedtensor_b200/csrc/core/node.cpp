@@ -96,6 +96,10 @@ bool CpuNode::do_join(bool first, const float* init) {
     listen_addr_ = jr.listen_addr;
     listener_->add_listen_fd(lfd);
   } else {
+    // The new parent knows this node by the source address of the new connection and hands that address to later
+    // joiners: accept joins there too (best effort; the first address stays open for redirects already handed out).
+    int lfd = open_listener(jr.listen_addr, cfg_.listen_backlog, &err);
+    if (lfd >= 0) listener_->add_listen_fd(lfd);
     // Re-join keeping the part of the state the lost parent had not been told yet:
     // values <- values - mirror_up, so that it is sent up the new edge (whose mirror starts at 0)
     // while the new parent streams its whole state down.  Child edges pause meanwhile.

@@ -322,6 +322,7 @@ void GpuReplica::order_user_after(void* user_stream) {
 
 void GpuReplica::load_values(const float* src, void* user_stream) {
   DeviceGuard g(device_);
+  std::lock_guard<std::mutex> gate(gate_mu_);
   {
     std::lock_guard<std::mutex> lk(mu_);
     order_after_user(user_stream);
@@ -336,6 +337,7 @@ void GpuReplica::load_values(const float* src, void* user_stream) {
 
 void GpuReplica::add(const float* delta, void* user_stream) {
   DeviceGuard g(device_);
+  std::lock_guard<std::mutex> gate(gate_mu_);
   {
     std::lock_guard<std::mutex> lk(mu_);
     order_after_user(user_stream);
@@ -349,6 +351,7 @@ void GpuReplica::add(const float* delta, void* user_stream) {
 
 void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) {
   DeviceGuard g(device_);
+  std::lock_guard<std::mutex> gate(gate_mu_);
   {
     std::lock_guard<std::mutex> lk(mu_);
     order_after_user(user_stream);
@@ -362,6 +365,7 @@ void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) 
 
 void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) {
   DeviceGuard gd(device_);
+  std::lock_guard<std::mutex> gate(gate_mu_);
   {
     std::lock_guard<std::mutex> lk(mu_);
     order_after_user(user_stream);
@@ -371,6 +375,14 @@ void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) 
     order_user_after(user_stream);
   }
   local_update();
+}
+
+void GpuReplica::add_gate_held(const float* delta) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
+  epoch_++;
+  launches_ += 1;
 }
 
 void GpuReplica::snapshot(float* out, void* user_stream) {
@@ -457,6 +469,7 @@ float GpuReplica::tcp_encode(int link, uint32_t* words, float min_scale_abs, flo
 void GpuReplica::tcp_decode(int link, const uint32_t* words, float scale) {
   if (scale == 0.f) return;
   DeviceGuard g(device_);
+  std::lock_guard<std::mutex> gate(gate_mu_);
   {
     std::lock_guard<std::mutex> lk(mu_);
     if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");

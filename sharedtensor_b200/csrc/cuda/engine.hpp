@@ -76,6 +76,13 @@ class GpuReplica {
   void add(const float* delta, void* user_stream);
   void sub_add(const float* neu, const float* old, void* user_stream);
   void add_scaled_bf16(const void* g_bf16, float alpha, void* user_stream);  // values += alpha * g
+  // While the gate is held every update of the values from outside the rounds (add, sub_add, add_scaled_bf16,
+  // load_values, tcp_decode) waits.  A node that re-joins holds it from the moment it works out what its lost parent
+  // had not been told until that has been added back on top of the new parent's snapshot, so that an update made in
+  // between is neither overwritten by the snapshot nor counted twice.
+  void gate_lock() { gate_mu_.lock(); }
+  void gate_unlock() { gate_mu_.unlock(); }
+  void add_gate_held(const float* delta);   // values += delta on the comm stream; the caller holds the gate
   void snapshot(float* out, void* user_stream);
   void snapshot_bf16(void* out, void* user_stream);
   void copy_mirror_from_values(int link);                 // mirror <- values (neighbour is given a snapshot)
@@ -159,6 +166,7 @@ class GpuReplica {
   void* ev_comm_ = nullptr;            // cudaEvent_t: comm -> user stream
   std::vector<void*> ev_round_;
   mutable std::mutex mu_;
+  std::mutex gate_mu_;                 // taken before mu_ by every update from outside the rounds
   std::mutex engine_mu_;               // serialises start_engine / stop_engine
   std::thread engine_;
   std::atomic<bool> engine_on_{false}, engine_stop_{false};

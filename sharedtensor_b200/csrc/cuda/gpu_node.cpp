@@ -137,12 +137,15 @@ class GpuNode {
     if (rep_) rep_->stop_engine();
     if (listener_) listener_->stop();
     if (unix_fd_ >= 0) ::shutdown(unix_fd_, SHUT_RDWR);
+    for (int fd : extra_unix_fds_) ::shutdown(fd, SHUT_RDWR);
     if (upgrade_thread_.joinable()) upgrade_thread_.join();
     if (watch_thread_.joinable()) watch_thread_.join();
     if (unix_fd_ >= 0) {
       ::close(unix_fd_);
       unix_fd_ = -1;
     }
+    for (int fd : extra_unix_fds_) ::close(fd);
+    extra_unix_fds_.clear();
     for (int s = 0; s < kNumSlots; s++) drop_edge(s, false);
     rep_.reset();
   }
@@ -331,14 +334,16 @@ class GpuNode {
     }
   }
 
-  Hello my_hello() const {
+  Hello my_hello() const { return my_hello(listen_addr_); }
+  // `seen_as`: the source address of the TCP connection this hello belongs to (what the parent matches it by)
+  Hello my_hello(const sockaddr_in& seen_as) const {
     Hello h;
     h.n = n_;
     h.block = gcfg_.block;
     h.ring_slots = gcfg_.ring_slots;
     h.edge_bytes = 0;
     h.values_bytes = rep_->values_block().bytes;
-    h.listen_addr = listen_addr_;
+    h.listen_addr = seen_as;
     h.device = device_;
     return h;
   }
@@ -366,6 +371,7 @@ class GpuNode {
         if (init_dev) rep_->load_values(init_dev, stream);
       }
       listener_->add_listen_fd(lfd);
+      drop_orphan_link();  // became the root: the values are intact, nothing to add back
       {
         std::lock_guard<std::mutex> g(mu_);
         master_.store(true);
@@ -389,6 +395,17 @@ class GpuNode {
         std::fprintf(stderr, "[sharedtensor] %s\n", err.c_str());
         return false;
       }
+    } else {
+      // The new parent knows this node by the source address of the new connection and will hand that address to
+      // later joiners: accept TCP joins and peer-memory hellos there too (the first address stays open for the
+      // redirects already handed out).  Best effort: without it this node is simply never a redirect target.
+      int lfd = open_listener(jr.listen_addr, opt_.listen_backlog, &err);
+      if (lfd >= 0) listener_->add_listen_fd(lfd);
+      int ufd = unix_listen_abstract(unix_name(jr.listen_addr), &err);
+      if (ufd >= 0) {
+        std::lock_guard<std::mutex> g(mu_);
+        extra_unix_fds_.push_back(ufd);
+      }
     }
     master_.store(false);
     bool no_endpoint = false;
@@ -396,11 +413,16 @@ class GpuNode {
       if (no_endpoint) {
         // the parent is a CPU node, the reference, or on another host: speak TCP frames with it.  A node that
         // re-joins keeps only what its lost parent had not been told (like the CPU node).
-        if (!first && carry_valid_) {
-          cudaMemcpy(rep_->values(), carry_, size_t(n_) * 4, cudaMemcpyDeviceToDevice);
-          cudaFree(carry_);
-          carry_ = nullptr;
-          carry_valid_ = false;
+        if (!first && orphan_link_ >= 0) {
+          rep_->gate_lock();
+          float* carry = make_carry();
+          if (carry) {
+            cudaSetDevice(device_);
+            cudaMemcpy(rep_->values(), carry, size_t(n_) * 4, cudaMemcpyDeviceToDevice);
+            cudaFree(carry);
+          }
+          drop_orphan_link();
+          rep_->gate_unlock();
         }
         start_tcp_edge(kSlotUp, jr.fd, jr.parent_addr);
         std::fprintf(stderr, "[sharedtensor] joined %s:%d below %s after %d redirect(s), GPU %d, TCP edge\n", host_.c_str(), port_,
@@ -430,18 +452,21 @@ class GpuNode {
       *no_endpoint = true;
       return false;
     }
-    bool ok = false;
+    // A re-joining node takes its old up link along: its mirror says what the lost parent had been told.
+    const bool reuse = !first && orphan_link_ >= 0;
+    bool ok = false, gate_held = false;
     int block = -1, link = -1;
+    float* carry = nullptr;
     VmmBlock remote;
     do {
       // the hello goes out first, so that the parent knows at once that this child will not speak TCP frames
-      Hello h = my_hello();
+      Hello h = my_hello(jr.listen_addr);
       if (!unix_send_fd(us, -1, &h, sizeof(h))) {
         *err = "hello send failed";
         break;
       }
       block = rep_->alloc_edge_block();
-      link = rep_->add_link();
+      link = reuse ? orphan_link_ : rep_->add_link();
       if (block < 0 || link < 0) {
         *err = "out of links or edge blocks";
         break;
@@ -465,8 +490,20 @@ class GpuNode {
         if (fd_vals >= 0) ::close(fd_vals);
         break;
       }
-      // A re-joining node keeps what its lost parent had not been told: u = values - mirror_up is set
-      // aside now and added back on top of the new parent's snapshot.
+      if (reuse) {
+        // From here until the snapshot has arrived and the carry is back on top of it, nobody else may change the
+        // values: what the lost parent had not been told, u = values - mirror, is set aside now, updates made
+        // while the edge was down included.
+        rep_->gate_lock();
+        gate_held = true;
+        carry = make_carry();
+        if (!carry) {
+          *err = "no memory for the carry";
+          ::close(fd_edge);
+          ::close(fd_vals);
+          break;
+        }
+      }
       const uint64_t sz_edge = rep_->edge_block(block).bytes, sz_vals = rep_->values_block().bytes;
       bool sent = unix_send_fd(us, fd_edge, &sz_edge, 8) && unix_send_fd(us, fd_vals, &sz_vals, 8);
       ::close(fd_edge);
@@ -494,12 +531,9 @@ class GpuNode {
         break;
       }
       rep_->copy_mirror_from_values(link);  // the parent knows exactly what it just gave us
-      if (!first && carry_valid_) {
-        rep_->add(carry_, rep_->comm_stream());
+      if (carry) {
+        rep_->add_gate_held(carry);
         rep_->sync();
-        cudaFree(carry_);
-        carry_ = nullptr;
-        carry_valid_ = false;
       }
       int pid = rep_->attach_peer(link, block, remote.ptr);
       {
@@ -514,28 +548,64 @@ class GpuNode {
         e.remote = remote;
         ready_ = true;
       }
+      if (reuse) orphan_link_ = -1;  // it is the up link again
       cv_.notify_all();
       ok = true;
     } while (false);
+    if (carry) {
+      cudaSetDevice(device_);
+      cudaFree(carry);
+    }
+    if (gate_held) rep_->gate_unlock();
     ::close(us);
     if (!ok) {
       if (remote.ptr) vmm_free(&remote);
-      if (link >= 0) rep_->remove_link(link);
+      if (link >= 0 && !reuse) rep_->remove_link(link);
       if (block >= 0) rep_->free_edge_block(block);
     }
     return ok;
   }
 
+  // u = values - mirror of the lost parent's link, in a scratch buffer (the caller holds the update gate and frees it)
+  float* make_carry() {
+    if (orphan_link_ < 0) return nullptr;
+    cudaSetDevice(device_);
+    float* carry = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&carry), size_t(n_) * 4) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cudaStream_t cs = static_cast<cudaStream_t>(rep_->comm_stream());
+    cudaMemsetAsync(carry, 0, size_t(n_) * 4, cs);
+    launch_sub_add(carry, rep_->values(), rep_->mirror(orphan_link_), n_, nullptr, 0, 0, rep_->comm_stream());
+    rep_->sync();
+    return carry;
+  }
+
+  void drop_orphan_link() {
+    if (orphan_link_ < 0) return;
+    rep_->remove_link(orphan_link_);
+    orphan_link_ = -1;
+  }
+
   // ---- parent side of the upgrade ----
   void upgrade_loop() {
     while (!stop_.load()) {
-      struct pollfd pfd = {unix_fd_, POLLIN, 0};
-      int pr = ::poll(&pfd, 1, kPollMs);
+      std::vector<pollfd> pfds;
+      pfds.push_back({unix_fd_, POLLIN, 0});
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        for (int fd : extra_unix_fds_) pfds.push_back({fd, POLLIN, 0});
+      }
+      int pr = ::poll(pfds.data(), pfds.size(), kPollMs);
       if (pr <= 0) continue;
-      int us = ::accept(unix_fd_, nullptr, nullptr);
-      if (us < 0) continue;
-      serve_upgrade(us);
-      ::close(us);
+      for (auto& pfd : pfds) {
+        if (!(pfd.revents & POLLIN)) continue;
+        int us = ::accept(pfd.fd, nullptr, nullptr);
+        if (us < 0) continue;
+        serve_upgrade(us);
+        ::close(us);
+      }
     }
   }
 
@@ -702,8 +772,8 @@ class GpuNode {
         if (stop_.load()) break;
         std::fprintf(stderr, "[sharedtensor] edge %d lost (neighbour closed its connection)\n", s);
         bool was_up = s == kSlotUp;
-        if (was_up && opt_.rejoin) save_carry();
-        drop_edge(s, true);
+        // the up link of a node that will re-join stays (without its rings): its mirror is what the lost parent knew
+        drop_edge(s, true, was_up && opt_.rejoin);
         if (was_up) {
           if (!opt_.rejoin) {
             master_.store(true);
@@ -726,36 +796,12 @@ class GpuNode {
             if (backoff < 5000) backoff *= 2;
           }
           if (opt_.start_engine && !stop_.load()) rep_->start_engine();
-          if (master_.load() && carry_) {  // became the root: nothing to add back, values are intact
-            cudaFree(carry_);
-            carry_ = nullptr;
-            carry_valid_ = false;
-          }
         }
       }
     }
   }
 
-  // u = values - mirror_up, kept in a scratch buffer until the re-join has a new snapshot to add it to
-  void save_carry() {
-    int link;
-    {
-      std::lock_guard<std::mutex> g(mu_);
-      link = edges_[kSlotUp].link;
-    }
-    if (link < 0) return;
-    cudaSetDevice(device_);
-    if (cudaMalloc(reinterpret_cast<void**>(&carry_), size_t(n_) * 4) != cudaSuccess) {
-      carry_ = nullptr;
-      return;
-    }
-    cudaMemsetAsync(carry_, 0, size_t(n_) * 4, static_cast<cudaStream_t>(rep_->comm_stream()));
-    launch_sub_add(carry_, rep_->values(), rep_->mirror(link), n_, nullptr, 0, 0, rep_->comm_stream());
-    rep_->sync();
-    carry_valid_ = true;
-  }
-
-  void drop_edge(int slot, bool count) {
+  void drop_edge(int slot, bool count, bool keep_link = false) {
     Edge old;
     std::unique_ptr<TcpEdge> te;
     {
@@ -778,7 +824,10 @@ class GpuNode {
     if (!old.state) return;
     if (rep_) {
       if (old.peer_id >= 0) rep_->detach_peer(old.peer_id);
-      if (old.link >= 0) rep_->remove_link(old.link);
+      if (old.link >= 0) {
+        if (keep_link && orphan_link_ < 0) orphan_link_ = old.link;
+        else rep_->remove_link(old.link);
+      }
       if (old.block >= 0) rep_->free_edge_block(old.block);
     }
     if (old.remote.ptr) vmm_free(&old.remote);
@@ -806,8 +855,8 @@ class GpuNode {
   std::atomic<bool> master_{false}, closed_{false}, started_{false}, stop_{false};
   std::thread upgrade_thread_, watch_thread_;
   uint64_t rejoins_ = 0, edge_failures_ = 0;
-  float* carry_ = nullptr;
-  bool carry_valid_ = false;
+  int orphan_link_ = -1;  // the lost parent's link, kept (with its mirror) until a new parent has been found
+  std::vector<int> extra_unix_fds_;  // peer-memory endpoints under the addresses of later up connections
 };
 
 

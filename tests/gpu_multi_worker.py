@@ -60,6 +60,56 @@ def train(rank, world, port, sync_dir, dev):
     st.close()
 
 
+def rejoin(rank, world, port, n, sync_dir, dev):
+    """Host-side fault: rank 1 cuts its own up connection (both ends see EOF), goes on adding while it looks for a
+    parent, and comes back below the master; nothing that was added anywhere may be lost."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    init = torch.randn(n, generator=g, device=dev)
+    _touch_and_wait(sync_dir, f"up_{rank}", [f"joined_{r}" for r in range(rank)])
+    st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), rejoin_backoff_ms=50)
+    (Path(sync_dir) / f"joined_{rank}").touch()
+    d = []
+    for i in range(3):
+        g.manual_seed(50 + i)
+        d.append(torch.randn(n, generator=g, device=dev) * 1e-2)
+    _touch_and_wait(sync_dir, f"in_{rank}", [f"in_{r}" for r in range(world)])
+    expect = init + d[0] + d[1] + d[2]
+    res = {"rank": rank}
+    if rank == 0:
+        st.addFromTensor(d[0])
+    else:
+        st.addFromTensor(d[1])
+        assert st.flush(10.0)             # everything said so far has been delivered
+        st._b.inject_sever("up")
+        for i in range(10):               # keeps adding while the edge is down and while it re-joins
+            st.addFromTensor(d[2] / 10)
+            time.sleep(0.02)
+        deadline = time.time() + 20
+        while time.time() < deadline and st.stats()["rejoins"] < 1:
+            time.sleep(0.02)
+        res["rejoins"] = st.stats()["rejoins"]
+    out = torch.empty(n, device=dev)
+    deadline = time.time() + 30
+    rel = None
+    while time.time() < deadline:
+        st.copyToTensor(out)
+        torch.cuda.synchronize()
+        rel = ((out - expect).norm() / expect.norm()).item()
+        if rel < 5e-5:
+            break
+        time.sleep(0.01)
+    res["rel"] = rel
+    s = st.stats()
+    res["errors"] = s["device"]["errors"]
+    res["edge_failures"] = s.get("edge_failures", 0)
+    res["edges"] = {k: v["state"] for k, v in s["edges"].items()}
+    print(json.dumps(res), flush=True)
+    _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(world)])
+    time.sleep(0.2 + 0.3 * (world - rank))
+    st.close()
+
+
 def main():
     sync_dir = os.environ["ST_TEST_SYNC_DIR"]
     rank, world, port, n, scenario = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
@@ -67,6 +117,8 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     if scenario == "train":
         return train(rank, world, port, sync_dir, dev)
+    if scenario == "rejoin":
+        return rejoin(rank, world, port, n, sync_dir, dev)
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
     init = torch.randn(n, generator=g, device=dev)

@@ -91,3 +91,15 @@ def test_trainers_that_queue_their_own_rounds(free_port):
         assert r["loss_last"] < 0.8 * r["loss_first"], r
         assert r["rounds"] >= 120
     assert abs(res[0]["checksum"] - res[1]["checksum"]) <= 1e-3 * res[0]["norm"], res
+
+
+def test_cut_up_edge_rejoins_without_losing_updates(free_port):
+    """T7 on GPUs, failure made on the host: a replica's up connection is cut, it keeps adding while it re-joins,
+    and every update (before, during and after) ends up on both replicas."""
+    _need(2)
+    res = _run(2, free_port, 3 * 4096 + 17, "rejoin")
+    assert res[1]["rejoins"] == 1
+    assert res[0]["edge_failures"] == 1
+    for r in res:
+        assert r["errors"] == 0
+        assert r["rel"] < 5e-5, res
