@@ -369,6 +369,13 @@ class GpuNode {
           return false;
         }
         if (init_dev) rep_->load_values(init_dev, stream);
+      } else {
+        // took over the tensor's address: joiners will look for the peer-memory endpoint under that address
+        int ufd = unix_listen_abstract(unix_name(jr.listen_addr), &err);
+        if (ufd >= 0) {
+          std::lock_guard<std::mutex> g(mu_);
+          extra_unix_fds_.push_back(ufd);
+        }
       }
       listener_->add_listen_fd(lfd);
       drop_orphan_link();  // became the root: the values are intact, nothing to add back

@@ -110,6 +110,67 @@ def rejoin(rank, world, port, n, sync_dir, dev):
     st.close()
 
 
+def master_leaves(rank, world, port, n, sync_dir, dev):
+    """Host-side failure: the master closes its replica between steps and exits.  Its two children notice on the
+    host, one of them takes over the tensor's address, the other joins below it, and work goes on."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    init = torch.randn(n, generator=g, device=dev)
+    _touch_and_wait(sync_dir, f"up_{rank}", [f"joined_{r}" for r in range(rank)])
+    st = sharedtensor.createOrFetch("127.0.0.1", port, init if rank == 0 else torch.zeros(n, device=dev), rejoin_backoff_ms=50)
+    (Path(sync_dir) / f"joined_{rank}").touch()
+    d = []
+    for i in range(2):
+        g.manual_seed(60 + i)
+        d.append(torch.randn(n, generator=g, device=dev) * 1e-2)
+    _touch_and_wait(sync_dir, f"in_{rank}", [f"in_{r}" for r in range(world)])
+    out = torch.empty(n, device=dev)
+
+    def wait_for(expect, seconds):
+        deadline = time.time() + seconds
+        rel = None
+        while time.time() < deadline:
+            st.copyToTensor(out)
+            torch.cuda.synchronize()
+            rel = ((out - expect).norm() / expect.norm()).item()
+            if rel < 5e-5:
+                break
+            time.sleep(0.01)
+        return rel
+
+    if rank == 0:
+        st.addFromTensor(d[0])
+        st.flush(10.0)
+        _touch_and_wait(sync_dir, "got_0", [f"got_{r}" for r in range(world)])  # the children hold the update
+        time.sleep(0.3)
+        st.close()  # nothing in flight: leaves between steps
+        (Path(sync_dir) / "left").touch()
+        print(json.dumps({"rank": 0, "left": True}), flush=True)
+        return
+    res = {"rank": rank, "rel_before": wait_for(init + d[0], 30)}
+    st.flush(10.0)
+    _touch_and_wait(sync_dir, f"got_{rank}", [f"got_{r}" for r in range(world)] + ["left"])
+    deadline = time.time() + 30
+    while time.time() < deadline:  # a new home: either this replica is the master now or it has an up edge again
+        s = st.stats()
+        if s["master"] or s["edges"]["up"]["state"] == "connected":
+            break
+        time.sleep(0.02)
+    _touch_and_wait(sync_dir, f"home_{rank}", [f"home_{r}" for r in range(1, world)])
+    time.sleep(0.3)
+    if rank == 1:
+        st.addFromTensor(d[1])
+    res["rel_after"] = wait_for(init + d[0] + d[1], 30)
+    s = st.stats()
+    res["master"] = bool(s["master"])
+    res["errors"] = s["device"]["errors"]
+    res["rejoins"] = s["rejoins"]
+    print(json.dumps(res), flush=True)
+    _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(1, world)])
+    time.sleep(0.2 + (0.0 if res["master"] else 0.0) + (0.6 if res["master"] else 0.0))  # the new master leaves last
+    st.close()
+
+
 def main():
     sync_dir = os.environ["ST_TEST_SYNC_DIR"]
     rank, world, port, n, scenario = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
@@ -119,6 +180,8 @@ def main():
         return train(rank, world, port, sync_dir, dev)
     if scenario == "rejoin":
         return rejoin(rank, world, port, n, sync_dir, dev)
+    if scenario == "master_leaves":
+        return master_leaves(rank, world, port, n, sync_dir, dev)
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
     init = torch.randn(n, generator=g, device=dev)

@@ -103,3 +103,16 @@ def test_cut_up_edge_rejoins_without_losing_updates(free_port):
     for r in res:
         assert r["errors"] == 0
         assert r["rel"] < 5e-5, res
+
+
+def test_master_leaves_and_a_child_takes_over(free_port):
+    """T7 on GPUs: the master closes and exits between steps; one of its children becomes the master of the tensor's
+    address, the other joins below it, and a later update reaches both."""
+    _need(3)
+    res = _run(3, free_port, 2 * 4096 + 9, "master_leaves")
+    assert res[0].get("left")
+    survivors = res[1:]
+    assert sum(r["master"] for r in survivors) == 1, survivors
+    for r in survivors:
+        assert r["errors"] == 0
+        assert r["rel_before"] < 5e-5 and r["rel_after"] < 5e-5, survivors
