@@ -110,3 +110,35 @@ def test_dropped_frames_show_up_as_a_bounded_error(free_port):
         b.cfg.rejoin = False
         b.close()
         a.close()
+
+
+def test_master_leaves_and_a_child_takes_over_the_address(free_port):
+    """The master closes; its two children notice, one of them becomes the master of host:port, the other joins
+    below it, a newcomer can still join through host:port, and an update made afterwards reaches all of them."""
+    n = 96
+    torch.manual_seed(4)
+    init = torch.randn(n)
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone())
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=50)
+    c = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=50)
+    e = None
+    try:
+        d0 = torch.randn(n) * 1e-2
+        a.addFromTensor(d0)
+        out = torch.zeros(n)
+        for x in (b, c):
+            assert _poll(lambda x=x: (x.copyToTensor(out) - (init + d0)).abs().max().item() < 1e-4)
+        assert a.flush(10.0)
+        a.close()
+        assert _poll(lambda: sum(bool(x.stats()["master"]) for x in (b, c)) == 1), "exactly one child takes over"
+        assert _poll(lambda: any(x.stats()["edges"]["up"]["state"] == "connected" for x in (b, c))), "the other joins below it"
+        e = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin=False)  # a newcomer finds the tree
+        d1 = torch.randn(n) * 1e-2
+        b.addFromTensor(d1)
+        for x in (b, c, e):
+            assert _poll(lambda x=x: (x.copyToTensor(out) - (init + d0 + d1)).abs().max().item() < 1e-4), x.stats()
+    finally:
+        for x in (e, c, b):
+            if x is not None:
+                x.cfg.rejoin = False
+                x.close()
