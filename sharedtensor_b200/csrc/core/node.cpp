@@ -233,6 +233,24 @@ void CpuNode::tx_loop(Edge* e) {
     }
     IoStatus st = write_full(e->fd, frame.data(), frame.size(), &e->stop);
     if (st != IoStatus::Ok) {
+      // Not written: the mirror's step is taken back, so that the frame's content is still in values - mirror when
+      // the node re-joins.  (A frame the kernel accepted but the peer never read is lost for good: no resend.)
+      if (!noop) {
+        std::lock_guard<std::mutex> g(mu_);
+        if (e->mirror.size() == n) {
+          if (B == 0) {
+            float scale;
+            std::memcpy(&scale, frame.data(), 4);
+            decode_tensor_add_fast(frame.data() + 4, -scale, n, e->mirror.data(), nullptr);
+          } else {
+            size_t ns = block_scales(n, B);
+            std::vector<uint32_t> flipped(block_words(n));
+            std::memcpy(flipped.data(), frame.data() + ns, 4 * flipped.size());
+            for (auto& w : flipped) w = ~w;
+            decode_block_add_fast(flipped.data(), frame.data(), n, B, e->mirror.data(), nullptr);
+          }
+        }
+      }
       if (st != IoStatus::Stopped) edge_failed(e, "send", st);
       break;
     }

@@ -491,6 +491,21 @@ void GpuReplica::tcp_decode(int link, const uint32_t* words, float scale) {
   local_update();  // the frame has to travel on over the other links
 }
 
+void GpuReplica::tcp_unsend(int link, const uint32_t* words, float scale) {
+  if (scale == 0.f) return;
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (link < 0 || link >= kMaxLinks || !links_[link].used || !tcp_words_dev_) return;
+  const size_t n_words = size_t((n_ + 31) / 32);
+  std::memcpy(tcp_pinned_ + 2, words, n_words * 4);
+  check(cudaMemcpyAsync(tcp_words_dev_, tcp_pinned_ + 2, n_words * 4, cudaMemcpyHostToDevice, S(comm_)), "cudaMemcpyAsync");
+  // the mirror steps back by exactly what tcp_encode stepped it forward: the frame counts as never made
+  check(launch_tensor_decode(tcp_words_dev_, -scale, n_, static_cast<float*>(links_[link].mirror.ptr), nullptr, tile_state_, comm_),
+        "tensor_decode kernel");
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  launches_ += 1;
+}
+
 void GpuReplica::sync() {
   DeviceGuard g(device_);
   check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");

@@ -92,6 +92,9 @@ class GpuReplica {
   // made and applied on the device, host threads only move bytes.  `words` is host memory of ceil(n/32) words.
   float tcp_encode(int link, uint32_t* words, float min_scale_abs, float min_scale_rel);  // returns the frame's scale
   void tcp_decode(int link, const uint32_t* words, float scale);
+  // A frame made by tcp_encode that could not be written to the socket: the mirror's step is taken back, so that
+  // the frame's content stays in the residual and goes out over the next connection.
+  void tcp_unsend(int link, const uint32_t* words, float scale);
   void sync();
 
   // ---- engine thread: free-running rounds ----

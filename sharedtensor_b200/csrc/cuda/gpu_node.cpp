@@ -284,6 +284,11 @@ class GpuNode {
       std::memcpy(frame.data() + 4, words.data(), n_bytes);
       IoStatus st = write_full(e->fd, frame.data(), frame.size(), &e->stop);
       if (st != IoStatus::Ok) {
+        // not written: the frame counts as never made, its content goes out over the next connection
+        try {
+          rep_->tcp_unsend(e->link, words.data(), scale);
+        } catch (const std::exception&) {
+        }
         if (st != IoStatus::Stopped) e->failed.store(true);
         break;
       }

@@ -99,3 +99,33 @@ def test_gpu_child_below_reference_master(free_port):
         if g is not None:
             g.close()
         ref.kill()
+
+
+def test_gpu_child_rejoins_a_cpu_master_over_tcp(free_port):
+    """Host-side failure on a TCP edge: the GPU replica's connection to its CPU parent is cut; it keeps what the
+    parent had not been told (updates made during the outage included), joins again and both sides end up with
+    every update."""
+    n = 6000
+    torch.manual_seed(2)
+    init = torch.randn(n)
+    m = sharedtensor.createOrFetch("127.0.0.1", free_port, init)
+    g = None
+    try:
+        g = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n, device="cuda"), rejoin_backoff_ms=50)
+        out_g, out_m = torch.zeros(n, device="cuda"), torch.zeros(n)
+        d1, d2 = torch.randn(n) * 1e-2, torch.randn(n) * 1e-2
+        g.addFromTensor(d1.cuda())
+        assert _poll(lambda: _rel(m, init + d1, out_m) < 1e-5)
+        g._b.inject_sever("up")
+        for _ in range(5):
+            g.addFromTensor((d2 / 5).cuda())
+            time.sleep(0.02)
+        assert _poll(lambda: g.stats()["rejoins"] == 1), g.stats()
+        expect = init + d1 + d2
+        assert _poll(lambda: _rel(m, expect, out_m) < 1e-5), _rel(m, expect, out_m)
+        assert _poll(lambda: _rel(g, expect, out_g) < 1e-5), _rel(g, expect, out_g)
+    finally:
+        if g is not None:
+            g.cfg.rejoin = False
+            g.close()
+        m.close()
