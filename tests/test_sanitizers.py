@@ -15,6 +15,9 @@ def _have(lib):
 
 @pytest.mark.skipif(not _have("libtsan.so"), reason="ThreadSanitizer runtime not installed")
 def test_core_is_race_free_under_tsan():
-    res = subprocess.run([sys.executable, str(HERE / "sanitize_core.py"), "thread"], capture_output=True, text=True, timeout=900)
+    for attempt in range(3):  # exit code 75 = the sanitised interpreter stalled (not a report): run it again
+        res = subprocess.run([sys.executable, str(HERE / "sanitize_core.py"), "thread"], capture_output=True, text=True, timeout=500)
+        if res.returncode != 75:
+            break
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
     assert "reports=0" in res.stdout
