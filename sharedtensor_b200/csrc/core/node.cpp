@@ -48,7 +48,15 @@ void CpuNode::start(const std::string& host, int port, const float* init) {
         *out = edges_[slot].peer;
         return true;
       }));
-  if (!do_join(true, init)) {
+  // A first join can fail for a passing reason: the node listens on the source address of its up connection, and on
+  // a busy host that ephemeral port may just have been taken by another process's listener.  A new connection gets a
+  // new port, so a few attempts are made before giving up.
+  bool joined = false;
+  for (int attempt = 0; attempt < 4 && !joined && !stop_.load(); attempt++) {
+    if (attempt) ::usleep(50 * 1000);
+    joined = do_join(true, init);
+  }
+  if (!joined) {
     started_.store(false);
     listener_.reset();
     throw std::runtime_error("shared tensor could not join or found a tree at " + host + ":" + std::to_string(port));
@@ -58,7 +66,7 @@ void CpuNode::start(const std::string& host, int port, const float* init) {
 }
 
 bool CpuNode::do_join(bool first, const float* init) {
-  JoinResult jr = join_tree(host_, port_, &stop_);
+  JoinResult jr = join_tree(host_, port_, &stop_, 64, 10000, &my_addrs_);
   if (!jr.ok) {
     std::fprintf(stderr, "[sharedtensor] join failed: %s\n", jr.error.c_str());
     return false;
@@ -77,6 +85,7 @@ bool CpuNode::do_join(bool first, const float* init) {
       if (first && init)
         for (int64_t i = 0; i < n_; i++) values_[size_t(i)] += init[i];
       if (first) listen_addr_ = jr.listen_addr;
+      my_addrs_.push_back(jr.listen_addr);
       master_.store(true);
       ready_.store(true);
       for (int s = kSlotLeft; s <= kSlotRight; s++) edges_[s].paused.store(false);
@@ -94,12 +103,16 @@ bool CpuNode::do_join(bool first, const float* init) {
       return false;
     }
     listen_addr_ = jr.listen_addr;
+    my_addrs_.push_back(jr.listen_addr);
     listener_->add_listen_fd(lfd);
   } else {
     // The new parent knows this node by the source address of the new connection and hands that address to later
     // joiners: accept joins there too (best effort; the first address stays open for redirects already handed out).
     int lfd = open_listener(jr.listen_addr, cfg_.listen_backlog, &err);
-    if (lfd >= 0) listener_->add_listen_fd(lfd);
+    if (lfd >= 0) {
+      listener_->add_listen_fd(lfd);
+      my_addrs_.push_back(jr.listen_addr);
+    }
     // Re-join keeping the part of the state the lost parent had not been told yet:
     // values <- values - mirror_up, so that it is sent up the new edge (whose mirror starts at 0)
     // while the new parent streams its whole state down.  Child edges pause meanwhile.
@@ -492,7 +505,12 @@ NodeStats CpuNode::stats() {
 
 void CpuNode::close() {
   if (closed_.exchange(true)) return;
-  stop_.store(true);
+  {
+    // under the supervisor's mutex: set between its check of the flag and its wait, the notification would find
+    // nobody waiting and the supervisor would sleep for good
+    std::lock_guard<std::mutex> g(sup_mu_);
+    stop_.store(true);
+  }
   sup_cv_.notify_all();
   if (supervisor_.joinable()) supervisor_.join();
   if (listener_) listener_->stop();

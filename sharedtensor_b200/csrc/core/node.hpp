@@ -128,6 +128,7 @@ class CpuNode {
   std::condition_variable work_cv_;  // new data to send
   std::unique_ptr<TreeListener> listener_;
   sockaddr_in listen_addr_{};
+  std::vector<sockaddr_in> my_addrs_;  // every address this node listens on (supervisor/start thread only)
   std::atomic<bool> master_{false}, ready_{false}, closed_{false}, started_{false};
   std::condition_variable ready_cv_;
   // supervisor

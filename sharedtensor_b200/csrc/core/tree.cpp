@@ -40,7 +40,7 @@ static int make_tcp_socket(std::string* err) {
 }
 
 JoinResult join_tree(const std::string& host, int port, const std::atomic<bool>* stop, int max_hops,
-                     int reply_timeout_ms) {
+                     int reply_timeout_ms, const std::vector<sockaddr_in>* self) {
   JoinResult r;
   sockaddr_in root;
   if (!resolve_ipv4(host, port, &root, &r.error)) return r;
@@ -50,6 +50,19 @@ JoinResult join_tree(const std::string& host, int port, const std::atomic<bool>*
     if (stop && stop->load()) {
       r.error = "stopped";
       return r;
+    }
+    bool to_self = false;
+    if (self)
+      for (const sockaddr_in& a : *self)
+        to_self |= a.sin_port == target.sin_port && a.sin_addr.s_addr == target.sin_addr.s_addr;
+    if (to_self) {  // redirected to this very node: its old parent still lists it; start over
+      if (++restarts > 8) {
+        r.error = "redirected to this node itself";
+        return r;
+      }
+      target = root;
+      ::usleep(50 * 1000);
+      continue;
     }
     int fd = make_tcp_socket(&r.error);
     if (fd < 0) return r;

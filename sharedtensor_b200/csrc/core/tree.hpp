@@ -37,9 +37,11 @@ struct JoinResult {
 
 bool resolve_ipv4(const std::string& host, int port, sockaddr_in* out, std::string* err);
 
-// Walks the tree from host:port until some node answers 'Y'.
+// Walks the tree from host:port until some node answers 'Y'.  `self`: addresses this node itself listens on; a
+// redirect to one of them (a parent that has not noticed yet that this node's old connection is gone hands out the
+// node's own address) is treated like an unreachable target, so that a re-joining node cannot adopt itself.
 JoinResult join_tree(const std::string& host, int port, const std::atomic<bool>* stop,
-                     int max_hops = 64, int reply_timeout_ms = 10000);
+                     int max_hops = 64, int reply_timeout_ms = 10000, const std::vector<sockaddr_in>* self = nullptr);
 
 // socket + SO_REUSEADDR + bind + listen(backlog).  Returns -1 and fills err on failure.
 int open_listener(const sockaddr_in& addr, int backlog, std::string* err);

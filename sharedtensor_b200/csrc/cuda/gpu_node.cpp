@@ -112,7 +112,14 @@ class GpuNode {
           *out = edges_[slot].peer;
           return true;
         }));
-    if (!join(true, init_dev, stream)) {
+    // a first join can fail for a passing reason (the ephemeral port this node has to listen on was just taken by
+    // another process's listener): a new connection gets a new port
+    bool joined = false;
+    for (int attempt = 0; attempt < 4 && !joined && !stop_.load(); attempt++) {
+      if (attempt) ::usleep(50 * 1000);
+      joined = join(true, init_dev, stream);
+    }
+    if (!joined) {
       started_.store(false);
       listener_.reset();
       throw std::runtime_error("shared tensor could not join or found a tree at " + host + ":" + std::to_string(port));
@@ -354,7 +361,7 @@ class GpuNode {
   }
 
   bool join(bool first, const float* init_dev, void* stream) {
-    JoinResult jr = join_tree(host_, port_, &stop_);
+    JoinResult jr = join_tree(host_, port_, &stop_, 64, 10000, &my_addrs_);
     if (!jr.ok) {
       std::fprintf(stderr, "[sharedtensor] join failed: %s\n", jr.error.c_str());
       return false;
@@ -366,6 +373,7 @@ class GpuNode {
         std::fprintf(stderr, "[sharedtensor] cannot serve %s:%d as master: %s\n", host_.c_str(), port_, err.c_str());
         return false;
       }
+      my_addrs_.push_back(jr.listen_addr);
       if (first) {
         listen_addr_ = jr.listen_addr;
         if (!open_unix(&err)) {
@@ -401,6 +409,7 @@ class GpuNode {
         return false;
       }
       listen_addr_ = jr.listen_addr;
+      my_addrs_.push_back(jr.listen_addr);
       listener_->add_listen_fd(lfd);
       if (!open_unix(&err)) {
         ::close(jr.fd);
@@ -412,7 +421,10 @@ class GpuNode {
       // later joiners: accept TCP joins and peer-memory hellos there too (the first address stays open for the
       // redirects already handed out).  Best effort: without it this node is simply never a redirect target.
       int lfd = open_listener(jr.listen_addr, opt_.listen_backlog, &err);
-      if (lfd >= 0) listener_->add_listen_fd(lfd);
+      if (lfd >= 0) {
+        listener_->add_listen_fd(lfd);
+        my_addrs_.push_back(jr.listen_addr);
+      }
       int ufd = unix_listen_abstract(unix_name(jr.listen_addr), &err);
       if (ufd >= 0) {
         std::lock_guard<std::mutex> g(mu_);
@@ -867,6 +879,7 @@ class GpuNode {
   std::atomic<bool> master_{false}, closed_{false}, started_{false}, stop_{false};
   std::thread upgrade_thread_, watch_thread_;
   uint64_t rejoins_ = 0, edge_failures_ = 0;
+  std::vector<sockaddr_in> my_addrs_;  // every address this node listens on (start / watch thread only)
   int orphan_link_ = -1;  // the lost parent's link, kept (with its mirror) until a new parent has been found
   std::vector<int> extra_unix_fds_;  // peer-memory endpoints under the addresses of later up connections
 };

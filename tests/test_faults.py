@@ -142,3 +142,41 @@ def test_master_leaves_and_a_child_takes_over_the_address(free_port):
             if x is not None:
                 x.cfg.rejoin = False
                 x.close()
+
+
+def test_closing_while_a_node_rejoins_never_blocks(free_port):
+    """Five nodes; one cuts its up connection; after a random short while all are closed, in either order.  Every
+    close has to come back promptly whatever the re-joining node is doing at that moment (a close that set its
+    stop flag between the supervisor's check and its wait used to leave the supervisor asleep for good)."""
+    import random
+    import socket
+
+    from sharedtensor_b200 import _native
+
+    core = _native.core()
+    rnd = random.Random(7)
+    n = 500
+
+    def node():
+        c = core.NodeConfig()
+        c.rejoin_backoff_ms = 50
+        return core.CpuNode(n, c)
+
+    for it in range(40):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        init = torch.randn(n)
+        nodes = [node()]
+        nodes[0].start("127.0.0.1", port, init.data_ptr())
+        for _ in range(4):
+            nd = node()
+            nd.start("127.0.0.1", port, 0)
+            assert nd.wait_ready(20000)
+            nodes.append(nd)
+        nodes[rnd.choice([1, 2, 3, 4])].inject_sever(0)
+        time.sleep(rnd.choice([0.0, 0.01, 0.05, 0.1, 0.3]))
+        t0 = time.time()
+        for nd in (reversed(nodes) if rnd.random() < 0.5 else nodes):
+            nd.close()
+        assert time.time() - t0 < 10.0, f"iteration {it}: closing five nodes took {time.time() - t0:.1f} s"
