@@ -76,8 +76,8 @@ def main():
     try:
         res = subprocess.run([sys.executable, "-c", SCENARIO, str(so), str(port)], env=env, capture_output=True, text=True, timeout=150)
     except subprocess.TimeoutExpired:
-        # seen about once in twenty runs: the interpreter under the preloaded sanitizer runtime stops making progress
-        # (the scenario itself takes a few seconds); the caller runs it again
+        # the scenario takes a few seconds: running out of time means some thread is stuck (a lost wake-up in
+        # close() once showed up exactly like this); reported to the caller as exit code 75
         print(f"sanitizer={kind} timeout")
         sys.exit(75)
     reports = res.stderr.count("WARNING: ThreadSanitizer") + res.stderr.count("ERROR: AddressSanitizer")
