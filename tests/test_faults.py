@@ -180,3 +180,49 @@ def test_closing_while_a_node_rejoins_never_blocks(free_port):
         for nd in (reversed(nodes) if rnd.random() < 0.5 else nodes):
             nd.close()
         assert time.time() - t0 < 10.0, f"iteration {it}: closing five nodes took {time.time() - t0:.1f} s"
+
+
+def test_churn_between_quiet_rounds_keeps_the_exact_sum(free_port):
+    """Five replicas; every round all of them add, the tree goes quiet, one random replica (the master included)
+    leaves, the survivors find each other again through host:port, and a newcomer joins.  Every replica holds
+    initial + all updates after every step."""
+    import random
+
+    rnd = random.Random(3)
+    torch.manual_seed(3)
+    n = 256
+    init = torch.randn(n)
+    nodes = [sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone(), rejoin_backoff_ms=50)]
+    for _ in range(4):
+        nodes.append(sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=50))
+    expect = init.clone()
+    out = torch.zeros(n)
+
+    def converged():
+        return max(float((nd.copyToTensor(out) - expect).abs().max()) for nd in nodes) < 2e-4
+
+    def reformed():
+        st = [nd.stats() for nd in nodes]
+        return sum(bool(s["master"]) for s in st) == 1 and all(s["master"] or s["edges"]["up"]["state"] == "connected" for s in st)
+
+    try:
+        for r in range(8):
+            for nd in nodes:
+                d = torch.randn(n) * 1e-2
+                nd.addFromTensor(d)
+                expect += d
+            assert _poll(converged), f"round {r}: updates"
+            for nd in nodes:
+                nd.flush(5.0)
+            gone = nodes.pop(rnd.randrange(len(nodes)))
+            gone.cfg.rejoin = False
+            gone.close()
+            assert _poll(reformed), f"round {r}: one master, everybody else attached"
+            assert _poll(converged), f"round {r}: after the leave"
+            nodes.append(sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=50))
+            assert _poll(converged), f"round {r}: after the join"
+    finally:
+        for nd in nodes:
+            nd.cfg.rejoin = False
+        for nd in reversed(nodes):
+            nd.close()
