@@ -226,3 +226,45 @@ def test_churn_between_quiet_rounds_keeps_the_exact_sum(free_port):
             nd.cfg.rejoin = False
         for nd in reversed(nodes):
             nd.close()
+
+
+def test_cut_edge_under_continuous_traffic_loses_nothing_on_loopback(free_port):
+    """A child adds without pause while its up connection is cut five times.  What it had written before a cut still
+    reaches the parent (the FIN follows the queued data), a frame whose write failed is taken back, the rest is
+    carried over the re-join: both replicas end up with every update."""
+    import threading
+
+    n = 4096
+    torch.manual_seed(0)
+    init = torch.randn(n)
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone())
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=20)
+    expect = init.clone()
+    stop = threading.Event()
+
+    def adder():
+        g = torch.Generator().manual_seed(1)
+        while not stop.is_set():
+            d = torch.randn(n, generator=g) * 1e-2
+            b.addFromTensor(d)
+            expect.add_(d)
+            time.sleep(0.002)
+
+    t = threading.Thread(target=adder)
+    t.start()
+    try:
+        for i in range(5):
+            time.sleep(0.15)
+            b._b.inject_sever("up")
+            assert _poll(lambda: b.stats()["rejoins"] >= i + 1, timeout=10.0)
+        stop.set()
+        t.join()
+        out = torch.zeros(n)
+        assert _poll(lambda: float((a.copyToTensor(out) - expect).abs().max()) < 1e-4)
+        assert _poll(lambda: float((b.copyToTensor(out) - expect).abs().max()) < 1e-4)
+    finally:
+        stop.set()
+        t.join()
+        b.cfg.rejoin = False
+        b.close()
+        a.close()
