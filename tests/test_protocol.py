@@ -166,3 +166,36 @@ def test_frames_of_the_reference_binary_decode_with_our_codec(free_port):
         c.close()
     finally:
         ref.kill()
+
+
+def test_garbage_from_a_peer_costs_only_that_edge(free_port):
+    """A connection that is adopted and then sends a frame with a NaN scale, a negative scale, or nothing at all
+    before it closes: the node drops that edge, frees the slot and keeps serving (the reference adds whatever
+    arrives into its arrays, src/sharedtensor.c:106-127, or exits)."""
+    n = 64
+    init = torch.arange(float(n))
+    master = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone())
+    try:
+        nbytes = (n + 7) // 8
+        for bad in (struct.pack("<f", float("nan")), struct.pack("<f", -1.0), None):
+            c = _connect(free_port)
+            assert _recv_exact(c, 1) == b"Y"
+            if bad is not None:
+                c.sendall(bad + b"\xff" * nbytes)
+                deadline = time.time() + 10
+                while time.time() < deadline and master.stats()["edges"]["left"]["state"] == "connected":
+                    time.sleep(0.02)
+            c.close()
+            deadline = time.time() + 10
+            while time.time() < deadline and master.stats()["edges"]["left"]["state"] != "free":
+                time.sleep(0.02)
+            assert master.stats()["edges"]["left"]["state"] == "free"
+        out = torch.zeros(n)
+        master.copyToTensor(out)
+        assert torch.equal(out, init), "nothing of the garbage reached the values"
+        child = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin=False)
+        child.copyToTensor(out)
+        assert torch.allclose(out, init, atol=1e-1)
+        child.close()
+    finally:
+        master.close()
