@@ -30,6 +30,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--tol", type=float, default=0.01)
     ap.add_argument("--timeout", type=float, default=300.0)
+    ap.add_argument("--tcp-scale-mode", default="tensor",
+                    help="tensor = the reference's wire format (one scale per frame); block32 ... block4096 = one exponent "
+                         "byte per block, between nodes of this framework only")
     args = ap.parse_args()
     n = int(args.elements)
     with socket.socket() as s:
@@ -37,9 +40,9 @@ def main() -> None:
         port = s.getsockname()[1]
     torch.manual_seed(0)
     init = torch.randn(n)
-    a = sharedtensor.createOrFetch("127.0.0.1", port, init.clone())
+    a = sharedtensor.createOrFetch("127.0.0.1", port, init.clone(), tcp_scale_mode=args.tcp_scale_mode)
     t0 = time.perf_counter()
-    b = sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n))
+    b = sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), tcp_scale_mode=args.tcp_scale_mode)
     out = torch.empty(n)
     b.flush(args.timeout)
     join_s = time.perf_counter() - t0
@@ -74,7 +77,7 @@ def main() -> None:
     print(json.dumps({"metric": "applied_updates_per_s", "impl": "ours, CPU node, loopback TCP", "value": args.steps / secs,
                       "elements": n, "steps": args.steps, "seconds": secs, "final_rel_err": rel, "converged": rel <= args.tol,
                       "late_join_state_transfer_s": join_s, "frames_sent": st["frames_sent"], "bytes_sent": st["bytes_sent"],
-                      "tol": args.tol, "checked": f"every {SAMPLE}th element"}))
+                      "tol": args.tol, "tcp_scale_mode": args.tcp_scale_mode, "checked": f"every {SAMPLE}th element"}))
     b.close()
     a.close()
 

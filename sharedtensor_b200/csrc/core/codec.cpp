@@ -106,7 +106,7 @@ void decode_tensor_add(const uint8_t* bits, float scale, size_t n, float* dst, f
 // Cut-off: a step below 2^(emax - rel_bits), emax the exponent of the block's largest |value|, is not sent.
 // With rel_bits <= 22 every step is a whole number of ulps of every element of the block, so stepping the
 // mirror is exact and the stream cannot get stuck re-sending a step that rounds away.
-static inline int block_code(float xmax, uint32_t vmax_bits, const BlockGate& gate) {
+int block_code(float xmax, uint32_t vmax_bits, const BlockGate& gate) {
   float scaled = xmax * 0.6666667f;
   if ((f32_bits(scaled) >> 23) == 0) return kSilent;  // zero or denormal
   int kx = floor_log2_f32(scaled);

@@ -98,6 +98,9 @@ void copy_fast(float* dst, const float* src, size_t n);
 size_t block_words(size_t n);              // ceil(n/32)
 size_t block_scales(size_t n, int block);  // ceil(n/block)
 
+// Exponent code of one block from its largest |residual| and the bit pattern of its largest |value| (0 = silent).
+int block_code(float xmax, uint32_t vmax_bits, const BlockGate& gate);
+
 // Encodes n elements (n need not be a multiple of anything; missing elements count as zero residual
 // and their bits are 1).  v: values, k: mirror (updated), words/scales: outputs.
 // Returns the largest |residual| (before the update), a cheap convergence statistic.

@@ -233,12 +233,95 @@ void copy_fast(float* dst, const float* src, size_t n) {
   parallel_chunks(n, 16, [&](size_t b, size_t e, int) { std::memcpy(dst + b, src + b, (e - b) * sizeof(float)); });
 }
 
+namespace {
+
+// Full blocks only (n a multiple of `block`, block a multiple of 32); same results as encode_block.
+__attribute__((target("avx2"))) double encode_blocks_avx2(const float* v, float* k, size_t n, int block, const BlockGate& gate,
+                                                          uint32_t* words, uint8_t* scales) {
+  const __m256 absmask = _mm256_castsi256_ps(_mm256_set1_epi32(0x7fffffff));
+  const __m256 zero = _mm256_setzero_ps();
+  double worst = 0.0;
+  const size_t nb = n / size_t(block);
+  for (size_t b = 0; b < nb; b++) {
+    const float* vb = v + b * size_t(block);
+    float* kb = k + b * size_t(block);
+    __m256 xm = _mm256_setzero_ps();
+    __m256i vm = _mm256_setzero_si256();
+    for (int j = 0; j < block; j += 8) {
+      const __m256 vv = _mm256_loadu_ps(vb + j);
+      const __m256 x = _mm256_sub_ps(vv, _mm256_loadu_ps(kb + j));
+      xm = _mm256_max_ps(_mm256_and_ps(x, absmask), xm);  // a NaN residual is skipped, like "if (ax > xmax)"
+      vm = _mm256_max_epu32(vm, _mm256_castps_si256(_mm256_and_ps(vv, absmask)));
+    }
+    float tx[8];
+    uint32_t tv[8];
+    _mm256_storeu_ps(tx, xm);
+    _mm256_storeu_si256(reinterpret_cast<__m256i*>(tv), vm);
+    float xmax = 0.0f;
+    uint32_t vmax = 0;
+    for (int j = 0; j < 8; j++) {
+      if (tx[j] > xmax) xmax = tx[j];
+      if (tv[j] > vmax) vmax = tv[j];
+    }
+    if (double(xmax) > worst) worst = double(xmax);
+    const int code = block_code(xmax, vmax, gate);
+    scales[b] = uint8_t(code);
+    const float scale = code ? exp2i(code - 127) : 0.0f;
+    const __m256 pos = _mm256_set1_ps(scale), neg = _mm256_set1_ps(-scale);
+    uint32_t* wb = words + b * size_t(block / 32);
+    for (int g = 0; g < block / 32; g++) {
+      uint32_t w = 0;
+      for (int j = 0; j < 32; j += 8) {
+        const int o = g * 32 + j;
+        const __m256 kk = _mm256_loadu_ps(kb + o);
+        const __m256 gt = _mm256_cmp_ps(_mm256_sub_ps(_mm256_loadu_ps(vb + o), kk), zero, _CMP_GT_OQ);
+        w |= (~uint32_t(_mm256_movemask_ps(gt)) & 0xffu) << j;
+        if (code) _mm256_storeu_ps(kb + o, _mm256_add_ps(kk, _mm256_blendv_ps(neg, pos, gt)));
+      }
+      wb[g] = w;
+    }
+  }
+  return worst;
+}
+
+__attribute__((target("avx2"))) void decode_blocks_avx2(const uint32_t* words, const uint8_t* scales, size_t n, int block,
+                                                        float* dst, float* dst2) {
+  const __m256i lane_bit = _mm256_setr_epi32(1, 2, 4, 8, 16, 32, 64, 128);
+  const size_t nb = n / size_t(block);
+  for (size_t b = 0; b < nb; b++) {
+    const int code = scales[b];
+    if (!code) continue;
+    const float scale = exp2i(code - 127);
+    const __m256 pos = _mm256_set1_ps(scale), neg = _mm256_set1_ps(-scale);
+    const size_t base = b * size_t(block);
+    for (int j = 0; j < block; j += 8) {
+      const size_t i = base + size_t(j);
+      const __m256i byte = _mm256_set1_epi32(int((words[i >> 5] >> (i & 31)) & 0xffu));
+      const __m256 isneg = _mm256_castsi256_ps(_mm256_cmpeq_epi32(_mm256_and_si256(byte, lane_bit), lane_bit));
+      const __m256 f = _mm256_blendv_ps(pos, neg, isneg);
+      _mm256_storeu_ps(dst + i, _mm256_add_ps(_mm256_loadu_ps(dst + i), f));
+      if (dst2) _mm256_storeu_ps(dst2 + i, _mm256_add_ps(_mm256_loadu_ps(dst2 + i), f));
+    }
+  }
+}
+
+}  // namespace
+
 double encode_block_fast(const float* v, float* k, size_t n, int block, const BlockGate& gate, uint32_t* words,
                          uint8_t* scales) {
+  const bool avx = have_avx2();
   double worst[64];
   for (int i = 0; i < 64; i++) worst[i] = 0.0;
   parallel_chunks(n, size_t(block), [&](size_t b, size_t e, int idx) {
-    worst[idx] = encode_block(v + b, k + b, e - b, block, gate, words + b / 32, scales + b / size_t(block));
+    const size_t full = avx ? (e - b) / size_t(block) * size_t(block) : 0;  // whole blocks go through AVX2
+    double w = 0.0;
+    if (full) w = encode_blocks_avx2(v + b, k + b, full, block, gate, words + b / 32, scales + b / size_t(block));
+    if (b + full < e) {
+      const size_t o = b + full;
+      double w2 = encode_block(v + o, k + o, e - o, block, gate, words + o / 32, scales + o / size_t(block));
+      if (w2 > w) w = w2;
+    }
+    worst[idx] = w;
   });
   double w = 0.0;
   for (int i = 0; i < 64; i++)
@@ -247,8 +330,14 @@ double encode_block_fast(const float* v, float* k, size_t n, int block, const Bl
 }
 
 void decode_block_add_fast(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst, float* dst2) {
+  const bool avx = have_avx2();
   parallel_chunks(n, size_t(block), [&](size_t b, size_t e, int) {
-    decode_block_add(words + b / 32, scales + b / size_t(block), e - b, block, dst + b, dst2 ? dst2 + b : nullptr);
+    const size_t full = avx ? (e - b) / size_t(block) * size_t(block) : 0;
+    if (full) decode_blocks_avx2(words + b / 32, scales + b / size_t(block), full, block, dst + b, dst2 ? dst2 + b : nullptr);
+    if (b + full < e) {
+      const size_t o = b + full;
+      decode_block_add(words + o / 32, scales + o / size_t(block), e - o, block, dst + o, dst2 ? dst2 + o : nullptr);
+    }
   });
 }
 

@@ -220,18 +220,22 @@ def test_fast_paths_are_bit_identical_to_the_plain_codec(n):
     core.decode_tensor_add(P(b1), 0.25, n, P(d1), P(m1))
     core.decode_tensor_add_fast(P(b1), 0.25, n, P(d2), P(m2))
     assert torch.equal(d1, d2) and torch.equal(m1, m2)
-    # block format, cut into block-aligned pieces
-    v = torch.randn(n, generator=g)
-    k1, k2 = k.clone(), k.clone()
-    B = 64
-    w1 = torch.zeros((n + 31) // 32, dtype=torch.int32)
-    w2 = torch.zeros_like(w1)
-    c1 = torch.zeros((n + B - 1) // B, dtype=torch.uint8)
-    c2 = torch.zeros_like(c1)
-    r1 = core.encode_block(P(v), P(k1), n, B, -100, 22, P(w1), P(c1))
-    r2 = core.encode_block_fast(P(v), P(k2), n, B, -100, 22, P(w2), P(c2))
-    assert r1 == r2 and torch.equal(w1, w2) and torch.equal(c1, c2) and torch.equal(k1, k2)
-    a1, a2 = torch.zeros(n), torch.zeros(n)
-    core.decode_block_add(P(w1), P(c1), n, B, P(a1), 0)
-    core.decode_block_add_fast(P(w1), P(c1), n, B, P(a2), 0)
-    assert torch.equal(a1, a2)
+    # block format: whole blocks vectorised, the ragged tail through the plain loop, pieces over threads
+    for B in (32, 64, 256, 4096):
+        v = torch.randn(n, generator=g)
+        if n > 100:
+            v[3] = float("nan")
+            v[40] = 0.0
+        k1, k2 = k.clone(), k.clone()
+        w1 = torch.zeros((n + 31) // 32, dtype=torch.int32)
+        w2 = torch.full_like(w1, 0x5A5A5A5A)
+        c1 = torch.zeros((n + B - 1) // B, dtype=torch.uint8)
+        c2 = torch.full_like(c1, 7)
+        r1 = core.encode_block(P(v), P(k1), n, B, -100, 22, P(w1), P(c1))
+        r2 = core.encode_block_fast(P(v), P(k2), n, B, -100, 22, P(w2), P(c2))
+        assert r1 == r2 and torch.equal(w1, w2) and torch.equal(c1, c2), B
+        assert torch.equal(torch.nan_to_num(k1, nan=7.0), torch.nan_to_num(k2, nan=7.0)), B
+        a1, a2, m1, m2 = torch.zeros(n), torch.zeros(n), torch.ones(n), torch.ones(n)
+        core.decode_block_add(P(w1), P(c1), n, B, P(a1), P(m1))
+        core.decode_block_add_fast(P(w1), P(c1), n, B, P(a2), P(m2))
+        assert torch.equal(a1, a2) and torch.equal(m1, m2), B
