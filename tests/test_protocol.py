@@ -199,3 +199,38 @@ def test_garbage_from_a_peer_costs_only_that_edge(free_port):
         child.close()
     finally:
         master.close()
+
+
+def test_simultaneous_founders_end_up_in_one_tree(free_port):
+    """Six callers reach createOrFetch at the same moment with nobody serving host:port yet: exactly one becomes the
+    master, the others lose the race for the address, try again and join below it with the master's values."""
+    import threading
+
+    n = 64
+    for _ in range(3):
+        nodes, errs = [None] * 6, []
+
+        def go(i):
+            try:
+                nodes[i] = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.full((n,), float(i + 1)), rejoin=False)
+            except Exception as e:  # noqa: BLE001
+                errs.append(repr(e))
+
+        ts = [threading.Thread(target=go, args=(i,)) for i in range(6)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        try:
+            assert not errs, errs
+            masters = [i for i, x in enumerate(nodes) if x.stats()["master"]]
+            assert len(masters) == 1
+            want = float(masters[0] + 1)
+            out = torch.zeros(n)
+            for x in nodes:
+                deadline = time.time() + 10
+                while time.time() < deadline and abs(float(x.copyToTensor(out).mean()) - want) > 1e-3:
+                    time.sleep(0.02)
+                assert abs(float(out.mean()) - want) <= 1e-3
+        finally:
+            for x in reversed([x for x in nodes if x is not None]):
+                x.close()
+        time.sleep(0.1)
