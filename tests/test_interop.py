@@ -87,3 +87,30 @@ def test_reference_nodes_below_our_master_with_redirect(free_port):
         ours.close()
         for r in refs:
             r.kill()
+
+
+def test_our_node_survives_the_death_of_a_reference_master(free_port):
+    """The reference master is killed (host-side failure).  Our child notices the closed connection, finds nobody at
+    host:port, takes the address over and serves newcomers with the state it held."""
+    n = 96
+    torch.manual_seed(5)
+    init = torch.randn(n)
+    ref = RefWorker(n, call_timeout=60.0)
+    ours = newcomer = None
+    try:
+        ref.call(op="create", host="127.0.0.1", port=free_port, n=n, values=init.tolist())
+        ours = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=50)
+        out = torch.zeros(n)
+        assert _poll(lambda: (ours.copyToTensor(out) - init).abs().max().item() <= 2e-4)
+        ref.kill()
+        assert _poll(lambda: bool(ours.stats()["master"])), ours.stats()
+        d = torch.randn(n) * 1e-2
+        ours.addFromTensor(d)
+        newcomer = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin=False)
+        assert _poll(lambda: (newcomer.copyToTensor(out) - (init + d)).abs().max().item() <= 2e-4)
+    finally:
+        for x in (newcomer, ours):
+            if x is not None:
+                x.cfg.rejoin = False
+                x.close()
+        ref.kill()
