@@ -167,3 +167,23 @@ def test_rate_cap(free_port):
         b.close()
     finally:
         a.close()
+
+
+def test_dropping_a_connected_tensor_and_using_a_closed_one(free_port):
+    """Garbage-collecting a connected tensor closes it quietly (the reference calls exit(-1) there,
+    src/sharedtensor.c:421-430); closing twice is fine; using a closed tensor raises."""
+    import gc
+
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.ones(100))
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(100))
+    assert a.stats()["edges"]["left"]["state"] == "connected"
+    del b
+    gc.collect()
+    t0 = time.time()
+    while time.time() - t0 < 10 and a.stats()["edges"]["left"]["state"] != "free":
+        time.sleep(0.02)
+    assert a.stats()["edges"]["left"]["state"] == "free"
+    a.close()
+    a.close()
+    with pytest.raises(RuntimeError, match="closed"):
+        a.addFromTensor(torch.ones(100))
