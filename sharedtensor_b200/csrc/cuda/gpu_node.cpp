@@ -144,7 +144,10 @@ class GpuNode {
     if (rep_) rep_->stop_engine();
     if (listener_) listener_->stop();
     if (unix_fd_ >= 0) ::shutdown(unix_fd_, SHUT_RDWR);
-    for (int fd : extra_unix_fds_) ::shutdown(fd, SHUT_RDWR);
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      for (int fd : extra_unix_fds_) ::shutdown(fd, SHUT_RDWR);
+    }
     if (upgrade_thread_.joinable()) upgrade_thread_.join();
     if (watch_thread_.joinable()) watch_thread_.join();
     if (unix_fd_ >= 0) {
