@@ -34,7 +34,7 @@ def _run(world, port, mode, steps):
 def test_two_cpu_ranks_learn(free_port, mode):
     res = _run(2, free_port, mode, 120)
     for r in res:
-        assert r["loss_last"] < 0.8 * r["loss_first"], r
+        assert r["loss_last"] < 0.9 * r["loss_first"], r
     if mode == "async":
         (s0, n0), (s1, _) = res[0]["checksum"], res[1]["checksum"]
         assert abs(s0 - s1) <= 1e-3 * n0, res
