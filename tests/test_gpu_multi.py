@@ -88,7 +88,7 @@ def test_trainers_that_queue_their_own_rounds(free_port):
     res = _run(2, free_port, 0, "train")
     for r in res:
         assert r["errors"] == 0
-        assert r["loss_last"] < 0.8 * r["loss_first"], r
+        assert r["loss_last"] < 0.9 * r["loss_first"], r
         assert r["rounds"] >= 120
     assert abs(res[0]["checksum"] - res[1]["checksum"]) <= 1e-3 * res[0]["norm"], res
 
