@@ -268,3 +268,67 @@ def test_cut_edge_under_continuous_traffic_loses_nothing_on_loopback(free_port):
         b.cfg.rejoin = False
         b.close()
         a.close()
+
+
+def test_abrupt_churn_under_traffic_leaves_the_survivors_in_agreement(free_port):
+    """Replicas are closed without warning while updates keep coming in at random places, and newcomers join.  What a
+    closed replica had not passed on is gone for everybody, so the sum is not checked; but once the churn stops, one
+    tree is left and all its replicas hold the same values."""
+    import random
+    import threading
+
+    rnd = random.Random(5)
+    torch.manual_seed(5)
+    n = 256
+
+    def mk(t):
+        return sharedtensor.createOrFetch("127.0.0.1", free_port, t, rejoin_backoff_ms=30)
+
+    nodes = [mk(torch.randn(n))] + [mk(torch.zeros(n)) for _ in range(5)]
+    lock = threading.Lock()
+    stop = threading.Event()
+
+    def adder():
+        g = torch.Generator().manual_seed(6)
+        while not stop.is_set():
+            with lock:
+                nd = rnd.choice(nodes)
+            try:
+                nd.addFromTensor(torch.randn(n, generator=g) * 1e-2)
+            except RuntimeError:  # closed in between
+                pass
+            time.sleep(0.001)
+
+    t = threading.Thread(target=adder)
+    t.start()
+    try:
+        for _ in range(6):
+            time.sleep(rnd.choice([0.02, 0.05, 0.1]))
+            with lock:
+                gone = nodes.pop(rnd.randrange(len(nodes)))
+            gone.cfg.rejoin = False
+            gone.close()
+            time.sleep(rnd.choice([0.0, 0.05, 0.2]))
+            with lock:
+                nodes.append(mk(torch.zeros(n)))
+        stop.set()
+        t.join()
+        ref, out = torch.zeros(n), torch.zeros(n)
+
+        def settled():
+            st = [nd.stats() for nd in nodes]
+            if sum(bool(s["master"]) for s in st) != 1:
+                return False
+            if not all(s["master"] or s["edges"]["up"]["state"] == "connected" for s in st):
+                return False
+            nodes[0].copyToTensor(ref)
+            return max(float((nd.copyToTensor(out) - ref).abs().max()) for nd in nodes) < 2e-4
+
+        assert _poll(settled, timeout=40.0)
+    finally:
+        stop.set()
+        t.join()
+        for nd in nodes:
+            nd.cfg.rejoin = False
+        for nd in reversed(nodes):
+            nd.close()
