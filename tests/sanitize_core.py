@@ -47,7 +47,12 @@ while time.time() < deadline:
 print("worst rel err", worst)
 nodes[3].inject_sever(0)        # cut an up edge: exercise failure + re-join paths under the sanitizer
 time.sleep(1.0)
-for nd in reversed(nodes): nd.close()
+nodes[0].close()                # the master goes: its children race for host:port, the loser joins the winner
+time.sleep(1.5)
+d = torch.randn(n) * 1e-2
+nodes[2].add(d.data_ptr(), n)   # traffic through the re-formed tree
+time.sleep(0.5)
+for nd in reversed(nodes[1:]): nd.close()
 assert worst < 2e-5
 print("SCENARIO OK")
 '''
