@@ -94,6 +94,11 @@ class SharedTensor:
         s["config"] = self.cfg.asdict()
         return s
 
+    def events(self) -> list:
+        """Membership events of this replica, oldest first (CPU replicas: joined, master, adopted, edge_lost, rejoined,
+        took_over; each with a wall-clock time in milliseconds and a detail string)."""
+        return list(self._b.stats().get("events", []))
+
     def trace(self) -> list:
         """Per-round records kept on the device (GPU replicas): when each of the last 64 rounds ended on the GPU's
         clock, how many tiles it had to look at and how many frames had been sent by then."""

@@ -207,6 +207,15 @@ void bind_core(py::module_& m) {
         d["redirects"] = s.redirects;
         d["rejoins"] = s.rejoins;
         d["edge_failures"] = s.edge_failures;
+        py::list evs;
+        for (const NodeEvent& ev : s.events) {
+          py::dict e1;
+          e1["ms"] = ev.ms;
+          e1["kind"] = ev.kind;
+          e1["detail"] = ev.detail;
+          evs.append(e1);
+        }
+        d["events"] = evs;
         py::dict e;
         e["up"] = edge_stats_dict(s.edge[kSlotUp]);
         e["left"] = edge_stats_dict(s.edge[kSlotLeft]);

@@ -93,6 +93,7 @@ bool CpuNode::do_join(bool first, const float* init) {
     listener_->add_listen_fd(lfd);
     ready_cv_.notify_all();
     std::fprintf(stderr, "[sharedtensor] master of %s:%d (%lld elements)\n", host_.c_str(), port_, (long long)n_);
+    log_event(first ? "master" : "took_over", host_ + ":" + std::to_string(port_));
     return true;
   }
   if (first) {
@@ -125,9 +126,20 @@ bool CpuNode::do_join(bool first, const float* init) {
   }
   master_.store(false);
   attach_edge(kSlotUp, jr.fd, jr.parent_addr);
+  log_event(first ? "joined" : "rejoined", "below " + addr_to_string(jr.parent_addr) + " after " + std::to_string(jr.hops) + " redirect(s)");
   std::fprintf(stderr, "[sharedtensor] joined %s:%d below %s after %d redirect(s)\n", host_.c_str(), port_,
                addr_to_string(jr.parent_addr).c_str(), jr.hops);
   return true;
+}
+
+void CpuNode::log_event(const char* kind, const std::string& detail) {
+  NodeEvent ev;
+  ev.ms = uint64_t(std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::system_clock::now().time_since_epoch()).count());
+  ev.kind = kind;
+  ev.detail = detail;
+  std::lock_guard<std::mutex> g(ev_mu_);
+  events_.push_back(std::move(ev));
+  if (events_.size() > 64) events_.pop_front();
 }
 
 void CpuNode::attach_edge(int slot, int fd, const sockaddr_in& peer) {
@@ -150,6 +162,7 @@ void CpuNode::attach_edge(int slot, int fd, const sockaddr_in& peer) {
   e.st = EdgeStats();
   e.st.peer = addr_to_string(peer);
   e.state.store(1);
+  if (slot != kSlotUp) log_event("adopted", std::string(slot == kSlotLeft ? "left " : "right ") + addr_to_string(peer));
   e.tx = std::thread([this, &e] { tx_loop(&e); });
   e.rx = std::thread([this, &e] { rx_loop(&e); });
 }
@@ -158,6 +171,7 @@ void CpuNode::edge_failed(Edge* e, const char* why, IoStatus st) {
   int expect = 1;
   if (!e->state.compare_exchange_strong(expect, 2)) return;
   e->stop.store(true);
+  if (!stop_.load()) log_event("edge_lost", std::string(e->slot == kSlotUp ? "up " : (e->slot == kSlotLeft ? "left " : "right ")) + e->st.peer + ": " + why);
   if (!stop_.load())
     std::fprintf(stderr, "[sharedtensor] edge %d (%s) lost: %s (%s)\n", e->slot, e->st.peer.c_str(), why,
                  io_status_name(st));
@@ -499,6 +513,10 @@ NodeStats CpuNode::stats() {
   s.copies = copies_;
   s.redirects = listener_ ? listener_->redirects() : 0;
   s.rejoins = rejoins_;
+  {
+    std::lock_guard<std::mutex> g2(ev_mu_);
+    s.events.assign(events_.begin(), events_.end());
+  }
   s.edge_failures = edge_failures_;
   return s;
 }

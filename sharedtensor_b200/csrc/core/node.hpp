@@ -50,7 +50,14 @@ struct EdgeStats {
   uint64_t dropped_by_injection = 0;
 };
 
+// One membership event (joined, master, edge_lost, rejoined, adopted, ...), kept in a small ring for stats().
+struct NodeEvent {
+  uint64_t ms = 0;  // wall clock, milliseconds since the epoch
+  std::string kind, detail;
+};
+
 struct NodeStats {
+  std::vector<NodeEvent> events;  // oldest first, at most 64
   bool master = false, ready = false, closed = false;
   int64_t n = 0;
   std::string listen_addr;
@@ -128,6 +135,9 @@ class CpuNode {
   std::condition_variable work_cv_;  // new data to send
   std::unique_ptr<TreeListener> listener_;
   sockaddr_in listen_addr_{};
+  std::mutex ev_mu_;
+  std::deque<NodeEvent> events_;
+  void log_event(const char* kind, const std::string& detail);
   std::vector<sockaddr_in> my_addrs_;  // every address this node listens on (supervisor/start thread only)
   std::atomic<bool> master_{false}, ready_{false}, closed_{false}, started_{false};
   std::condition_variable ready_cv_;

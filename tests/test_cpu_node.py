@@ -187,3 +187,29 @@ def test_dropping_a_connected_tensor_and_using_a_closed_one(free_port):
     a.close()
     with pytest.raises(RuntimeError, match="closed"):
         a.addFromTensor(torch.ones(100))
+
+
+def test_membership_events_are_recorded(free_port):
+    """stats()["events"]: what happened to this node's place in the tree, oldest first."""
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.ones(64))
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(64), rejoin_backoff_ms=50)
+    try:
+        assert [e["kind"] for e in a.stats()["events"]] == ["master", "adopted"]
+        assert [e["kind"] for e in b.stats()["events"]] == ["joined"]
+        b._b.inject_sever("up")
+        t0 = time.time()
+        while time.time() - t0 < 10 and b.stats()["rejoins"] < 1:
+            time.sleep(0.02)
+        kb = [e["kind"] for e in b.stats()["events"]]
+        assert kb[:2] == ["joined", "edge_lost"] and kb[-1] == "rejoined", kb
+        t0 = time.time()
+        while time.time() - t0 < 10 and [e["kind"] for e in a.stats()["events"]].count("adopted") < 2:
+            time.sleep(0.02)
+        ka = [e["kind"] for e in a.stats()["events"]]
+        assert "edge_lost" in ka and ka.count("adopted") == 2, ka
+        ev = b.stats()["events"][-1]
+        assert ev["ms"] > 1.6e12 and "below 127.0.0.1" in ev["detail"]
+    finally:
+        b.cfg.rejoin = False
+        b.close()
+        a.close()
