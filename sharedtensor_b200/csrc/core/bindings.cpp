@@ -83,6 +83,27 @@ void bind_core(py::module_& m) {
     decode_block_add(ptr<uint32_t>(words), ptr<uint8_t>(scales), n, block, ptr<float>(dst),
                      dst2 ? ptr<float>(dst2) : nullptr);
   });
+  m.def("encode_block_int", [](uintptr_t v, uintptr_t k, size_t n, int block, int min_exp, int rel_bits, int bits, uintptr_t codes,
+                               uintptr_t scales) {
+    if (bits != 2 && bits != 4 && bits != 8) throw std::invalid_argument("integer frames have 2, 4 or 8 bits per element");
+    BlockGate g;
+    g.min_exp = min_exp;
+    g.rel_bits = rel_bits;
+    return encode_block_int(ptr<float>(v), ptr<float>(k), n, block, g, bits, ptr<uint8_t>(codes), ptr<uint8_t>(scales));
+  });
+  m.def("block_int_steps", [](uintptr_t codes, uintptr_t scales, size_t n, int block, int bits, uintptr_t steps) {
+    block_int_steps(ptr<uint8_t>(codes), ptr<uint8_t>(scales), n, block, bits, ptr<float>(steps));
+  });
+  m.def("block_sign_steps", [](uintptr_t words, uintptr_t scales, size_t n, int block, uintptr_t steps) {
+    block_sign_steps(ptr<uint32_t>(words), ptr<uint8_t>(scales), n, block, ptr<float>(steps));
+  });
+  m.def("block_code_int", [](float xmax, uint32_t vmax_bits, int min_exp, int rel_bits, int bits) {
+    BlockGate g;
+    g.min_exp = min_exp;
+    g.rel_bits = rel_bits;
+    return block_code_int(xmax, vmax_bits, g, bits);
+  });
+  m.def("pack_tile_codes", [](uintptr_t codes, int bits, uintptr_t out) { pack_tile_codes(ptr<uint8_t>(codes), bits, ptr<uint32_t>(out)); });
   m.def("segment_sumsq", [](uintptr_t x, std::vector<int64_t> offsets) {
     std::vector<double> out(offsets.size() - 1);
     segment_sumsq(ptr<float>(x), offsets.data(), int(out.size()), out.data());

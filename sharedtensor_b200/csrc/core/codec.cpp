@@ -180,6 +180,103 @@ void decode_block_add(const uint32_t* words, const uint8_t* scales, size_t n, in
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// integer block frames
+// ---------------------------------------------------------------------------------------------
+int block_code_int(float xmax, uint32_t vmax_bits, const BlockGate& gate, int bits) {
+  const uint32_t xb = f32_bits(xmax) & 0x7fffffffu;
+  const int ef = int(xb >> 23);
+  if (ef == 0 || ef == 255) return kSilent;       // zero, denormal, infinite or NaN
+  const int ex = ef - 127;
+  if (ex > 100) return kSilent;
+  const uint32_t mant = xb & 0x7fffffu;
+  // smallest exponent for which round(xmax / 2^e) <= 2^(bits-1) - 1
+  int es = ex - (bits - 2);
+  if (mant >= (1u << 23) - (1u << (24 - bits))) es += 1;
+  if (es < gate.min_exp) es = gate.min_exp;
+  if ((vmax_bits >> 23) != 0) {
+    const int emax = int((vmax_bits >> 23) & 0xff) - 127;
+    if (es < emax - gate.rel_bits) es = emax - gate.rel_bits;
+  }
+  if (es < kMinExp) es = kMinExp;
+  // every element would round to zero: xmax <= 2^(es-1)
+  if (ex < es - 1 || (ex == es - 1 && mant == 0)) return kSilent;
+  return es + 127;
+}
+
+double encode_block_int(const float* v, float* k, size_t n, int block, const BlockGate& gate, int bits, uint8_t* codes,
+                        uint8_t* scales) {
+  const size_t nb = block_scales(n, block);
+  const float M = 8388608.0f + float(1 << (bits - 1));
+  const uint32_t mask = (1u << bits) - 1u;
+  double worst = 0.0;
+  for (size_t b = 0; b < nb; b++) {
+    const size_t base = b * size_t(block);
+    const size_t end = base + size_t(block) < n ? base + size_t(block) : n;
+    float xmax = 0.0f;
+    uint32_t vmax = 0;
+    for (size_t i = base; i < end; i++) {
+      float ax = std::fabs(v[i] - k[i]);
+      if (ax > xmax) xmax = ax;
+      uint32_t a = f32_bits(v[i]) & 0x7fffffffu;
+      if (a > vmax) vmax = a;
+    }
+    if (double(xmax) > worst) worst = double(xmax);
+    const int code = block_code_int(xmax, vmax, gate, bits);
+    scales[b] = uint8_t(code);
+    if (!code) {
+      for (size_t i = base; i < end; i++) codes[i] = uint8_t(1u << (bits - 1));
+      continue;
+    }
+    const float s = exp2i(code - 127), inv = exp2i(127 - code), neg_ms = -(M * s);
+    for (size_t i = base; i < end; i++) {
+      const float x = v[i] - k[i];
+      const float z = std::fmaf(x, inv, M);
+      codes[i] = uint8_t(f32_bits(z) & mask);
+      k[i] += std::fmaf(z, s, neg_ms);
+    }
+  }
+  return worst;
+}
+
+void block_int_steps(const uint8_t* codes, const uint8_t* scales, size_t n, int block, int bits, float* steps) {
+  const size_t nb = block_scales(n, block);
+  const float M = 8388608.0f + float(1 << (bits - 1));
+  for (size_t b = 0; b < nb; b++) {
+    const int code = scales[b];
+    const size_t base = b * size_t(block);
+    const size_t end = base + size_t(block) < n ? base + size_t(block) : n;
+    if (code == 0 || code == 255) {
+      for (size_t i = base; i < end; i++) steps[i] = 0.0f;
+      continue;
+    }
+    const float s = exp2i(code - 127), neg_ms = -(M * s);
+    for (size_t i = base; i < end; i++) steps[i] = std::fmaf(bits_f32(0x4b000000u | codes[i]), s, neg_ms);
+  }
+}
+
+void block_sign_steps(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* steps) {
+  const size_t nb = block_scales(n, block);
+  for (size_t b = 0; b < nb; b++) {
+    const int code = scales[b];
+    const size_t base = b * size_t(block);
+    const size_t end = base + size_t(block) < n ? base + size_t(block) : n;
+    const float s = (code == 0 || code == 255) ? 0.0f : exp2i(code - 127);
+    for (size_t i = base; i < end; i++) steps[i] = s == 0.0f ? 0.0f : (((words[i >> 5] >> (i & 31)) & 1u) ? -s : s);
+  }
+}
+
+void pack_tile_codes(const uint8_t* codes, int bits, uint32_t* out) {
+  for (int w = 0; w < bits * 128; w++) out[w] = 0;
+  const uint32_t mask = (1u << bits) - 1u;
+  for (int i = 0; i < 4096; i++) {
+    const int c = i >> 5, g = (i >> 2) & 7, e = i & 3;
+    const int pos = c * 32 + ((g ^ (c & 7)) << 2) + e;   // position in the tile's code stream
+    const int bit = pos * bits;
+    out[bit >> 5] |= (uint32_t(codes[i]) & mask) << (bit & 31);
+  }
+}
+
 void segment_sumsq(const float* x, const int64_t* offsets, int n_seg, double* out) {
   for (int s = 0; s < n_seg; s++) {
     double acc = 0.0;

@@ -115,6 +115,44 @@ double encode_block_fast(const float* v, float* k, size_t n, int block, const Bl
                          uint8_t* scales);
 void decode_block_add_fast(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* dst, float* dst2);
 
+// ---------------------------------------------------------------------------------------------
+// Integer block frames (GPU rings with 2, 4 or 8 bits per element; CPU oracle)
+//
+// One exponent byte per block (as above) and one `bits`-bit integer per element: the block's residuals
+// x = v - k are rounded to the nearest multiple of the block's step 2^e (ties to even) and the multiple m,
+// |m| <= 2^(bits-1) - 1, travels as m + 2^(bits-1).  The step is the smallest power of two for which the
+// block's largest residual still fits, but never below the cut-off of BlockGate, so one frame takes the
+// largest residual of a block down by a factor of about 2^(bits-1): 8-bit frames bring a fresh update to
+// under one percent in a single frame where sign frames (the reference's 1 bit per element,
+// src/sharedtensor.c:166-174) need about ten.  A residual of zero is the code of zero: elements that have
+// nothing to say do not move.  The arithmetic is spelled out so that the kernels (../cuda/round.cu) and this
+// file agree bit for bit:
+//   z = fma(x, 2^-e, M)   with M = 2^23 + 2^(bits-1)      (the low bits of z's mantissa are the code)
+//   step = fma(z, 2^e, -(M * 2^e))                         (exact: (z - M) * 2^e)
+//   k += step
+// Residuals at or above 2^101 are not sent (the block stays silent): M * 2^e must not overflow.
+// ---------------------------------------------------------------------------------------------
+
+// Exponent code (0 = silent) of a block from its largest |residual| and the bits of its largest |value|.
+int block_code_int(float xmax, uint32_t vmax_bits, const BlockGate& gate, int bits);
+
+// Encodes n elements into one code byte per element (unpacked; the low `bits` bits are used) and one scale
+// byte per block; steps the mirror.  Returns the largest |residual| before the update.
+double encode_block_int(const float* v, float* k, size_t n, int block, const BlockGate& gate, int bits, uint8_t* codes,
+                        uint8_t* scales);
+
+// The step every element receives from one frame (0 where the block is silent), for integer frames
+// (bits = 2, 4, 8; `codes` one byte per element) ...
+void block_int_steps(const uint8_t* codes, const uint8_t* scales, size_t n, int block, int bits, float* steps);
+// ... and for sign frames (`words` as produced by encode_block).
+void block_sign_steps(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* steps);
+
+// Layout of one tile (4096 elements) in a GPU ring slot: `bits` * 128 words of codes, then the scale bytes.
+// Codes are packed little-endian, `bits` per element, in the order the kernel's threads hold them: within
+// the c-th run of 32 elements the g-th group of four elements sits at position g ^ (c & 7).  `codes` holds
+// 4096 unpacked codes (for sign frames: 0 or 1), `out` receives bits * 128 words.
+void pack_tile_codes(const uint8_t* codes, int bits, uint32_t* out);
+
 // Per-segment sum of squares over a flat arena (table sync; README.md:41 of the reference lists
 // per-tensor magnitudes as a TODO).  offsets has n_seg+1 entries.
 void segment_sumsq(const float* x, const int64_t* offsets, int n_seg, double* out);

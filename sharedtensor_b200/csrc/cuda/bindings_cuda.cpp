@@ -50,12 +50,16 @@ PYBIND11_MODULE(_cuda, m) {
   m.def("snapshot_bf16", [](uintptr_t v, uintptr_t out, int64_t n, uintptr_t s) {
     ck(launch_snapshot_bf16(ptr<float>(v), ptr<void>(out), n, strm(s)), "snapshot_bf16");
   });
-  m.def("add", [](uintptr_t v, uintptr_t d, int64_t n, uintptr_t tile_state, int n_tiles, bool atomic, uintptr_t s) {
-    ck(launch_add(ptr<float>(v), ptr<float>(d), n, ptr<uint8_t>(tile_state), n_tiles, atomic, strm(s)), "add");
+  m.def("add", [](uintptr_t v, uintptr_t d, int64_t n, bool atomic, uintptr_t s) {
+    ck(launch_add(ptr<float>(v), ptr<float>(d), n, atomic, strm(s)), "add");
   });
-  m.def("sub_add", [](uintptr_t v, uintptr_t a, uintptr_t b, int64_t n, uintptr_t tile_state, int n_tiles, bool atomic, uintptr_t s) {
-    ck(launch_sub_add(ptr<float>(v), ptr<float>(a), ptr<float>(b), n, ptr<uint8_t>(tile_state), n_tiles, atomic, strm(s)), "sub_add");
+  m.def("sub_add", [](uintptr_t v, uintptr_t a, uintptr_t b, int64_t n, bool atomic, uintptr_t s) {
+    ck(launch_sub_add(ptr<float>(v), ptr<float>(a), ptr<float>(b), n, atomic, strm(s)), "sub_add");
   });
+  m.def("add_scaled_bf16", [](uintptr_t v, uintptr_t g, float alpha, int64_t n, bool atomic, uintptr_t s) {
+    ck(launch_add_scaled_bf16(ptr<float>(v), ptr<void>(g), alpha, n, atomic, strm(s)), "add_scaled_bf16");
+  });
+  m.def("round_smem_bytes", &round_smem_bytes);
   m.def("table_scales_scratch_doubles", &table_scales_scratch_doubles);
   m.def("table_scales", [](uintptr_t x, uintptr_t offsets, int n_seg, int64_t n_total, uintptr_t scratch, uintptr_t out_sumsq,
                            uintptr_t out_exp, uintptr_t s) {
@@ -74,8 +78,7 @@ PYBIND11_MODULE(_cuda, m) {
     ck(launch_tensor_encode(ptr<float>(v), ptr<float>(k), n, scale, ptr<uint32_t>(words), strm(s)), "tensor_encode");
   });
   m.def("tensor_decode", [](uintptr_t words, float scale, int64_t n, uintptr_t v, uintptr_t k, uintptr_t s) {
-    ck(launch_tensor_decode(ptr<uint32_t>(words), scale, n, ptr<float>(v), k ? ptr<float>(k) : nullptr, nullptr, strm(s)),
-       "tensor_decode");
+    ck(launch_tensor_decode(ptr<uint32_t>(words), scale, n, ptr<float>(v), k ? ptr<float>(k) : nullptr, 0, strm(s)), "tensor_decode");
   });
 
   // ---- GPU replica ----
@@ -90,8 +93,9 @@ PYBIND11_MODULE(_cuda, m) {
       .def_readwrite("rounds_in_flight", &GpuConfig::rounds_in_flight)
       .def_readwrite("idle_sleep_us", &GpuConfig::idle_sleep_us)
       .def_readwrite("round_interval_us", &GpuConfig::round_interval_us)
-      .def_readwrite("frames_per_round", &GpuConfig::frames_per_round)
-      .def_readwrite("use_graph", &GpuConfig::use_graph);
+      .def_readwrite("bits", &GpuConfig::bits)
+      .def_readwrite("sweeps", &GpuConfig::sweeps)
+      .def_readwrite("poll_deadline_us", &GpuConfig::poll_deadline_us);
 
   py::class_<GpuReplica>(m, "GpuReplica")
       .def(py::init<int, int64_t, const GpuConfig&>())
@@ -128,7 +132,10 @@ PYBIND11_MODULE(_cuda, m) {
       .def("snapshot", [](GpuReplica& r, uintptr_t out, uintptr_t s) { r.snapshot(ptr<float>(out), strm(s)); })
       .def("snapshot_bf16", [](GpuReplica& r, uintptr_t out, uintptr_t s) { r.snapshot_bf16(ptr<void>(out), strm(s)); })
       .def("copy_mirror_from_values", &GpuReplica::copy_mirror_from_values)
-      .def("round", &GpuReplica::round, py::arg("do_rx") = true, py::arg("do_tx") = true)
+      .def("round", &GpuReplica::round, py::arg("do_rx") = true, py::arg("do_tx") = true, py::arg("sweeps") = 1)
+      .def("set_test_stall_tile", &GpuReplica::set_test_stall_tile)
+      .def("check_guards", [](GpuReplica& r) { py::gil_scoped_release rel; return r.check_guards(); })
+      .def("bits", &GpuReplica::bits)
       .def("sync", [](GpuReplica& r) { py::gil_scoped_release rel; r.sync(); })
       .def("start_engine", &GpuReplica::start_engine)
       .def("stop_engine", [](GpuReplica& r) { py::gil_scoped_release rel; r.stop_engine(); })

@@ -103,10 +103,9 @@ int launch_snapshot_bf16(const float* values, void* out, int64_t n, void* stream
 // ---------------------------------------------------------------------------------------------
 template <bool SUB, bool ATOMIC>
 __global__ void __launch_bounds__(kEwThreads) add_vec(float4* __restrict__ values, const float4* __restrict__ a, const float4* __restrict__ b,
-                                                      int64_t n4, uint8_t* __restrict__ tile_state, int n_tiles) {
+                                                      int64_t n4) {
   int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * kEwThreads;
-  for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
   // four independent 16-byte streams per thread and iteration
   for (; i + 3 * stride < n4; i += 4 * stride) {
     float4 d[4], v[4];
@@ -148,12 +147,9 @@ __global__ void __launch_bounds__(kEwThreads) add_vec(float4* __restrict__ value
   }
 }
 template <bool SUB, bool ATOMIC>
-__global__ void add_scalar(float* __restrict__ values, const float* __restrict__ a, const float* __restrict__ b, int64_t begin, int64_t n,
-                           uint8_t* __restrict__ tile_state, int n_tiles, int mark) {
+__global__ void add_scalar(float* __restrict__ values, const float* __restrict__ a, const float* __restrict__ b, int64_t begin, int64_t n) {
   int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  if (mark)
-    for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
   for (i += begin; i < n; i += stride) {
     float d = SUB ? a[i] - b[i] : a[i];
     if (ATOMIC)
@@ -164,83 +160,89 @@ __global__ void add_scalar(float* __restrict__ values, const float* __restrict__
 }
 
 template <bool SUB>
-static int launch_add_t(float* values, const float* a, const float* b, int64_t n, uint8_t* tile_state, int n_tiles, int atomic,
-                        cudaStream_t s) {
+static int launch_add_t(float* values, const float* a, const float* b, int64_t n, int atomic, cudaStream_t s) {
   bool al = aligned16(values) && aligned16(a) && (!SUB || aligned16(b));
   int64_t n4 = al ? n / 4 : 0;
   if (n4) {
     int blocks = ew_blocks(n4 / 4 + 1);
     if (atomic)
       add_vec<SUB, true><<<blocks, kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), reinterpret_cast<const float4*>(a),
-                                                       reinterpret_cast<const float4*>(b), n4, tile_state, n_tiles);
+                                                       reinterpret_cast<const float4*>(b), n4);
     else
       add_vec<SUB, false><<<blocks, kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), reinterpret_cast<const float4*>(a),
-                                                        reinterpret_cast<const float4*>(b), n4, tile_state, n_tiles);
+                                                        reinterpret_cast<const float4*>(b), n4);
   }
   if (n4 * 4 < n) {
     int blocks = ew_blocks(n - n4 * 4);
     if (atomic)
-      add_scalar<SUB, true><<<blocks, kEwThreads, 0, s>>>(values, a, b, n4 * 4, n, tile_state, n_tiles, n4 == 0);
+      add_scalar<SUB, true><<<blocks, kEwThreads, 0, s>>>(values, a, b, n4 * 4, n);
     else
-      add_scalar<SUB, false><<<blocks, kEwThreads, 0, s>>>(values, a, b, n4 * 4, n, tile_state, n_tiles, n4 == 0);
+      add_scalar<SUB, false><<<blocks, kEwThreads, 0, s>>>(values, a, b, n4 * 4, n);
   }
   return int(cudaGetLastError());
 }
 
-int launch_add(float* values, const float* delta, int64_t n, uint8_t* tile_state, int n_tiles, int atomic, void* stream) {
-  return launch_add_t<false>(values, delta, nullptr, n, tile_state, n_tiles, atomic, static_cast<cudaStream_t>(stream));
+int launch_add(float* values, const float* delta, int64_t n, int atomic, void* stream) {
+  return launch_add_t<false>(values, delta, nullptr, n, atomic, static_cast<cudaStream_t>(stream));
 }
-int launch_sub_add(float* values, const float* neu, const float* old, int64_t n, uint8_t* tile_state, int n_tiles, int atomic,
-                   void* stream) {
-  return launch_add_t<true>(values, neu, old, n, tile_state, n_tiles, atomic, static_cast<cudaStream_t>(stream));
+int launch_sub_add(float* values, const float* neu, const float* old, int64_t n, int atomic, void* stream) {
+  return launch_add_t<true>(values, neu, old, n, atomic, static_cast<cudaStream_t>(stream));
 }
 
 // values += alpha * g for a bf16 gradient: the optimiser step of plain SGD fused with addFromTensor, so
 // that bf16 training never materialises an fp32 delta.
+template <bool ATOMIC>
 __global__ void __launch_bounds__(kEwThreads) add_scaled_bf16_vec(float4* __restrict__ values, const uint2* __restrict__ g, float alpha,
-                                                                  int64_t n4, uint8_t* __restrict__ tile_state, int n_tiles) {
+                                                                  int64_t n4) {
   int64_t i = int64_t(blockIdx.x) * kEwThreads + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * kEwThreads;
-  for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
   for (; i < n4; i += stride) {
     uint2 raw = g[i];
     __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
     float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
-    float4 v = values[i];
-    v.x += alpha * a.x;
-    v.y += alpha * a.y;
-    v.z += alpha * b.x;
-    v.w += alpha * b.y;
-    values[i] = v;
+    if (ATOMIC) {
+      red_add_v4(reinterpret_cast<float*>(values + i), make_float4(alpha * a.x, alpha * a.y, alpha * b.x, alpha * b.y));
+    } else {
+      float4 v = values[i];
+      v.x += alpha * a.x;
+      v.y += alpha * a.y;
+      v.z += alpha * b.x;
+      v.w += alpha * b.y;
+      values[i] = v;
+    }
   }
 }
+template <bool ATOMIC>
 __global__ void add_scaled_bf16_scalar(float* __restrict__ values, const __nv_bfloat16* __restrict__ g, float alpha, int64_t begin,
-                                       int64_t n, uint8_t* __restrict__ tile_state, int n_tiles, int mark) {
+                                       int64_t n) {
   int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  if (mark)
-    for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
-  for (i += begin; i < n; i += stride) values[i] += alpha * __bfloat162float(g[i]);
+  for (i += begin; i < n; i += stride) {
+    if (ATOMIC) atomicAdd(values + i, alpha * __bfloat162float(g[i]));
+    else values[i] += alpha * __bfloat162float(g[i]);
+  }
 }
-int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, uint8_t* tile_state, int n_tiles, void* stream_v) {
+int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, int atomic, void* stream_v) {
   cudaStream_t s = static_cast<cudaStream_t>(stream_v);
   bool al = aligned16(values) && (reinterpret_cast<uintptr_t>(g_bf16) & 7) == 0;
   int64_t n4 = al ? n / 4 : 0;
-  if (n4)
-    add_scaled_bf16_vec<<<ew_blocks(n4), kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), static_cast<const uint2*>(g_bf16), alpha,
-                                                            n4, tile_state, n_tiles);
-  if (n4 * 4 < n)
-    add_scaled_bf16_scalar<<<ew_blocks(n - n4 * 4), kEwThreads, 0, s>>>(values, static_cast<const __nv_bfloat16*>(g_bf16), alpha, n4 * 4,
-                                                                        n, tile_state, n_tiles, n4 == 0);
+  if (n4) {
+    if (atomic) add_scaled_bf16_vec<true><<<ew_blocks(n4), kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), static_cast<const uint2*>(g_bf16), alpha, n4);
+    else add_scaled_bf16_vec<false><<<ew_blocks(n4), kEwThreads, 0, s>>>(reinterpret_cast<float4*>(values), static_cast<const uint2*>(g_bf16), alpha, n4);
+  }
+  if (n4 * 4 < n) {
+    if (atomic) add_scaled_bf16_scalar<true><<<ew_blocks(n - n4 * 4), kEwThreads, 0, s>>>(values, static_cast<const __nv_bfloat16*>(g_bf16), alpha, n4 * 4, n);
+    else add_scaled_bf16_scalar<false><<<ew_blocks(n - n4 * 4), kEwThreads, 0, s>>>(values, static_cast<const __nv_bfloat16*>(g_bf16), alpha, n4 * 4, n);
+  }
   return int(cudaGetLastError());
 }
 
-__global__ void fill_state_kernel(uint8_t* s, int n, uint8_t v) {
+__global__ void fill_state_kernel(uint32_t* s, int n, uint32_t v) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) s[i] = v;
 }
-int launch_fill_state(uint8_t* tile_state, int n_tiles, int value, void* stream) {
-  fill_state_kernel<<<(n_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tile_state, n_tiles, uint8_t(value));
+int launch_fill_state(uint32_t* tile_state, int n_tiles, uint32_t value, void* stream) {
+  fill_state_kernel<<<(n_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tile_state, n_tiles, value);
   return int(cudaGetLastError());
 }
 
@@ -453,22 +455,22 @@ int launch_tensor_encode(const float* v, float* k, int64_t n, float scale, uint3
   tensor_encode_kernel<<<ew_blocks(n_words * 32, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(v, k, n, scale, words, n_words);
   return int(cudaGetLastError());
 }
+template <bool ATOMIC>
 __global__ void __launch_bounds__(256) tensor_decode_kernel(const uint32_t* __restrict__ words, float scale, int64_t n, float* __restrict__ v,
-                                                            float* __restrict__ k, uint8_t* __restrict__ tile_state, int n_tiles) {
+                                                            float* __restrict__ k) {
   int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * 256;
-  if (tile_state)
-    for (int64_t t = i; t < n_tiles; t += stride) tile_state[t] = 1;
   for (; i < n; i += stride) {
     float f = ((words[i >> 5] >> (i & 31)) & 1u) ? -scale : scale;
-    v[i] += f;
+    if (ATOMIC) atomicAdd(v + i, f);
+    else v[i] += f;
     if (k) k[i] += f;
   }
 }
-int launch_tensor_decode(const uint32_t* words, float scale, int64_t n, float* v, float* k, uint8_t* tile_state, void* stream) {
+int launch_tensor_decode(const uint32_t* words, float scale, int64_t n, float* v, float* k, int atomic_v, void* stream) {
   if (scale == 0.f) return 0;
-  int n_tiles = int((n + kTile - 1) / kTile);
-  tensor_decode_kernel<<<ew_blocks(n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(words, scale, n, v, k, tile_state, n_tiles);
+  if (atomic_v) tensor_decode_kernel<true><<<ew_blocks(n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(words, scale, n, v, k);
+  else tensor_decode_kernel<false><<<ew_blocks(n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(words, scale, n, v, k);
   return int(cudaGetLastError());
 }
 

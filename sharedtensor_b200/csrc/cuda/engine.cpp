@@ -42,44 +42,43 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
     throw std::invalid_argument("block must be a power of two in 32..4096");
   if (cfg.ring_slots < 2 || cfg.ring_slots > 64 || (cfg.ring_slots & (cfg.ring_slots - 1)))
     throw std::invalid_argument("ring_slots must be a power of two in 2..64");
+  if (cfg.bits != 1 && cfg.bits != 2 && cfg.bits != 4 && cfg.bits != 8)
+    throw std::invalid_argument("bits per element must be 1, 2, 4 or 8");
   DeviceGuard g(device_);
   n_tiles_ = int((n + kTile - 1) / kTile);
   n_padded_ = int64_t(n_tiles_) * kTile;
   int lb = 0;
   while ((1 << lb) < cfg.block) lb++;
   const int spt = kTile >> lb;
-  const int pb = 4 * kWordsPerTile + (spt < 16 ? 16 : spt);
-  layout_.off_payload = 0;
-  layout_.off_flags = align_up(size_t(cfg.ring_slots) * n_tiles_ * pb, 256);
+  const int pb = cfg.bits * 4 * kWordsPerTile + (spt < 16 ? 16 : spt);
+  // an edge block: canary, ring payload slots, sequence flags, credit words, canary
+  layout_.off_payload = kGuardBytes;
+  layout_.off_flags = layout_.off_payload + align_up(size_t(cfg.ring_slots) * n_tiles_ * pb, 256);
   layout_.off_credit = layout_.off_flags + align_up(size_t(cfg.ring_slots) * n_tiles_ * 4, 256);
-  layout_.bytes = layout_.off_credit + align_up(size_t(n_tiles_) * 4, 256);
-
-  std::string err;
-  values_ = vmm_alloc(device_, size_t(n_padded_) * 4, cfg.shareable, &err);
-  if (!values_.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate values: " + err);
-  links_.resize(kMaxLinks);
-  blocks_.resize(kMaxRings);
-  peers_.resize(kMaxRings);
-
-  check(cudaMalloc(reinterpret_cast<void**>(&ctrl_), size_t(n_tiles_) * 16), "cudaMalloc ctrl");
-  check(cudaMalloc(reinterpret_cast<void**>(&sent_), size_t(n_tiles_) * 8), "cudaMalloc sent");
-  check(cudaMalloc(reinterpret_cast<void**>(&tile_state_), size_t(n_tiles_)), "cudaMalloc tile_state");
-  check(cudaMalloc(reinterpret_cast<void**>(&worklist_), size_t(n_tiles_) * 4), "cudaMalloc worklist");
-  check(cudaMalloc(reinterpret_cast<void**>(&work_count_), 2 * 4), "cudaMalloc work_count");
-  check(cudaMalloc(reinterpret_cast<void**>(&status_), kStTotalWords * 8), "cudaMalloc status");
-  check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), kStTotalWords * 8), "cudaMallocHost status");
-  check(cudaMemset(ctrl_, 0, size_t(n_tiles_) * 16), "memset");
-  check(cudaMemset(sent_, 0, size_t(n_tiles_) * 8), "memset");
-  check(cudaMemset(tile_state_, 1, size_t(n_tiles_)), "memset");
-  check(cudaMemset(work_count_, 0, 8), "memset");
-  check(cudaMemset(status_, 0, kStTotalWords * 8), "memset");
-  std::memset(status_host_, 0, kStTotalWords * 8);
+  layout_.bytes = layout_.off_credit + align_up(size_t(n_tiles_) * 4, 256) + kGuardBytes;
 
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
   cudaStream_t s;
   check(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi), "cudaStreamCreate");
   comm_ = s;
+
+  std::string err;
+  values_ = vmm_alloc(device_, size_t(n_padded_) * 4 + 2 * kGuardBytes, cfg.shareable, &err);
+  if (!values_.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate values: " + err);
+  fill_guards(values_, size_t(n_padded_) * 4 + 2 * kGuardBytes);
+  links_.resize(kMaxLinks);
+  blocks_.resize(kMaxRings);
+  peers_.resize(kMaxRings);
+
+  // Everything is zeroed on the comm stream, the stream that uses it (a plain cudaMemset would run on the legacy
+  // default stream, which nothing here is ordered against).
+  check(cudaMalloc(reinterpret_cast<void**>(&tile_state_), size_t(n_tiles_) * 4), "cudaMalloc tile_state");
+  check(cudaMalloc(reinterpret_cast<void**>(&status_), kDsTotalWords * 8), "cudaMalloc status");
+  check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), (kDsTotalWords + 16) * 8), "cudaMallocHost status");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
+  check(cudaMemsetAsync(status_, 0, kDsTotalWords * 8, s), "memset");
+  std::memset(status_host_, 0, (kDsTotalWords + 16) * 8);
   cudaEvent_t e1, e2;
   check(cudaEventCreateWithFlags(&e1, cudaEventDisableTiming), "cudaEventCreate");
   check(cudaEventCreateWithFlags(&e2, cudaEventDisableTiming), "cudaEventCreate");
@@ -100,16 +99,15 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   params_.ring_slots = cfg.ring_slots;
   params_.log2_block = lb;
   params_.scales_per_tile = spt;
+  params_.bits = cfg.bits;
   params_.payload_bytes = pb;
   params_.min_exp = cfg.min_exp;
   params_.rel_bits = cfg.rel_bits;
-  params_.ctrl = ctrl_;
-  params_.sent = sent_;
   params_.tile_state = tile_state_;
-  params_.worklist = worklist_;
-  params_.work_count = work_count_;
   params_.status = status_;
-  params_.frames_per_round = cfg.frames_per_round < 1 ? 1 : (cfg.frames_per_round > 3 ? 3 : cfg.frames_per_round);
+  params_.sweeps = 1;
+  params_.wait_ns = uint32_t(cfg.poll_deadline_us < 1 ? 1 : (cfg.poll_deadline_us > 2000000 ? 2000000 : cfg.poll_deadline_us)) * 1000u;
+  params_.stall_tile = -1;
   check(cudaDeviceSynchronize(), "init");
 }
 
@@ -124,13 +122,8 @@ GpuReplica::~GpuReplica() {
   for (auto& l : links_) vmm_free(&l.mirror);
   for (auto& b : blocks_) vmm_free(&b.mem);
   vmm_free(&values_);
-  cudaFree(ctrl_);
-  cudaFree(sent_);
   cudaFree(tile_state_);
-  cudaFree(worklist_);
-  cudaFree(work_count_);
   cudaFree(status_);
-  if (graph_exec_) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
   if (status_host_) cudaFreeHost(status_host_);
   if (tcp_words_dev_) cudaFree(tcp_words_dev_);
   if (tcp_stat_dev_) cudaFree(tcp_stat_dev_);
@@ -151,8 +144,9 @@ int GpuReplica::add_link() {
     if (!links_[i].used) {
       std::string err;
       publish_pending();
-      links_[i].mirror = vmm_alloc(device_, size_t(n_padded_) * 4, false, &err);
+      links_[i].mirror = vmm_alloc(device_, size_t(n_padded_) * 4 + 2 * kGuardBytes, false, &err);
       if (!links_[i].mirror.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate mirror: " + err);
+      fill_guards(links_[i].mirror, size_t(n_padded_) * 4 + 2 * kGuardBytes);
       links_[i].used = true;
       rebuild_params();
       return i;
@@ -187,6 +181,7 @@ int GpuReplica::alloc_edge_block() {
       std::string err;
       blocks_[i].mem = vmm_alloc(device_, layout_.bytes, cfg_.shareable, &err);
       if (!blocks_[i].mem.ptr) throw std::runtime_error("sharedtensor GPU engine: cannot allocate edge block: " + err);
+      fill_guards(blocks_[i].mem, layout_.bytes);
       blocks_[i].used = true;
       return i;
     }
@@ -215,14 +210,14 @@ int GpuReplica::attach_peer(int link, int local_block, void* remote_base) {
       publish_pending();
       check(cudaMalloc(reinterpret_cast<void**>(&p.rx_seq), size_t(n_tiles_) * 4), "cudaMalloc rx_seq");
       check(cudaMalloc(reinterpret_cast<void**>(&p.tx_seq), size_t(n_tiles_) * 4), "cudaMalloc tx_seq");
-      check(cudaMemset(p.rx_seq, 0, size_t(n_tiles_) * 4), "memset");
-      check(cudaMemset(p.tx_seq, 0, size_t(n_tiles_) * 4), "memset");
+      check(cudaMemsetAsync(p.rx_seq, 0, size_t(n_tiles_) * 4, S(comm_)), "memset");
+      check(cudaMemsetAsync(p.tx_seq, 0, size_t(n_tiles_) * 4, S(comm_)), "memset");
       p.link = link;
       p.local_block = local_block;
       p.remote = static_cast<uint8_t*>(remote_base);
       p.used = true;
       // whatever the link still had to say must be looked at again
-      launch_fill_state(tile_state_, n_tiles_, 1, comm_);
+      launch_fill_state(tile_state_, n_tiles_, 1u, comm_);
       rebuild_params();
       return i;
     }
@@ -263,11 +258,6 @@ void GpuReplica::publish_pending() {
 }
 
 void GpuReplica::rebuild_params() {
-  if (graph_exec_) {
-    cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
-    graph_exec_ = nullptr;
-  }
-  graph_warm_ = false;
   int dense = 0;
   for (int i = 0; i < kMaxLinks; i++) {
     map_link_[i] = -1;
@@ -280,7 +270,7 @@ void GpuReplica::rebuild_params() {
     for (auto& p : peers_) has_peer |= p.used && p.link == i;
     if (!has_peer) continue;
     map_link_[i] = dense;
-    params_.mirror[dense] = static_cast<float*>(links_[i].mirror.ptr);
+    params_.mirror[dense] = mirror(i);
     dense++;
   }
   params_.n_links = dense;
@@ -320,6 +310,59 @@ void GpuReplica::order_user_after(void* user_stream) {
   check(cudaStreamWaitEvent(S(user_stream), E(ev_comm_), 0), "cudaStreamWaitEvent");
 }
 
+void GpuReplica::gate_lock() {
+  gate_mu_.lock();
+  // updates already issued on user streams have to be in the values before the holder looks at them
+  DeviceGuard g(device_);
+  cudaDeviceSynchronize();
+}
+
+// canaries at both ends of the used part of a block (the mapped size may be larger: it is rounded to the granularity)
+void GpuReplica::fill_guards(const VmmBlock& b, size_t used_bytes) {
+  uint8_t* base = static_cast<uint8_t*>(b.ptr);
+  cudaMemsetAsync(base, 0xA5, kGuardBytes, S(comm_));
+  cudaMemsetAsync(base + used_bytes - kGuardBytes, 0xA5, kGuardBytes, S(comm_));
+}
+
+int GpuReplica::check_guards() {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  std::vector<uint8_t> host(kGuardBytes);
+  int bad = 0;
+  auto look = [&](const uint8_t* p) {
+    if (cudaMemcpy(host.data(), p, kGuardBytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+      cudaGetLastError();
+      bad++;
+      return;
+    }
+    for (size_t i = 0; i < kGuardBytes; i++)
+      if (host[i] != 0xA5) {
+        bad++;
+        return;
+      }
+  };
+  const size_t arr = size_t(n_padded_) * 4;
+  look(static_cast<const uint8_t*>(values_.ptr));
+  look(static_cast<const uint8_t*>(values_.ptr) + kGuardBytes + arr);
+  for (auto& l : links_)
+    if (l.used) {
+      look(static_cast<const uint8_t*>(l.mirror.ptr));
+      look(static_cast<const uint8_t*>(l.mirror.ptr) + kGuardBytes + arr);
+    }
+  for (auto& b : blocks_)
+    if (b.used) {
+      look(static_cast<const uint8_t*>(b.mem.ptr));
+      look(static_cast<const uint8_t*>(b.mem.ptr) + layout_.bytes - kGuardBytes);
+    }
+  return bad;
+}
+
+void GpuReplica::set_test_stall_tile(int tile) {
+  std::lock_guard<std::mutex> lk(mu_);
+  params_.stall_tile = tile;
+}
+
 void GpuReplica::load_values(const float* src, void* user_stream) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
@@ -327,7 +370,7 @@ void GpuReplica::load_values(const float* src, void* user_stream) {
     std::lock_guard<std::mutex> lk(mu_);
     order_after_user(user_stream);
     check(cudaMemcpyAsync(values(), src, size_t(n_) * 4, cudaMemcpyDeviceToDevice, S(comm_)), "cudaMemcpyAsync");
-    check(launch_fill_state(tile_state_, n_tiles_, 1, comm_), "fill_state");
+    check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
     launches_ += 1;
     epoch_++;
     order_user_after(user_stream);
@@ -338,51 +381,39 @@ void GpuReplica::load_values(const float* src, void* user_stream) {
 void GpuReplica::add(const float* delta, void* user_stream) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
-  {
-    std::lock_guard<std::mutex> lk(mu_);
-    order_after_user(user_stream);
-    check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
-    epoch_++;
-    launches_ += 1;
-    order_user_after(user_stream);
-  }
+  check(launch_add(values(), delta, n_, 1, user_stream), "add kernel");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, user_stream), "fill_state");  // marks after the data, in stream order
+  epoch_++;
+  launches_ += 2;
   local_update();
 }
 
 void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
-  {
-    std::lock_guard<std::mutex> lk(mu_);
-    order_after_user(user_stream);
-    check(launch_sub_add(values(), neu, old, n_, tile_state_, n_tiles_, 0, comm_), "sub_add kernel");
-    epoch_++;
-    launches_ += 1;
-    order_user_after(user_stream);
-  }
+  check(launch_sub_add(values(), neu, old, n_, 1, user_stream), "sub_add kernel");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, user_stream), "fill_state");
+  epoch_++;
+  launches_ += 2;
   local_update();
 }
 
 void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) {
   DeviceGuard gd(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
-  {
-    std::lock_guard<std::mutex> lk(mu_);
-    order_after_user(user_stream);
-    check(launch_add_scaled_bf16(values(), g, alpha, n_, tile_state_, n_tiles_, comm_), "add_scaled_bf16 kernel");
-    epoch_++;
-    launches_ += 1;
-    order_user_after(user_stream);
-  }
+  check(launch_add_scaled_bf16(values(), g, alpha, n_, 1, user_stream), "add_scaled_bf16 kernel");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, user_stream), "fill_state");
+  epoch_++;
+  launches_ += 2;
   local_update();
 }
 
 void GpuReplica::add_gate_held(const float* delta) {
   DeviceGuard g(device_);
-  std::lock_guard<std::mutex> lk(mu_);
-  check(launch_add(values(), delta, n_, tile_state_, n_tiles_, 0, comm_), "add kernel");
+  check(launch_add(values(), delta, n_, 1, comm_), "add kernel");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
   epoch_++;
-  launches_ += 1;
+  launches_ += 2;
 }
 
 void GpuReplica::snapshot(float* out, void* user_stream) {
@@ -401,32 +432,45 @@ void GpuReplica::copy_mirror_from_values(int link) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> lk(mu_);
   if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
-  check(cudaMemcpyAsync(links_[link].mirror.ptr, values(), size_t(n_padded_) * 4, cudaMemcpyDeviceToDevice, S(comm_)),
-        "cudaMemcpyAsync");
+  check(cudaMemcpyAsync(mirror(link), values(), size_t(n_padded_) * 4, cudaMemcpyDeviceToDevice, S(comm_)), "cudaMemcpyAsync");
 }
 
 void GpuReplica::push_snapshot(int link, float* remote_values) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> lk(mu_);
   if (link < 0 || link >= kMaxLinks || !links_[link].used) throw std::invalid_argument("no such link");
-  check(launch_snapshot_join(values(), remote_values, static_cast<float*>(links_[link].mirror.ptr), n_padded_, comm_),
-        "snapshot_join kernel");
+  check(launch_snapshot_join(values(), remote_values, mirror(link), n_padded_, comm_), "snapshot_join kernel");
   launches_ += 1;
   check(cudaStreamSynchronize(S(comm_)), "snapshot_join");
 }
 
-void GpuReplica::round(bool do_rx, bool do_tx) {
+int GpuReplica::auto_sweeps() const {
+  if (cfg_.sweeps > 0) return cfg_.sweeps > 64 ? 64 : cfg_.sweeps;
+  // Small tensors: a pass takes a few microseconds, so one launch makes several and the host's launch latency is
+  // paid once per batch.  Large tensors: a pass is long enough by itself.
+  const int groups = ctas_ * 3;
+  const int per_group = (n_tiles_ + groups - 1) / groups;
+  int sw = 32 / (per_group < 1 ? 1 : per_group);
+  return sw < 1 ? 1 : (sw > 16 ? 16 : sw);
+}
+
+void GpuReplica::launch(bool do_rx, bool do_tx, int sweeps) {
+  params_.round = round_no_++;
+  params_.parity = params_.round & 1;
+  params_.do_rx = do_rx ? 1 : 0;
+  params_.do_tx = do_tx ? 1 : 0;
+  params_.sweeps = sweeps < 1 ? 1 : sweeps;
+  check(launch_round(params_, ctas_, comm_), "round kernel");
+  last_parity_ = params_.parity;
+  launches_ += 1;
+  epoch_++;
+}
+
+void GpuReplica::round(bool do_rx, bool do_tx, int sweeps) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> lk(mu_);
   if (params_.n_in == 0 && params_.n_out == 0) return;
-  params_.round = round_no_++;
-  params_.do_rx = do_rx ? 1 : 0;
-  params_.do_tx = do_tx ? 1 : 0;
-  check(launch_round_begin(params_, comm_), "round_begin kernel");
-  check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
-  check(launch_round_publish(params_, comm_), "round_publish kernel");
-  launches_ += 3;
-  epoch_++;
+  launch(do_rx, do_tx, sweeps);
 }
 
 float GpuReplica::tcp_encode(int link, uint32_t* words, float min_scale_abs, float min_scale_rel) {
@@ -439,7 +483,7 @@ float GpuReplica::tcp_encode(int link, uint32_t* words, float min_scale_abs, flo
     check(cudaMalloc(reinterpret_cast<void**>(&tcp_stat_dev_), 8), "cudaMalloc tcp stat");
     check(cudaMallocHost(reinterpret_cast<void**>(&tcp_pinned_), 8 + n_words * 4), "cudaMallocHost tcp staging");
   }
-  float* k = static_cast<float*>(links_[link].mirror.ptr);
+  float* k = mirror(link);
   check(cudaMemsetAsync(tcp_stat_dev_, 0, 8, S(comm_)), "memset");
   check(launch_tensor_maxabs(values(), k, n_, tcp_stat_dev_, comm_), "tensor_maxabs kernel");
   check(cudaMemcpyAsync(tcp_pinned_, tcp_stat_dev_, 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
@@ -481,11 +525,10 @@ void GpuReplica::tcp_decode(int link, const uint32_t* words, float scale) {
     }
     std::memcpy(tcp_pinned_ + 2, words, n_words * 4);
     check(cudaMemcpyAsync(tcp_words_dev_, tcp_pinned_ + 2, n_words * 4, cudaMemcpyHostToDevice, S(comm_)), "cudaMemcpyAsync");
-    check(launch_tensor_decode(tcp_words_dev_, scale, n_, values(), static_cast<float*>(links_[link].mirror.ptr), tile_state_,
-                               comm_),
-          "tensor_decode kernel");
+    check(launch_tensor_decode(tcp_words_dev_, scale, n_, values(), mirror(link), 1, comm_), "tensor_decode kernel");
+    check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
     check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
-    launches_ += 1;
+    launches_ += 2;
     epoch_++;
   }
   local_update();  // the frame has to travel on over the other links
@@ -500,10 +543,10 @@ void GpuReplica::tcp_unsend(int link, const uint32_t* words, float scale) {
   std::memcpy(tcp_pinned_ + 2, words, n_words * 4);
   check(cudaMemcpyAsync(tcp_words_dev_, tcp_pinned_ + 2, n_words * 4, cudaMemcpyHostToDevice, S(comm_)), "cudaMemcpyAsync");
   // the mirror steps back by exactly what tcp_encode stepped it forward: the frame counts as never made
-  check(launch_tensor_decode(tcp_words_dev_, -scale, n_, static_cast<float*>(links_[link].mirror.ptr), nullptr, tile_state_, comm_),
-        "tensor_decode kernel");
+  check(launch_tensor_decode(tcp_words_dev_, -scale, n_, mirror(link), nullptr, 0, comm_), "tensor_decode kernel");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
   check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
-  launches_ += 1;
+  launches_ += 2;
 }
 
 void GpuReplica::sync() {
@@ -514,10 +557,25 @@ void GpuReplica::sync() {
 std::vector<uint64_t> GpuReplica::status() {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> lk(mu_);
-  std::vector<uint64_t> out(kStTotalWords);
-  check(cudaMemcpyAsync(status_host_, status_, kStTotalWords * 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
+  std::vector<uint64_t> dev(kDsTotalWords);
+  check(cudaMemcpyAsync(status_host_, status_, kDsTotalWords * 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
   check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
-  std::memcpy(out.data(), status_host_, kStTotalWords * 8);
+  std::memcpy(dev.data(), status_host_, kDsTotalWords * 8);
+  const uint64_t* lw = dev.data() + (last_parity_ ? kDsLaunch1 : kDsLaunch0);
+  std::vector<uint64_t> out(kStTotalWords, 0);
+  out[kStRounds] = dev[kDsSweeps];
+  out[kStTilesProcessed] = dev[kDsTilesProcessed];
+  out[kStFramesSent] = dev[kDsFramesSent];
+  out[kStFramesRecv] = dev[kDsFramesRecv];
+  out[kStBlockedNoCredit] = dev[kDsBlockedNoCredit];
+  out[kStErrors] = dev[kDsErrors];
+  out[kStLastWorkCount] = lw[kDlWork];
+  out[kStResidualMax0] = lw[kDlResMax + 0];
+  out[kStResidualMax1] = lw[kDlResMax + 1];
+  out[kStResidualMax2] = lw[kDlResMax + 2];
+  out[kStPendingTiles] = lw[kDlPending];
+  out[kStWaitTimeouts] = dev[kDsWaitTimeouts];
+  std::memcpy(out.data() + kStWords, dev.data() + kDsTrace, size_t(kTraceEntries) * kTraceWords * 8);
   return out;
 }
 
@@ -587,6 +645,8 @@ void GpuReplica::engine_loop() {
   cudaSetDevice(device_);
   ::prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);  // 1 us instead of the default 50 us: the idle pauses start at 10 us
   const size_t depth = ev_round_.size();
+  // one pinned word per launch in flight: how many tiles that launch handled
+  uint64_t* work_host = status_host_ + kDsTotalWords;  // behind the part status() uses
   uint64_t r = 0;
   uint64_t idle_rounds = 0;
   while (!engine_stop_.load()) {
@@ -594,37 +654,11 @@ void GpuReplica::engine_loop() {
     try {
       std::lock_guard<std::mutex> lk(mu_);
       if (params_.n_in + params_.n_out > 0) {
-        params_.do_rx = 1;
-        params_.do_tx = 1;
-        bool by_graph = false;
-        if (cfg_.use_graph && graph_warm_ && (round_no_ & 1) == 0) {
-          // Two rounds (even and odd parity) replayed as one CUDA graph: one launch instead of six, which is what
-          // bounds the round rate of small tensors.  The graph is rebuilt whenever the ring set changes.
-          if (!graph_exec_) {
-            RoundParams two[2] = {params_, params_};
-            two[0].round = 0;
-            two[1].round = 1;
-            void* exec = nullptr;
-            if (build_round_graph(two, 2, ctas_, &exec) == 0) graph_exec_ = exec;
-            else cfg_.use_graph = false;  // no graphs here: plain launches from now on
-          }
-          if (graph_exec_) {
-            check(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec_), S(comm_)), "cudaGraphLaunch");
-            round_no_ += 2;
-            launches_ += 6;
-            by_graph = true;
-          }
-        }
-        if (!by_graph) {
-          params_.round = round_no_++;
-          check(launch_round_begin(params_, comm_), "round_begin kernel");
-          check(launch_round_main(params_, ctas_, comm_), "round_main kernel");
-          check(launch_round_publish(params_, comm_), "round_publish kernel");
-          launches_ += 3;
-          graph_warm_ = true;  // the kernels' attributes are set: later rounds may be replayed from a graph
-        }
-        // the work count of this round tells the thread whether anything is moving
-        cudaMemcpyAsync(status_host_ + kStLastWorkCount, status_ + kStLastWorkCount, 8, cudaMemcpyDeviceToHost, S(comm_));
+        // One launch makes several passes over a small tensor and returns; nothing on the device waits for this
+        // thread, which only starts the next launch and reads how much the last one found to do.
+        launch(true, true, auto_sweeps());
+        cudaMemcpyAsync(work_host + (r % depth), status_ + (last_parity_ ? kDsLaunch1 : kDsLaunch0) + kDlWork, 8, cudaMemcpyDeviceToHost,
+                        S(comm_));
         cudaEventRecord(E(ev_round_[r % depth]), S(comm_));
         launched = true;
       }
@@ -636,9 +670,13 @@ void GpuReplica::engine_loop() {
       continue;
     }
     r++;
-    if (r >= depth) cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
-    if (status_host_[kStLastWorkCount] != 0) epoch_++;
-    if (status_host_[kStLastWorkCount] == 0) {
+    uint64_t work = 1;
+    if (r >= depth) {
+      cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
+      work = work_host[(r - depth) % depth];
+    }
+    if (work != 0) epoch_++;
+    if (work == 0) {
       // nothing moved: back off from 10 us up to idle_sleep_us, so that a fresh update is picked up quickly after a
       // burst and an idle replica costs next to nothing
       idle_rounds++;

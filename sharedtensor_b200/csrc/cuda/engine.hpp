@@ -2,10 +2,16 @@
 // sync rounds.  This is the device-side counterpart of CpuNode (../core/node.hpp); it knows nothing
 // about sockets or membership, which live in gpu_node.hpp.
 //
-// Stream discipline: every kernel that writes `values` or a mirror runs on the replica's own comm
-// stream, so those kernels never race with each other; user-stream work is ordered against them with
-// events.  copyToTensor reads `values` from the caller's stream and may overlap a round (per-element
-// tearing is impossible, per-tensor tearing is allowed, as in the reference, src/sharedtensor.c:442-444).
+// Stream discipline: mirrors are written by the round kernel only, on the replica's own comm stream.
+// `values` has many writers (the round kernel adds what it received, addFromTensor adds from the caller's
+// stream, TCP frames are added by their receiver threads) and every one of them adds with a reduction at
+// the L2, so they commute and none waits for another: an update never queues behind a round in flight.
+// (The reference adds from the user thread while its sender and receiver threads run, without any
+// synchronisation, src/sharedtensor.c:334-344.)  Whoever changes the values marks the tiles as changed
+// AFTER the change, on the same stream; the round kernel clears a tile's mark BEFORE it reads the tile,
+// so a change it does not see is looked at in the next sweep.  copyToTensor reads `values` from the
+// caller's stream and may overlap a round (per-element tearing is impossible, per-tensor tearing is
+// allowed, as in the reference, src/sharedtensor.c:442-444).
 #pragma once
 #include <atomic>
 #include <chrono>
@@ -32,9 +38,12 @@ struct GpuConfig {
   int rounds_in_flight = 2;
   int idle_sleep_us = 1000;  // longest pause of the engine thread between rounds while nothing moves
   int round_interval_us = 0; // pause after every busy round (0 = run rounds back to back)
-  int frames_per_round = 1;  // successive 1-bit frames per link and round (1..3)
-  bool use_graph = true;     // the engine thread replays pairs of rounds as a CUDA graph
+  int bits = 8;              // bits per element of a frame: 1 (sign frames), 2, 4 or 8 (integer frames)
+  int sweeps = 0;            // passes over the tensor per launch of the engine thread (0 = chosen from the tensor's size)
+  int poll_deadline_us = 1000;  // upper bound of every wait inside the round kernel
 };
+
+constexpr size_t kGuardBytes = 256;  // canary before and after every mirror, edge block and the values
 
 struct EdgeBlockLayout {
   size_t off_payload = 0, off_flags = 0, off_credit = 0, bytes = 0;
@@ -50,9 +59,9 @@ class GpuReplica {
   int64_t size() const { return n_; }
   int64_t padded() const { return n_padded_; }
   int tiles() const { return n_tiles_; }
-  float* values() const { return static_cast<float*>(values_.ptr); }
+  float* values() const { return reinterpret_cast<float*>(static_cast<uint8_t*>(values_.ptr) + kGuardBytes); }
   const VmmBlock& values_block() const { return values_; }
-  float* mirror(int link) const { return static_cast<float*>(links_[link].mirror.ptr); }
+  float* mirror(int link) const { return reinterpret_cast<float*>(static_cast<uint8_t*>(links_[link].mirror.ptr) + kGuardBytes); }
   EdgeBlockLayout edge_layout() const { return layout_; }
   void* comm_stream() const { return comm_; }
 
@@ -71,8 +80,7 @@ class GpuReplica {
 
   // ---- data path ----
   void load_values(const float* src, void* user_stream);
-  // Updates run on the comm stream (a round must never see a half-applied update), after the work already queued
-  // on `user_stream`; the user stream then waits for the update, so a snapshot that follows sees it.
+  // Updates run on the caller's stream, concurrently with rounds (every add is a reduction at the L2).
   void add(const float* delta, void* user_stream);
   void sub_add(const float* neu, const float* old, void* user_stream);
   void add_scaled_bf16(const void* g_bf16, float alpha, void* user_stream);  // values += alpha * g
@@ -80,14 +88,19 @@ class GpuReplica {
   // load_values, tcp_decode) waits.  A node that re-joins holds it from the moment it works out what its lost parent
   // had not been told until that has been added back on top of the new parent's snapshot, so that an update made in
   // between is neither overwritten by the snapshot nor counted twice.
-  void gate_lock() { gate_mu_.lock(); }
+  void gate_lock();   // also waits until the updates issued so far have run on the device
   void gate_unlock() { gate_mu_.unlock(); }
   void add_gate_held(const float* delta);   // values += delta on the comm stream; the caller holds the gate
   void snapshot(float* out, void* user_stream);
   void snapshot_bf16(void* out, void* user_stream);
   void copy_mirror_from_values(int link);                 // mirror <- values (neighbour is given a snapshot)
   void push_snapshot(int link, float* remote_values);     // neighbour's values <- values, mirror <- values
-  void round(bool do_rx = true, bool do_tx = true);
+  void round(bool do_rx = true, bool do_tx = true, int sweeps = 1);
+  // Test hook: while set (>= 0), the round kernel's copy barrier of this tile expects more bytes than are copied,
+  // so the bounded wait of the group that owns the tile runs out.
+  void set_test_stall_tile(int tile);
+  // Compares the canaries around the values, every mirror and every edge block; returns the number of damaged ones.
+  int check_guards();
   // TCP links: a link with a mirror and no ring peers; its tensor-scale frames (the reference's wire format) are
   // made and applied on the device, host threads only move bytes.  `words` is host memory of ceil(n/32) words.
   float tcp_encode(int link, uint32_t* words, float min_scale_abs, float min_scale_rel);  // returns the frame's scale
@@ -110,6 +123,7 @@ class GpuReplica {
 
   // ---- observation ----
   std::vector<uint64_t> status();      // StatusWord order, then the trace ring; synchronises the comm stream
+  int bits() const { return cfg_.bits; }
   uint64_t launches() const { return launches_.load(); }
   uint64_t change_epoch() const { return epoch_.load(); }  // bumped whenever values may have changed
   std::string last_error() const;
@@ -133,6 +147,9 @@ class GpuReplica {
   };
   void rebuild_params();               // under mu_
   void publish_pending();              // under mu_
+  void launch(bool do_rx, bool do_tx, int sweeps);  // under mu_
+  int auto_sweeps() const;
+  void fill_guards(const VmmBlock& b, size_t used_bytes);
   void check(int cuda_err, const char* what);
   void engine_loop();
   void order_after_user(void* user_stream);
@@ -147,13 +164,8 @@ class GpuReplica {
   std::vector<Link> links_;
   std::vector<Block> blocks_;
   std::vector<Peer> peers_;
-  // scratch
-  uint8_t* ctrl_ = nullptr;
-  uint8_t* sent_ = nullptr;
-  uint8_t* tile_state_ = nullptr;
-  int32_t* worklist_ = nullptr;
-  int32_t* work_count_ = nullptr;
-  uint64_t* status_ = nullptr;
+  uint32_t* tile_state_ = nullptr;     // change mark per tile
+  uint64_t* status_ = nullptr;         // DevStatus layout
   uint64_t* status_host_ = nullptr;    // pinned
   uint32_t* tcp_words_dev_ = nullptr;  // ceil(n/32) words, staging of TCP frames
   uint32_t* tcp_stat_dev_ = nullptr;   // 2 words
@@ -161,8 +173,7 @@ class GpuReplica {
   RoundParams params_{};
   int map_link_[kMaxLinks] = {0, 0, 0};  // dense link index of each link id
   int round_no_ = 0;
-  void* graph_exec_ = nullptr;         // cudaGraphExec_t: two rounds (even, odd parity) of the current ring set
-  bool graph_warm_ = false;            // one plain round has run since the ring set last changed
+  int last_parity_ = 0;                // which half of the per-launch status words the last launch used
   int ctas_ = 148;
   void* comm_ = nullptr;               // cudaStream_t
   void* ev_user_ = nullptr;            // cudaEvent_t: user stream -> comm

@@ -40,7 +40,7 @@ namespace st {
 namespace {
 
 constexpr uint32_t kHelloMagic = 0x32425453;  // "STB2"
-constexpr uint32_t kHelloVersion = 1;
+constexpr uint32_t kHelloVersion = 2;
 
 struct Hello {
   uint32_t magic = kHelloMagic;
@@ -48,6 +48,8 @@ struct Hello {
   int64_t n = 0;
   int32_t block = 0;
   int32_t ring_slots = 0;
+  int32_t bits = 0;            // bits per element of a frame
+  int32_t reserved = 0;
   uint64_t edge_bytes = 0;     // mapped size of the sender's edge block
   uint64_t values_bytes = 0;   // mapped size of the sender's values block
   sockaddr_in listen_addr{};   // the sender's TCP listen address (identifies the child to its parent)
@@ -356,6 +358,7 @@ class GpuNode {
     h.n = n_;
     h.block = gcfg_.block;
     h.ring_slots = gcfg_.ring_slots;
+    h.bits = gcfg_.bits;
     h.edge_bytes = 0;
     h.values_bytes = rep_->values_block().bytes;
     h.listen_addr = seen_as;
@@ -446,6 +449,7 @@ class GpuNode {
           if (carry) {
             cudaSetDevice(device_);
             cudaMemcpy(rep_->values(), carry, size_t(n_) * 4, cudaMemcpyDeviceToDevice);
+            cudaDeviceSynchronize();
             cudaFree(carry);
           }
           drop_orphan_link();
@@ -604,7 +608,7 @@ class GpuNode {
     }
     cudaStream_t cs = static_cast<cudaStream_t>(rep_->comm_stream());
     cudaMemsetAsync(carry, 0, size_t(n_) * 4, cs);
-    launch_sub_add(carry, rep_->values(), rep_->mirror(orphan_link_), n_, nullptr, 0, 0, rep_->comm_stream());
+    launch_sub_add(carry, rep_->values(), rep_->mirror(orphan_link_), n_, 0, rep_->comm_stream());
     rep_->sync();
     return carry;
   }
@@ -648,7 +652,8 @@ class GpuNode {
     if (!unix_recv_fd(us, nullptr, &h, sizeof(h), opt_.upgrade_timeout_ms) || h.magic != kHelloMagic) return;
     if (h.version != kHelloVersion) return refuse(us, "protocol version mismatch");
     if (h.n != n_) return refuse(us, "Not the right size!");
-    if (h.block != gcfg_.block || h.ring_slots != gcfg_.ring_slots) return refuse(us, "scale block / ring geometry mismatch");
+    if (h.block != gcfg_.block || h.ring_slots != gcfg_.ring_slots || h.bits != gcfg_.bits)
+      return refuse(us, "scale block / frame bits / ring geometry mismatch");
     // find the TCP adoption this child belongs to (the two connections race)
     int slot = -1;
     {
@@ -700,7 +705,7 @@ class GpuNode {
       ::close(my_fd);
       if (!sent) break;
       // state transfer: one pass over the replica, in stream order with the rounds
-      rep_->push_snapshot(link, static_cast<float*>(child_values.ptr));
+      rep_->push_snapshot(link, reinterpret_cast<float*>(static_cast<uint8_t*>(child_values.ptr) + kGuardBytes));
       int pid = rep_->attach_peer(link, block, remote.ptr);
       {
         std::lock_guard<std::mutex> g(mu_);
@@ -905,6 +910,7 @@ struct MeshHello {
   int32_t rank = 0, world = 0;
   int64_t n = 0;
   int32_t block = 0, ring_slots = 0;
+  int32_t bits = 0, reserved = 0;
   uint64_t edge_bytes = 0, values_bytes = 0;
 };
 
@@ -945,7 +951,7 @@ class GpuMeshNode {
     // common initial state, then the go signal
     if (rank_ == 0) {
       for (int j = 1; j < world_; j++) {
-        rep_->push_snapshot(link_, static_cast<float*>(peers_[size_t(j)].values.ptr));
+        rep_->push_snapshot(link_, reinterpret_cast<float*>(static_cast<uint8_t*>(peers_[size_t(j)].values.ptr) + kGuardBytes));
         vmm_free(&peers_[size_t(j)].values);
       }
       if (world_ == 1) rep_->copy_mirror_from_values(link_);
@@ -1000,12 +1006,13 @@ class GpuMeshNode {
     h.n = n_;
     h.block = gcfg_.block;
     h.ring_slots = gcfg_.ring_slots;
+    h.bits = gcfg_.bits;
     h.edge_bytes = rep_->edge_block(block).bytes;
     h.values_bytes = rep_->values_block().bytes;
     MeshHello o;
     if (!unix_send_fd(fd, -1, &h, sizeof(h)) || !unix_recv_fd(fd, nullptr, &o, sizeof(o), 10000) || o.magic != h.magic)
       throw std::runtime_error("mesh: hello failed");
-    if (o.n != n_ || o.block != h.block || o.ring_slots != h.ring_slots || o.world != world_ || o.rank == rank_ ||
+    if (o.n != n_ || o.block != h.block || o.ring_slots != h.ring_slots || o.bits != h.bits || o.world != world_ || o.rank == rank_ ||
         (expect_rank >= 0 && o.rank != expect_rank))
       throw std::runtime_error("mesh: members disagree on size, block, ring geometry or group");
     int my_fd = vmm_export_fd(rep_->edge_block(block), &err);

@@ -1,25 +1,31 @@
-// Sync-round kernels for sm_100a: round_begin, round_main and round_publish (see round.h for the protocol).
+// The sync-round kernel for sm_100a (see round.h for the protocol and ../core/codec.hpp for the arithmetic).
 //
-// round_main is the fused hot path.  A CTA is three independent groups of 128 threads; a group works
-// through its share of the listed tiles, one 16 KB array-tile (values, then each link's mirror) at a time:
-//   1. array-tiles are staged into shared memory with 1-D TMA bulk copies (cp.async.bulk, completion on an
-//      mbarrier, a three-slot ring per group so the next copy is in flight while this one is computed;
-//      every source is this GPU's own memory);
-//   2. a thread owns 32 consecutive elements (read with an XOR swizzle, so no bank conflicts) and keeps its
-//      values in registers for the whole tile; in a link's step it decodes the frames that arrived on that
-//      link (sign bit + per-block power-of-two scale) once and adds them to the values and to the link's
-//      mirror                                             (reference src/sharedtensor.c:106-111, 124-127);
-//   3. per link it forms the residual values - mirror, the block's sum of squares, the exponent code from
-//      the float's exponent bits, its 32 sign bits as one word, and steps the mirror by -/+ 2^k
-//                                                         (reference 156-174);
-//   4. changed mirror tiles and the tile's values go back to global memory with TMA bulk stores, and the packed words + scale bytes go straight into the neighbours' ring slots with
-//      TMA bulk stores over NVLink
-//      (reference 176-177: two socket writes).
-// Nothing in here waits for another GPU.  The only waits are on this CTA's own TMA copies, and they are
-// bounded: on a timeout the group records an error in the status block and leaves.
+// A CTA holds three independent groups; a group is four compute warps and one I/O warp and owns every
+// (3 * gridDim.x)-th tile of the tensor.  The two kinds of warp talk through shared memory and mbarriers only:
+//
+//   I/O warp      reads its tiles' sequence flags, credits and change marks (32 tiles at a time, one per lane),
+//                 and for every tile with something to do hands the compute warps one *step* per link: it writes
+//                 the step's descriptor (tile, link, which frames arrived, which rings have room), and stages the
+//                 tile's values and the link's mirror into a slot with 1-D TMA bulk copies (cp.async.bulk,
+//                 completion on the slot's `full` mbarrier; every source is this GPU's own memory).  When the
+//                 compute warps have finished a step (`done` mbarrier) it issues the step's bulk stores straight
+//                 from the slot: the decoded frames as a bulk reduce-add into the values (so an update another
+//                 stream adds at the same moment is never overwritten), the stepped mirror, and the packed codes
+//                 and scale bytes into the ring slot of every neighbour on the link (peer stores over NVLink;
+//                 reference src/sharedtensor.c:176-177, two socket writes).  Two steps later, when those stores
+//                 have completed, it fences and publishes: sequence flags to the receivers, credits to the senders.
+//   compute warps a thread owns 32 consecutive elements of the tile (read from shared memory through an XOR
+//                 swizzle, so no bank conflicts).  It decodes the frames that arrived (reference 106-111, 124-127)
+//                 into one accumulated step, adds it to its values and to the mirror of the link the frames came
+//                 from, then forms values - mirror, the block's largest magnitude, the exponent code, the codes
+//                 of its 32 elements, and steps the mirror by what the codes say (reference 156-174).
+//
+// Nothing in here waits for another GPU.  The waits are on this CTA's own copies and on its own warps, and every
+// one is bounded: when a wait runs out the group records an error in the status block, stores nothing of the step
+// it was on, marks its tiles for another visit and leaves.
 //
 // Arithmetic is written with explicit round-to-nearest operations; block statistics are maxima (order does not
-// matter), so words, scales and mirrors are bit-identical to the host codec (../core/codec.cpp).
+// matter), so codes, scales, mirrors and values are bit-identical to the host codec (../core/codec.cpp).
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -30,10 +36,12 @@ namespace st {
 
 namespace {
 
-
-constexpr int kGroupThreads = 128;  // one thread per 32 consecutive elements of a tile
-__host__ __device__ constexpr int slots_for(int) { return 3; }  // array-tile slots per group
+constexpr int kGroupThreads = 128;  // compute threads of a group: one per 32 consecutive elements of a tile
+constexpr int kGroups = 3;
+constexpr int kSlots = 2;           // staging slots per group
 constexpr int kTileBytes = kTile * 4;
+constexpr int kCtaThreads = kGroups * (kGroupThreads + 32);
+constexpr int kPubQueue = 4;
 
 // ----------------------------------------------------------------------------------------------
 // small PTX wrappers
@@ -46,6 +54,34 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// this GPU's own bookkeeping words, written and read by different lanes and launches: always at the L2
+__device__ __forceinline__ uint32_t ld_cg_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_cg_u32(uint32_t* p, uint32_t v) { asm volatile("st.global.cg.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+// frame words and scale bytes were written by a neighbour GPU: read them from the L2, never from this SM's L1
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_cg_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_cg_word(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_cg_u8(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -53,6 +89,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -73,29 +112,124 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// shared -> global bulk store / reduce (this CTA's memory as source), tracked by bulk async-groups
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_reduce_add_f32(float* dst_gmem, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all_but_2() { asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ uint32_t ld_shared_volatile(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
+__device__ __forceinline__ void st_shared_volatile(uint32_t* p, uint32_t v) { *reinterpret_cast<volatile uint32_t*>(p) = v; }
 
-// Bounded wait on one of this CTA's own copy barriers.  20 ms is three orders of magnitude above the
-// time a stage takes; running into it means the copy was mis-issued, and the caller bails out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// Bounded wait on one of this CTA's own barriers; false when `limit_ns` has passed.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
-  for (uint32_t it = 0; it < (1u << 24); it++) {
+  for (uint32_t it = 0; it < (1u << 26); it++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63) == 63 && globaltimer_ns() - t0 > 20ull * 1000 * 1000) return false;
+    if ((it & 15) == 15 && globaltimer_ns() - t0 > limit_ns) return false;
   }
   return false;
 }
 
+// A compute warp's wait for a step.  The clock of the limit only runs once the I/O warp has armed the step (while the
+// I/O warp looks for work, or there is none, a compute warp may sit here for the whole launch); a second, generous
+// limit covers an I/O warp that never comes back.
+__device__ __forceinline__ bool wait_step(uint64_t* bar, uint32_t parity, const uint32_t* armed, uint32_t step, const uint32_t* abort,
+                                          uint64_t limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t_start = globaltimer_ns();
+  uint64_t t_armed = 0;
+  for (uint32_t it = 0; it < (1u << 28); it++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 7) == 7) {
+      if (ld_shared_volatile(abort)) return false;
+      const uint64_t now = globaltimer_ns();
+      if (ld_shared_volatile(armed) > step) {
+        if (t_armed == 0) t_armed = now;
+        else if (now - t_armed > limit_ns) return false;
+      } else if (now - t_start > 2000ull * 1000 * 1000) {
+        return false;
+      }
+    }
+  }
+  return false;
+}
+
+// ----------------------------------------------------------------------------------------------
+// what the I/O warp tells the compute warps about a step (one per slot, in shared memory)
+// ----------------------------------------------------------------------------------------------
+struct __align__(16) StepDesc {
+  int32_t tile;
+  int32_t link;
+  uint32_t flags;
+  uint32_t sent;                 // publication queue only: the step's frame went out
+  uint32_t in_lo, in_hi;         // per in-ring r one byte: frames available << 6 | first slot
+  uint32_t out_lo, out_hi;       // per out-ring r one byte: has room << 6 | next slot
+};
+constexpr uint32_t kDescFirst = 1;   // the tile's first step: the slot also holds the values
+constexpr uint32_t kDescExit = 2;    // nothing more to do in this launch
+constexpr uint32_t kDescRxAny = 4;   // at least one frame arrived for the tile
+constexpr uint32_t kDescTxOk = 8;    // every out-ring of the link has room
+constexpr uint32_t kDescRxLink = 16; // at least one frame arrived on this step's link
+constexpr uint32_t kDescLast = 32;   // the tile's last step
+constexpr uint32_t kFlagChanged = 1, kFlagNonsilent = 2, kFlagFailed = 4;  // what the compute warps report about a step
+
+__device__ __forceinline__ uint32_t ctrl_byte(uint32_t lo, uint32_t hi, int r) { return ((r < 4 ? lo : hi) >> ((r & 3) * 8)) & 0xffu; }
+
+struct SmemLayout {
+  int slot_stride;  // values tile, mirror tile, payload
+  int off_slots;    // [kGroups][kSlots][slot_stride]
+  int off_desc;     // StepDesc[kGroups][kSlots]
+  int off_pubq;     // StepDesc[kGroups][kPubQueue]
+  int off_bar;      // uint64_t[kGroups][2 * kSlots + 1]: full, done, group sync
+  int off_words;    // uint32_t[kGroups][8]: step flags per slot, armed steps, abort
+  int off_red;      // float[kGroups][2][8]: cross-warp partials for blocks of 2048 / 4096 elements
+  int total;
+};
+__host__ __device__ inline SmemLayout smem_layout(int payload_bytes) {
+  SmemLayout m;
+  m.slot_stride = 2 * kTileBytes + ((payload_bytes + 127) & ~127);
+  int off = 0;
+  m.off_slots = off;
+  off += kGroups * kSlots * m.slot_stride;
+  m.off_desc = off;
+  off += kGroups * kSlots * int(sizeof(StepDesc));
+  m.off_pubq = off;
+  off += kGroups * kPubQueue * int(sizeof(StepDesc));
+  m.off_bar = off;
+  off += kGroups * (2 * kSlots + 1) * 8;
+  m.off_words = off;
+  off += kGroups * 8 * 4;
+  m.off_red = off;
+  off += kGroups * 2 * 8 * 4;
+  m.total = (off + 127) & ~127;
+  return m;
+}
+
+// ----------------------------------------------------------------------------------------------
+// per-thread arithmetic on 32 consecutive elements held as eight float4 pieces.  Register q holds the elements
+// 4*(q^sw) .. +3 of the thread's 32 (sw = thread & 7, the shared-memory swizzle); a frame stores a thread's codes in
+// the order of its registers, so the sender's and the receiver's thread of the same index agree without shuffling.
+// ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ int floor_log2_dev(float x) { return int((__float_as_uint(x) >> 23) & 0xff) - 127; }
 
-// exponent code of a block from its largest |residual| and the bits of its largest |value| (see block_code in
-// ../core/codec.cpp: step = 2^floor(log2(2/3 max|x|)), silent below 2^(emax - rel_bits))
-__device__ __forceinline__ int block_code_dev(float xmax, uint32_t vmax_bits, int min_exp, int rel_bits) {
+// sign frames: step = 2^floor(log2(2/3 max|x|)), silent below the cut-off (block_code in ../core/codec.cpp)
+__device__ __forceinline__ int block_code_sign(float xmax, uint32_t vmax_bits, int min_exp, int rel_bits) {
   const float scaled = __fmul_rn(xmax, 0.6666667f);
   if ((__float_as_uint(scaled) >> 23) == 0) return 0;
   int kx = floor_log2_dev(scaled);
@@ -109,157 +243,143 @@ __device__ __forceinline__ int block_code_dev(float xmax, uint32_t vmax_bits, in
   return kx + 127;
 }
 
-}  // namespace
+// integer frames: the smallest step for which the largest residual still fits (block_code_int in ../core/codec.cpp)
+template <int Q>
+__device__ __forceinline__ int block_code_int_dev(float xmax, uint32_t vmax_bits, int min_exp, int rel_bits) {
+  const uint32_t xb = __float_as_uint(xmax) & 0x7fffffffu;
+  const int ef = int(xb >> 23);
+  if (ef == 0 || ef == 255) return 0;
+  const int ex = ef - 127;
+  if (ex > 100) return 0;
+  const uint32_t mant = xb & 0x7fffffu;
+  int es = ex - (Q - 2);
+  if (mant >= (1u << 23) - (1u << (24 - Q))) es += 1;
+  es = max(es, min_exp);
+  if ((vmax_bits >> 23) != 0) es = max(es, int((vmax_bits >> 23) & 0xffu) - 127 - rel_bits);
+  es = max(es, -126);
+  if (ex < es - 1 || (ex == es - 1 && mant == 0)) return 0;
+  return es + 127;
+}
 
-// ----------------------------------------------------------------------------------------------
-// round_publish / round_begin: one thread per tile
-// ----------------------------------------------------------------------------------------------
-// After round_main: tell the neighbours what happened.  Credits for the frames this replica consumed
-// go to their senders, sequence flags for the frames it wrote go to their receivers.  round_main has
-// completed (stream order), so its peer stores are performed; one system-scope fence per publishing
-// thread orders them before the flag stores that follow it.
-__global__ void __launch_bounds__(256) round_publish_kernel(const __grid_constant__ RoundParams p) {
-  const int tile = blockIdx.x * blockDim.x + threadIdx.x;
-  if (tile >= p.n_tiles) return;
-  uint8_t* cptr = p.ctrl + size_t(tile) * 16;
-  const uint4 prev = *reinterpret_cast<const uint4*>(cptr);
-  const uint8_t* pc = reinterpret_cast<const uint8_t*>(&prev);
-  const uint2 sentw = *reinterpret_cast<const uint2*>(p.sent + size_t(tile) * 8);
-  const uint8_t* ps = reinterpret_cast<const uint8_t*>(&sentw);
-  if ((prev.x | prev.y) == 0u && (sentw.x | sentw.y) == 0u) return;  // nothing consumed, nothing sent
-  __threadfence_system();
-  for (int r = 0; r < p.n_in; r++) {
-    int avail = pc[r] >> 6;
-    if (avail) {
-      uint32_t seq = p.in[r].rx_seq[tile] + uint32_t(avail);
-      p.in[r].rx_seq[tile] = seq;
-      st_relaxed_sys(p.in[r].credit_remote + tile, seq);
-    }
+template <int Q>
+__device__ __forceinline__ int block_code_dev(float xmax, uint32_t vmax_bits, int min_exp, int rel_bits) {
+  if constexpr (Q == 1) return block_code_sign(xmax, vmax_bits, min_exp, rel_bits);
+  else return block_code_int_dev<Q>(xmax, vmax_bits, min_exp, rel_bits);
+}
+
+// the Q code words of thread t and the scale byte of its block, from a frame in a ring slot
+template <int Q>
+__device__ __forceinline__ void load_frame(const uint8_t* fp, int t, int tpb, uint32_t (&w)[Q], uint32_t& code) {
+  const uint8_t* mine = fp + size_t(t) * (4 * Q);
+  if (Q == 8) {
+    const uint4 a = ld_cg_v4(mine), b = ld_cg_v4(mine + 16);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4 % Q] = b.x; w[5 % Q] = b.y; w[6 % Q] = b.z; w[7 % Q] = b.w;
+  } else if (Q == 4) {
+    const uint4 a = ld_cg_v4(mine);
+    w[0] = a.x; w[1 % Q] = a.y; w[2 % Q] = a.z; w[3 % Q] = a.w;
+  } else if (Q == 2) {
+    const uint2 a = ld_cg_v2(mine);
+    w[0] = a.x; w[1 % Q] = a.y;
+  } else {
+    w[0] = ld_cg_word(mine);
   }
-  for (int r = 0; r < p.n_out; r++) {
-    const int frames = ps[r];  // frames written for this ring, in consecutive slots
-    if (frames) {
-      uint32_t seq = p.out[r].tx_seq[tile];
-      const int slot0 = pc[8 + r] & 63;
-      for (int f = 0; f < frames; f++) {
-        seq++;
-        st_relaxed_sys(p.out[r].flags_remote + size_t((slot0 + f) % p.ring_slots) * p.n_tiles + tile, seq);
-      }
-      p.out[r].tx_seq[tile] = seq;
-    }
-  }
-  *reinterpret_cast<uint4*>(cptr) = make_uint4(0u, 0u, 0u, 0u);
-  *reinterpret_cast<uint2*>(p.sent + size_t(tile) * 8) = make_uint2(0u, 0u);
+  code = ld_cg_u8(fp + 4 * Q * kWordsPerTile + (t >> tpb));
 }
 
-// Before round_main: look at every tile's rings once (frames that arrived, ring space) and list the
-// tiles that have something to do.
-__global__ void __launch_bounds__(256) round_begin_kernel(const __grid_constant__ RoundParams p) {
-  const int tile = blockIdx.x * blockDim.x + threadIdx.x;
-  const int par = p.round & 1;
-  if (tile == 0) {
-    p.work_count[par ^ 1] = 0;  // the next round appends to the other counter
-    p.status[kStPendingTiles] = 0;
-    p.status[kStResidualMax0] = 0;
-    p.status[kStResidualMax1] = 0;
-    p.status[kStResidualMax2] = 0;
-  }
-  if (tile >= p.n_tiles) return;
-  uint4 cur = make_uint4(0u, 0u, 0u, 0u);
-  uint8_t* cc = reinterpret_cast<uint8_t*>(&cur);
-  bool work = p.tile_state[tile] != 0;
-  const uint32_t S = uint32_t(p.ring_slots);
-  if (p.do_rx) {
-    for (int r = 0; r < p.n_in; r++) {
-      uint32_t e = p.in[r].rx_seq[tile];
-      int avail = 0;
-      while (avail < kRxMax) {
-        uint32_t slot = (e + uint32_t(avail)) % S;
-        uint32_t f = ld_acquire_sys(p.in[r].flags + size_t(slot) * p.n_tiles + tile);
-        if (f != e + uint32_t(avail) + 1u) break;
-        avail++;
-      }
-      cc[r] = uint8_t((avail << 6) | int(e % S));
-      if (avail) work = true;
-    }
-  }
-  if (p.do_tx) {
-    for (int r = 0; r < p.n_out; r++) {
-      uint32_t t = p.out[r].tx_seq[tile];
-      uint32_t c = ld_acquire_sys(p.out[r].credit + tile);
-      uint32_t used = t - c;
-      uint32_t room = used < S ? S - used : 0u;  // free slots, reported up to 3
-      cc[8 + r] = uint8_t((min(room, 3u) << 6) | (t % S));
-    }
-  }
-  *reinterpret_cast<uint4*>(p.ctrl + size_t(tile) * 16) = cur;
-  if (work) {
-    int idx = atomicAdd(p.work_count + par, 1);
-    p.worklist[idx] = tile;
-  }
-}
-
-// ----------------------------------------------------------------------------------------------
-// round_main
-// ----------------------------------------------------------------------------------------------
-namespace {
-
-// shared -> global bulk store / reduce (this CTA's memory as source), tracked by bulk async-groups
-__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// barrier over one 128-thread group (hardware barrier 1 + group)
-__device__ __forceinline__ void group_bar(int group) {
-  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kGroupThreads) : "memory");
-}
-constexpr uint32_t kFlagChanged = 1, kFlagFailed = 2, kFlagNonsilent0 = 4;  // nonsilent: one bit per pass, 4 << f
-constexpr int kMaxFrames = 3;       // 1-bit frames per link, tile and round
-
-// frame words and scale bytes were written by a neighbour GPU: read them from L2, never from this SM's L1
-__device__ __forceinline__ uint32_t ld_u32_ca(const void* p) {
-  uint32_t v;
-  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint32_t ld_u8_ca(const void* p) {
-  uint32_t v;
-  asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-
-// f = +/- 2^(code-127) for element `bit` of word w, as raw bits: the sign bit is the frame's bit
-__device__ __forceinline__ float signed_scale(uint32_t scale_bits, uint32_t w, int bit) {
-  return __uint_as_float(scale_bits | ((w << (31 - bit)) & 0x80000000u));
-}
-
-// ---- per-thread arithmetic on 32 consecutive elements held as eight float4 pieces; piece q holds elements
-// 4*(q^sw) .. +3.  VMASK: bit i set = element i of the 32 exists (all ones except in a tensor's last chunk).
-
-// a += frame and b += frame with one decode (values and the mirror of the link the frame came from)
-template <bool FULL>
-__device__ __forceinline__ void apply_frame2(float4 (&a)[8], float4 (&b)[8], uint32_t w, uint32_t sb, int sw, uint32_t vmask) {
+// acc += the step the frame gives each of the 32 elements
+template <int Q, bool MASKED>
+__device__ __forceinline__ void add_frame(float4 (&acc)[8], const uint32_t (&w)[Q], uint32_t code, int sw, uint32_t vmask) {
+  if (code == 0u || code == 255u) return;
+  const float s = __uint_as_float(code << 23);
+  if (Q == 1) {
+    const uint32_t sb = code << 23;
 #pragma unroll
-  for (int q = 0; q < 8; q++) {
-    const int sh = 4 * (q ^ sw);
-    const uint32_t wq = w >> sh;
-    const float f0 = signed_scale(sb, wq, 0), f1 = signed_scale(sb, wq, 1), f2 = signed_scale(sb, wq, 2), f3 = signed_scale(sb, wq, 3);
-    if (FULL) {
-      a[q].x = __fadd_rn(a[q].x, f0); b[q].x = __fadd_rn(b[q].x, f0);
-      a[q].y = __fadd_rn(a[q].y, f1); b[q].y = __fadd_rn(b[q].y, f1);
-      a[q].z = __fadd_rn(a[q].z, f2); b[q].z = __fadd_rn(b[q].z, f2);
-      a[q].w = __fadd_rn(a[q].w, f3); b[q].w = __fadd_rn(b[q].w, f3);
-    } else {
-      const uint32_t vq = vmask >> sh;
-      if (vq & 1u) { a[q].x = __fadd_rn(a[q].x, f0); b[q].x = __fadd_rn(b[q].x, f0); }
-      if (vq & 2u) { a[q].y = __fadd_rn(a[q].y, f1); b[q].y = __fadd_rn(b[q].y, f1); }
-      if (vq & 4u) { a[q].z = __fadd_rn(a[q].z, f2); b[q].z = __fadd_rn(b[q].z, f2); }
-      if (vq & 8u) { a[q].w = __fadd_rn(a[q].w, f3); b[q].w = __fadd_rn(b[q].w, f3); }
+    for (int q = 0; q < 8; q++) {
+      const uint32_t wq = w[0] >> (4 * q);
+      const float f0 = __uint_as_float(sb | ((wq << 31) & 0x80000000u)), f1 = __uint_as_float(sb | ((wq << 30) & 0x80000000u));
+      const float f2 = __uint_as_float(sb | ((wq << 29) & 0x80000000u)), f3 = __uint_as_float(sb | ((wq << 28) & 0x80000000u));
+      if (!MASKED) {
+        acc[q].x = __fadd_rn(acc[q].x, f0); acc[q].y = __fadd_rn(acc[q].y, f1);
+        acc[q].z = __fadd_rn(acc[q].z, f2); acc[q].w = __fadd_rn(acc[q].w, f3);
+      } else {
+        const uint32_t vq = vmask >> (4 * (q ^ sw));
+        if (vq & 1u) acc[q].x = __fadd_rn(acc[q].x, f0);
+        if (vq & 2u) acc[q].y = __fadd_rn(acc[q].y, f1);
+        if (vq & 4u) acc[q].z = __fadd_rn(acc[q].z, f2);
+        if (vq & 8u) acc[q].w = __fadd_rn(acc[q].w, f3);
+      }
+    }
+  } else {
+    // a code c stands for (c - 2^(Q-1)) steps; 2^23 + c as a float is 0x4B000000 | c
+    const float big = 8388608.f + float(1 << (Q - 1));
+    const float neg_ms = -__fmul_rn(big, s);
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      uint32_t z0, z1, z2, z3;
+      if (Q == 8) {
+        const uint32_t wq = w[q % Q];
+        z0 = __byte_perm(wq, 0x4B000000u, 0x7650); z1 = __byte_perm(wq, 0x4B000000u, 0x7651);
+        z2 = __byte_perm(wq, 0x4B000000u, 0x7652); z3 = __byte_perm(wq, 0x4B000000u, 0x7653);
+      } else {
+        constexpr uint32_t m = (1u << Q) - 1u;
+        const uint32_t wq = w[(q * Q / 8) % Q] >> ((q * 4 * Q) & 31);  // 4*Q bits per register
+        z0 = (wq & m) | 0x4B000000u; z1 = ((wq >> Q) & m) | 0x4B000000u;
+        z2 = ((wq >> (2 * Q)) & m) | 0x4B000000u; z3 = ((wq >> (3 * Q)) & m) | 0x4B000000u;
+      }
+      acc[q].x = __fadd_rn(acc[q].x, __fmaf_rn(__uint_as_float(z0), s, neg_ms));
+      acc[q].y = __fadd_rn(acc[q].y, __fmaf_rn(__uint_as_float(z1), s, neg_ms));
+      acc[q].z = __fadd_rn(acc[q].z, __fmaf_rn(__uint_as_float(z2), s, neg_ms));
+      acc[q].w = __fadd_rn(acc[q].w, __fmaf_rn(__uint_as_float(z3), s, neg_ms));
+    }
+  }
+}
+
+// the codes of v - k for a block with exponent code `code` (non-zero), and the mirror's step
+template <int Q, bool MASKED>
+__device__ __forceinline__ void quantise(const float4 (&v)[8], float4 (&k)[8], uint32_t code, uint32_t (&w)[Q], int sw, uint32_t vmask) {
+  if (Q == 1) {
+    const float sp = __uint_as_float(code << 23), sn = __uint_as_float((code << 23) | 0x80000000u);
+    uint32_t word = 0;
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
+      const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
+      uint32_t nib = (n0 ? 1u : 0u) | (n1 ? 2u : 0u) | (n2 ? 4u : 0u) | (n3 ? 8u : 0u);
+      if (!MASKED) {
+        k[q].x = __fadd_rn(k[q].x, n0 ? sn : sp); k[q].y = __fadd_rn(k[q].y, n1 ? sn : sp);
+        k[q].z = __fadd_rn(k[q].z, n2 ? sn : sp); k[q].w = __fadd_rn(k[q].w, n3 ? sn : sp);
+      } else {
+        const uint32_t vq = (vmask >> (4 * (q ^ sw))) & 0xfu;
+        nib &= vq;
+        if (vq & 1u) k[q].x = __fadd_rn(k[q].x, n0 ? sn : sp);
+        if (vq & 2u) k[q].y = __fadd_rn(k[q].y, n1 ? sn : sp);
+        if (vq & 4u) k[q].z = __fadd_rn(k[q].z, n2 ? sn : sp);
+        if (vq & 8u) k[q].w = __fadd_rn(k[q].w, n3 ? sn : sp);
+      }
+      word |= nib << (4 * q);
+    }
+    w[0] = word;
+  } else {
+    const float s = __uint_as_float(code << 23), inv = __uint_as_float((254u - code) << 23);
+    const float big = 8388608.f + float(1 << (Q - 1));
+    const float neg_ms = -__fmul_rn(big, s);
+#pragma unroll
+    for (int j = 0; j < Q; j++) w[j] = 0;
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      const float z0 = __fmaf_rn(__fsub_rn(v[q].x, k[q].x), inv, big), z1 = __fmaf_rn(__fsub_rn(v[q].y, k[q].y), inv, big);
+      const float z2 = __fmaf_rn(__fsub_rn(v[q].z, k[q].z), inv, big), z3 = __fmaf_rn(__fsub_rn(v[q].w, k[q].w), inv, big);
+      k[q].x = __fadd_rn(k[q].x, __fmaf_rn(z0, s, neg_ms)); k[q].y = __fadd_rn(k[q].y, __fmaf_rn(z1, s, neg_ms));
+      k[q].z = __fadd_rn(k[q].z, __fmaf_rn(z2, s, neg_ms)); k[q].w = __fadd_rn(k[q].w, __fmaf_rn(z3, s, neg_ms));
+      const uint32_t b0 = __float_as_uint(z0), b1 = __float_as_uint(z1), b2 = __float_as_uint(z2), b3 = __float_as_uint(z3);
+      if (Q == 8) {
+        w[q % Q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+      } else {
+        constexpr uint32_t m = (1u << Q) - 1u;
+        const uint32_t four = (b0 & m) | ((b1 & m) << Q) | ((b2 & m) << (2 * Q)) | ((b3 & m) << (3 * Q));
+        w[(q * Q / 8) % Q] |= four << ((q * 4 * Q) & 31);
+      }
     }
   }
 }
@@ -274,7 +394,6 @@ __device__ __forceinline__ float residual_maxabs(const float4 (&v)[8], const flo
   }
   return m;
 }
-
 // bits of the largest |v| among the 32 elements
 __device__ __forceinline__ uint32_t max_abs_bits(const float4 (&v)[8]) {
   float m = 0.f;
@@ -283,485 +402,535 @@ __device__ __forceinline__ uint32_t max_abs_bits(const float4 (&v)[8]) {
   return __float_as_uint(m);
 }
 
-// the sign word of v - k (bit i set = element i is not positive) and, if code != 0, the step of the mirror
-template <bool FULL>
-__device__ __forceinline__ uint32_t sign_word_and_step(const float4 (&v)[8], float4 (&k)[8], uint32_t code, int sw, uint32_t vmask) {
-  const float sp = __uint_as_float(code << 23), sn = __uint_as_float((code << 23) | 0x80000000u);
-  uint32_t word = 0;
-#pragma unroll
-  for (int q = 0; q < 8; q++) {
-    const int sh = 4 * (q ^ sw);
-    const bool n0 = !(__fsub_rn(v[q].x, k[q].x) > 0.f), n1 = !(__fsub_rn(v[q].y, k[q].y) > 0.f);
-    const bool n2 = !(__fsub_rn(v[q].z, k[q].z) > 0.f), n3 = !(__fsub_rn(v[q].w, k[q].w) > 0.f);
-    uint32_t nib = (n0 ? 1u : 0u) | (n1 ? 2u : 0u) | (n2 ? 4u : 0u) | (n3 ? 8u : 0u);
-    if (FULL) {
-      if (code) {
-        k[q].x = __fadd_rn(k[q].x, n0 ? sn : sp);
-        k[q].y = __fadd_rn(k[q].y, n1 ? sn : sp);
-        k[q].z = __fadd_rn(k[q].z, n2 ? sn : sp);
-        k[q].w = __fadd_rn(k[q].w, n3 ? sn : sp);
-      }
-    } else {
-      const uint32_t vq = (vmask >> sh) & 0xfu;
-      nib &= vq;
-      if (code) {
-        if (vq & 1u) k[q].x = __fadd_rn(k[q].x, n0 ? sn : sp);
-        if (vq & 2u) k[q].y = __fadd_rn(k[q].y, n1 ? sn : sp);
-        if (vq & 4u) k[q].z = __fadd_rn(k[q].z, n2 ? sn : sp);
-        if (vq & 8u) k[q].w = __fadd_rn(k[q].w, n3 ? sn : sp);
-      }
-    }
-    word |= nib << sh;
-  }
-  return word;
-}
-
-struct GroupSmem {
-  int off_slots;    // [kGroups][kSlots][kTileBytes]
-  int off_vstage;   // [kGroups][kTileBytes]   values of the tile on their way back to global memory
-  int off_out;      // [kGroups][2][3 frames][payload_bytes]
-  int off_bar;      // uint64_t[kGroups][kSlots]
-  int off_red;      // float[kGroups][2][4]   cross-warp partials for blocks of 2048/4096
-  int off_flags;    // uint32_t[kGroups][3]  per-step OR flags (changed / nonsilent / wait failed)
-  int total;
-};
-__host__ __device__ inline GroupSmem group_layout(int payload_bytes, int kGroups) {
-  GroupSmem m;
-  int off = 0;
-  m.off_slots = off;
-  const int kSlots = slots_for(kGroups);
-  off += kGroups * kSlots * kTileBytes;
-  m.off_vstage = off;
-  off += kGroups * kTileBytes;
-  m.off_out = off;
-  off += kGroups * 2 * 3 * ((payload_bytes + 127) & ~127);
-  m.off_bar = off;
-  off += 8 * kGroups * kSlots;
-  m.off_red = off;
-  off += 4 * kGroups * 2 * 4;
-  m.off_flags = off;
-  off += 4 * kGroups * 4;
-  m.total = (off + 127) & ~127;
-  return m;
-}
-
 }  // namespace
 
-int round_main_smem_bytes(int, int, int payload_bytes, int* stages_out) {
-  if (stages_out) *stages_out = slots_for(3);
-  return group_layout(payload_bytes, 3).total;
-}
+int round_smem_bytes(int, int payload_bytes) { return smem_layout(payload_bytes).total; }
 
-template <int kGroups>
-__global__ void __launch_bounds__(kGroups * kGroupThreads, 1) round_main_kernel(const __grid_constant__ RoundParams p) {
+// ----------------------------------------------------------------------------------------------
+// the kernel
+// ----------------------------------------------------------------------------------------------
+template <int Q>
+__global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_constant__ RoundParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kSlots = slots_for(kGroups);
-  const GroupSmem lay = group_layout(p.payload_bytes, kGroups);
+  const SmemLayout lay = smem_layout(p.payload_bytes);
   const int tid = threadIdx.x;
-  const int g = tid >> 7;           // group
-  const int t = tid & 127;          // thread in group = 32-element chunk of the tile
+  const bool is_io = tid >= kGroups * kGroupThreads;
+  const int g = is_io ? (tid - kGroups * kGroupThreads) >> 5 : tid >> 7;
   const int lane = tid & 31;
-  const int wig = (tid >> 5) & 3;   // warp in group
-  const int sw = t & 7;             // XOR swizzle of this thread's eight 16-byte pieces
-  uint8_t* slots = smem + lay.off_slots + size_t(g) * kSlots * kTileBytes;
-  float4* vstage4 = reinterpret_cast<float4*>(smem + lay.off_vstage + size_t(g) * kTileBytes) + t * 8;
-  const int pb_pad = (p.payload_bytes + 127) & ~127;
-  uint8_t* outbuf = smem + lay.off_out + size_t(g) * 2 * kMaxFrames * pb_pad;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + g * kSlots;
-  float* s_red = reinterpret_cast<float*>(smem + lay.off_red) + g * 8;
-  uint32_t* s_flags = reinterpret_cast<uint32_t*>(smem + lay.off_flags) + g * 4;
+  uint8_t* slots = smem + lay.off_slots + size_t(g) * kSlots * lay.slot_stride;
+  StepDesc* desc = reinterpret_cast<StepDesc*>(smem + lay.off_desc) + g * kSlots;
+  StepDesc* pubq = reinterpret_cast<StepDesc*>(smem + lay.off_pubq) + g * kPubQueue;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + g * (2 * kSlots + 1);
+  uint64_t* done = full + kSlots;
+  uint64_t* gsync = full + 2 * kSlots;
+  uint32_t* words = reinterpret_cast<uint32_t*>(smem + lay.off_words) + g * 8;
+  uint32_t* sflags = words;          // [kSlots]
+  uint32_t* armed = words + 4;       // steps armed so far
+  uint32_t* abort_flag = words + 5;
+  float* s_red = reinterpret_cast<float*>(smem + lay.off_red) + g * 16;
 
-  const int par = p.round & 1;
-  const int count = p.work_count[par];
-  const int L = p.n_links;
-  const int arrays = 1 + L;
-  const int lb = p.log2_block;
-  const int pb = p.payload_bytes;
-  const int64_t n = p.n;
-  const int stride = int(gridDim.x) * kGroups;
-  const int first = int(blockIdx.x) * kGroups + g;
-  const int my_count = count > first ? (count - first + stride - 1) / stride : 0;
-  const int total_steps = my_count * arrays;
-  const int tpb = lb - 5;           // log2(threads per block)
-
-  if (t == 0) {
-    s_flags[0] = s_flags[1] = s_flags[2] = 0;
-    for (int s = 0; s < kSlots; s++) mbar_init(full + s, 1);
+  if (tid == 0) {
+    for (int i = 0; i < kGroups; i++) {
+      uint64_t* b = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + i * (2 * kSlots + 1);
+      for (int s = 0; s < kSlots; s++) {
+        mbar_init(b + s, 1);           // full: the I/O warp's arrive (+ the copies' bytes)
+        mbar_init(b + kSlots + s, 4);  // done: one arrive per compute warp
+      }
+      mbar_init(b + 2 * kSlots, 4);    // group sync of the compute warps
+      uint32_t* wd = reinterpret_cast<uint32_t*>(smem + lay.off_words) + i * 8;
+      for (int j = 0; j < 8; j++) wd[j] = 0;
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
   }
-  __syncthreads();
+  __syncthreads();  // the only CTA-wide barrier: from here on the groups, and the two kinds of warp, run on their own
 
-  // ---- copy issue (thread 0 of the group).  Step c = (tile index c / arrays, array c % arrays).
-  // The tile ids of this and the next listed tile are kept in registers by every thread.
-  int tile_cur = my_count > 0 ? p.worklist[first] : 0;
-  int tile_next = my_count > 1 ? p.worklist[first + stride] : 0;
-  uint4 cw_cur = my_count > 0 ? *reinterpret_cast<const uint4*>(p.ctrl + size_t(tile_cur) * 16) : make_uint4(0u, 0u, 0u, 0u);
-  // Mirrors are visited in link order on even rounds and in reverse order on odd rounds: a frame is applied to the
-  // values in its own link's step, so links visited earlier in the same tile forward it one round later, and
-  // alternating the order shares that delay out.
-  const bool reverse = (p.round & 1) != 0;
-  auto link_of = [&](int a) -> int { return reverse ? L - a : a - 1; };
-  auto src_of = [&](int tile, int a) -> const float* {
-    return (a == 0 ? p.values : p.mirror[link_of(a)]) + size_t(tile) * kTile;
-  };
-  auto issue_load = [&](int c, int tile) {
-    const int s = c % kSlots;
-    mbar_expect_tx(full + s, kTileBytes);
-    bulk_g2s(slots + size_t(s) * kTileBytes, src_of(tile, c % arrays), kTileBytes, full + s);
-  };
-  if (t == 0) {
-    for (int c = 0; c < kSlots - 1 && c < total_steps; c++) issue_load(c, c / arrays == 0 ? tile_cur : tile_next);
-  }
+  const int L = p.n_links;
+  const int pb = p.payload_bytes;
+  const int tpb = p.log2_block - 5;  // log2(threads per block of the quantiser)
+  const uint64_t limit_ns = p.wait_ns;
+  uint64_t* const launch_words = p.status + (p.parity ? kDsLaunch1 : kDsLaunch0);
 
-  float res_max0 = 0.f, res_max1 = 0.f, res_max2 = 0.f;  // largest outstanding |residual| per link seen by this thread
-  uint32_t n_rx = 0, n_tx = 0, n_blocked = 0, n_pending = 0;
-  bool aborted = false;
+  if (!is_io) {
+    // =========================================================================================
+    // compute warps
+    // =========================================================================================
+    const int t = tid & 127;          // thread in group = 32-element chunk of the tile
+    const int wig = (tid >> 5) & 3;   // warp in group
+    const int sw = t & 7;             // XOR swizzle of this thread's eight 16-byte pieces
+    const int64_t n = p.n;
+    float res_max0 = 0.f, res_max1 = 0.f, res_max2 = 0.f;
+    uint32_t gphase = 0;
+    float4 v[8];
+    uint32_t vmax_mine = 0;
 
-  for (int i = 0; i < my_count && !aborted; i++) {
-    const int tile = tile_cur;
-    const int tile_nn = (i + 2 < my_count) ? p.worklist[first + (i + 2) * stride] : 0;  // prefetched two tiles ahead
-    const uint4 cw = cw_cur;
-    if (i + 1 < my_count) cw_cur = *reinterpret_cast<const uint4*>(p.ctrl + size_t(tile_next) * 16);  // used one tile later
-    const uint32_t in_lo = cw.x, in_hi = cw.y, out_lo = cw.z, out_hi = cw.w;
-    auto in_byte = [&](int r) -> uint32_t { return ((r < 4 ? in_lo : in_hi) >> ((r & 3) * 8)) & 0xffu; };
-    auto out_byte = [&](int r) -> uint32_t { return ((r < 4 ? out_lo : out_hi) >> ((r & 3) * 8)) & 0xffu; };
-    const int64_t ebase = int64_t(tile) * kTile + int64_t(t) * 32;
-    const bool full_chunk = ebase + 32 <= n;
-    const int64_t left = n - ebase;  // elements of this thread's chunk that exist
-    const uint32_t vmask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << int(left)) - 1u));
-    const bool rx_any = (in_lo & 0xc0c0c0c0u) != 0 || (in_hi & 0xc0c0c0c0u) != 0;
-    bool pend_tile = false;
-    uint32_t sent_lo = 0, sent_hi = 0;
-
-    float4 v[8];  // piece q holds elements 4*(q^sw) .. +3 of this thread's 32
-    for (int a = 0; a < arrays && !aborted; a++) {
-      const int c = i * arrays + a;
-      const int s = c % kSlots;
-      float4* slot4 = reinterpret_cast<float4*>(slots + size_t(s) * kTileBytes) + t * 8;
-      const int l = a == 0 ? -1 : link_of(a);
-
-      // Frames that concern this step: none for the values, the link's own in-rings for a mirror; they are
-      // decoded once and added to the mirror and to the values, which stay in registers for the whole tile.
-      // (A few hundred bytes per tile, from L1/L2.)  They are fetched three at a time so that their load
-      // latencies overlap, the first batch before the wait on the slot.
-      int it_r = -1, it_f = 0, it_avail = 0;
-      uint32_t it_ib = 0;
-      auto next_frame = [&]() -> const uint8_t* {
-        if (!rx_any || a == 0) return nullptr;
-        while (true) {
-          if (it_r >= 0 && it_f < it_avail) {
-            const int slot_no = (int(it_ib & 63u) + it_f) & (p.ring_slots - 1);  // ring_slots is a power of two
-            it_f++;
-            return p.in[it_r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
-          }
-          it_r++;
-          if (it_r >= p.n_in) return nullptr;
-          it_ib = in_byte(it_r);
-          it_avail = p.in[it_r].link != l ? 0 : int(it_ib >> 6);
-          it_f = 0;
-        }
-      };
-      const uint8_t *fp0 = next_frame(), *fp1 = fp0 ? next_frame() : nullptr, *fp2 = fp1 ? next_frame() : nullptr;
-      uint32_t fw0 = 0, fc0 = 0, fw1 = 0, fc1 = 0, fw2 = 0, fc2 = 0;
-      auto load_batch = [&]() {
-        if (fp0) { fw0 = ld_u32_ca(fp0 + 4 * t); fc0 = ld_u8_ca(fp0 + 4 * kWordsPerTile + (t >> tpb)); }
-        if (fp1) { fw1 = ld_u32_ca(fp1 + 4 * t); fc1 = ld_u8_ca(fp1 + 4 * kWordsPerTile + (t >> tpb)); }
-        if (fp2) { fw2 = ld_u32_ca(fp2 + 4 * t); fc2 = ld_u8_ca(fp2 + 4 * kWordsPerTile + (t >> tpb)); }
-      };
-      load_batch();
-
-      // A wait that runs out does not leave the loop by itself (the group's barrier below needs all 128
-      // threads): the thread finishes the step on whatever the slot holds and reports the failure through
-      // the step's flags, so that the whole group stops together before anything is stored.
-      const bool wait_failed = !mbar_wait_bounded(full + s, uint32_t(c / kSlots) & 1u);
-      if (t == 0) s_flags[(c + 1) % 3] = 0;  // flags of the next step; last read two barriers ago
-      float4 k[8];
-      if (a == 0) {
-#pragma unroll
-        for (int q = 0; q < 8; q++) v[q] = slot4[q ^ sw];
-      } else {
-#pragma unroll
-        for (int q = 0; q < 8; q++) k[q] = slot4[q ^ sw];
-      }
-
-      bool changed = false;
-      auto apply_one = [&](uint32_t w, uint32_t code) {
-        if (t == 0) n_rx++;
-        if (!code) return;
-        changed = true;
-        const uint32_t sb = code << 23;  // bits of 2^(code-127)
-        if (full_chunk) apply_frame2<true>(v, k, w, sb, sw, vmask); else apply_frame2<false>(v, k, w, sb, sw, vmask);
-      };
-      while (fp0) {
-        const uint32_t w0 = fw0, c0 = fc0, w1 = fw1, c1 = fc1, w2 = fw2, c2 = fc2;
-        const bool h1 = fp1 != nullptr, h2 = fp2 != nullptr;
-        fp0 = h2 ? next_frame() : nullptr;   // the next batch goes out before this one is applied
-        fp1 = fp0 ? next_frame() : nullptr;
-        fp2 = fp1 ? next_frame() : nullptr;
-        load_batch();
-        apply_one(w0, c0);
-        if (h1) apply_one(w1, c1);
-        if (h2) apply_one(w2, c2);
-      }
-
-      int n_frames = 0;             // frames this step may push: room in every out-ring of the link, at most frames_per_round
-      uint32_t nonsilent_mask = 0;  // bit f: this thread's block had something to say in pass f
-      if (a > 0) {
-        // ---------------- quantise values - mirror for link l, up to frames_per_round times in a row:
-        // every pass is one more 1-bit frame of the same stream, made while the data is in registers
-        int room = 3;             // free ring slots, the minimum over the link's out-rings
-        bool any_ring = false;
-        for (int r = 0; r < p.n_out; r++) {
-          if (p.out[r].link != l) continue;
-          any_ring = true;
-          room = min(room, int(out_byte(r) >> 6));
-        }
-        n_frames = any_ring ? min(room, p.frames_per_round) : 0;
-        uint32_t vmax = max_abs_bits(v);
-        for (int sft = 0; sft < tpb && sft < 5; sft++) vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1 << sft));
-        const int passes = n_frames > 0 ? n_frames : 1;  // without ring space one pass still tells whether work is left
-        for (int f = 0; f < passes; f++) {
-          float xm = residual_maxabs(v, k);
-          if (f == 0) {
-            if (l == 0) res_max0 = fmaxf(res_max0, xm); else if (l == 1) res_max1 = fmaxf(res_max1, xm); else res_max2 = fmaxf(res_max2, xm);
-          }
-          // blocks larger than 32 elements: maximum over lanes (up to 1024), then over the group's warps
-          for (int sft = 0; sft < tpb && sft < 5; sft++) xm = fmaxf(xm, __shfl_xor_sync(0xffffffffu, xm, 1 << sft));
-          uint32_t vm = vmax;
-          if (tpb > 5) {
-            if (lane == 0) {
-              s_red[wig] = xm;
-              s_red[4 + wig] = __uint_as_float(vmax);
-            }
-            group_bar(g);
-            const float a0 = s_red[0], a1 = s_red[1], a2 = s_red[2], a3 = s_red[3];
-            const uint32_t b0 = __float_as_uint(s_red[4]), b1 = __float_as_uint(s_red[5]);
-            const uint32_t b2 = __float_as_uint(s_red[6]), b3 = __float_as_uint(s_red[7]);
-            if (tpb == 6) {  // 2048: warps {0,1} and {2,3}
-              xm = wig < 2 ? fmaxf(a0, a1) : fmaxf(a2, a3);
-              vm = wig < 2 ? max(b0, b1) : max(b2, b3);
-            } else {         // 4096: the whole tile
-              xm = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
-              vm = max(max(b0, b1), max(b2, b3));
-            }
-            group_bar(g);  // s_red is reused by the next pass
-          }
-          const int code = block_code_dev(xm, vm, p.min_exp, p.rel_bits);
-          if (code) nonsilent_mask |= 1u << f;
-          if (n_frames > 0) {
-            const uint32_t word = full_chunk ? sign_word_and_step<true>(v, k, uint32_t(code), sw, vmask)
-                                             : sign_word_and_step<false>(v, k, uint32_t(code), sw, vmask);
-            if (code) changed = true;
-            uint8_t* ob = outbuf + size_t((c & 1) * kMaxFrames + f) * pb_pad;
-            reinterpret_cast<uint32_t*>(ob)[t] = word;
-            if ((t & ((1 << tpb) - 1)) == 0) ob[4 * kWordsPerTile + (t >> tpb)] = uint8_t(code);
-          }
-        }
-      }
-
-      // ---------------- a changed mirror goes back through its slot (the values are written at the end of the tile)
-      if (changed && a > 0) {
-#pragma unroll
-        for (int q = 0; q < 8; q++) slot4[q ^ sw] = k[q];
-      }
-      // the tile's values leave through a staging buffer after the last mirror (if any frame arrived for the tile)
-      const bool store_values = rx_any && a == arrays - 1;
-      if (store_values) {
-#pragma unroll
-        for (int q = 0; q < 8; q++) vstage4[q ^ sw] = v[q];
-      }
-      fence_async_smem();
-      {
-        const uint32_t mine = (changed ? kFlagChanged : 0u) | (nonsilent_mask * kFlagNonsilent0) | (wait_failed ? kFlagFailed : 0u);
-        const uint32_t warp_bits = __reduce_or_sync(0xffffffffu, mine);
-        if (lane == 0 && warp_bits) atomicOr(&s_flags[c % 3], warp_bits);
-      }
-      group_bar(g);
-      const uint32_t step_flags = s_flags[c % 3];
-      if (step_flags & kFlagFailed) {
-        aborted = true;
+    for (uint32_t c = 0;; c++) {
+      const int s = int(c % kSlots);
+      uint8_t* slot = slots + size_t(s) * lay.slot_stride;
+      if (!wait_step(full + s, (c / kSlots) & 1u, armed, c, abort_flag, limit_ns)) {
+        // Nothing of this step is stored: the warp reports the failure and leaves; the I/O warp then stops the group.
+        if (lane == 0) atomicOr(&sflags[s], kFlagFailed);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(done + s);
         break;
       }
-      const bool any_changed = (step_flags & kFlagChanged) != 0;
-      const uint32_t ns_bits = step_flags / kFlagNonsilent0;  // bit f: pass f produced a frame worth sending
-      // work is left if the last pass still had something to say (or nothing could be sent at all)
-      pend_tile |= (ns_bits >> (n_frames > 0 ? n_frames - 1 : 0)) != 0;
+      const StepDesc d = desc[s];
+      if (d.flags & kDescExit) break;
+      const int tile = d.tile, l = d.link;
+      float4* slot_v = reinterpret_cast<float4*>(slot) + t * 8;
+      float4* slot_k = reinterpret_cast<float4*>(slot + kTileBytes) + t * 8;
+      const int64_t left = n - (int64_t(tile) * kTile + int64_t(t) * 32);  // elements of this thread's chunk that exist
+      const bool full_chunk = left >= 32;
+      const uint32_t vmask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << int(left)) - 1u));
+      const bool masked = (Q == 1) && !full_chunk;
+      bool failed = false;
 
-      if (t == 0) {
-        void* gdst = const_cast<float*>(src_of(tile, a));
-        if (any_changed && a > 0) bulk_s2g(gdst, slots + size_t(s) * kTileBytes, kTileBytes);
-        if (store_values) bulk_s2g(p.values + size_t(tile) * kTile, smem + lay.off_vstage + size_t(g) * kTileBytes, kTileBytes);
-        if (a > 0 && n_frames > 0 && ns_bits) {
-          int sent_here = 0;
-          for (int f = 0; f < n_frames; f++) {
-            if (!((ns_bits >> f) & 1u)) continue;  // an all-silent pass is not a frame
-            const uint8_t* ob = outbuf + size_t((c & 1) * kMaxFrames + f) * pb_pad;
-            for (int r = 0; r < p.n_out; r++) {
-              if (p.out[r].link != l) continue;
-              const int slot_no = (int(out_byte(r) & 63u) + sent_here) & (p.ring_slots - 1);
-              bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + tile) * pb, ob, uint32_t(pb));
-              n_tx++;
+      // ---- frames: decoded into one accumulated step per element.  `only_link` < 0 takes every ring.
+      auto decode_frames = [&](float4 (&acc)[8], int only_link) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        int it_r = -1, it_f = 0, it_avail = 0;
+        uint32_t it_ib = 0;
+        auto next_frame = [&]() -> const uint8_t* {
+          while (true) {
+            if (it_r >= 0 && it_f < it_avail) {
+              const int slot_no = (int(it_ib & 63u) + it_f) & (p.ring_slots - 1);
+              it_f++;
+              return p.in[it_r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
             }
-            sent_here++;
+            it_r++;
+            if (it_r >= p.n_in) return nullptr;
+            it_ib = ctrl_byte(d.in_lo, d.in_hi, it_r);
+            it_avail = (only_link >= 0 && p.in[it_r].link != only_link) ? 0 : int(it_ib >> 6);
+            it_f = 0;
           }
-          for (int r = 0; r < p.n_out; r++) {
-            if (p.out[r].link != l) continue;
-            if (r < 4) sent_lo |= uint32_t(sent_here) << (r * 8); else sent_hi |= uint32_t(sent_here) << ((r - 4) * 8);
-          }
-        } else if (a > 0 && ns_bits && p.do_tx) {
-          n_blocked++;
+        };
+        // one frame is in flight while the one before it is applied
+        uint32_t w_cur[Q], c_cur = 0, w_nxt[Q], c_nxt = 0;
+        const uint8_t* fp = next_frame();
+        if (fp) load_frame<Q>(fp, t, tpb, w_cur, c_cur);
+        while (fp) {
+          const uint8_t* fn = next_frame();
+          if (fn) load_frame<Q>(fn, t, tpb, w_nxt, c_nxt);
+          if (masked) add_frame<Q, true>(acc, w_cur, c_cur, sw, vmask); else add_frame<Q, false>(acc, w_cur, c_cur, sw, vmask);
+          fp = fn;
+#pragma unroll
+          for (int j = 0; j < Q; j++) w_cur[j] = w_nxt[j];
+          c_cur = c_nxt;
         }
-        bulk_commit();
-        // the slot used one step ago is free once its store (if any) has read it: refill it
-        bulk_wait_read_1();
-        const int cn = c + kSlots - 1;
-        if (cn < total_steps) {
-          const int ti = cn / arrays;
-          issue_load(cn, ti == i ? tile : (ti == i + 1 ? tile_next : tile_nn));
+      };
+
+      if (d.flags & kDescFirst) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) v[q] = slot_v[q ^ sw];
+        if (d.flags & kDescRxAny) {
+          float4 acc[8];
+          decode_frames(acc, -1);
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            v[q].x = __fadd_rn(v[q].x, acc[q].x); v[q].y = __fadd_rn(v[q].y, acc[q].y);
+            v[q].z = __fadd_rn(v[q].z, acc[q].z); v[q].w = __fadd_rn(v[q].w, acc[q].w);
+            slot_v[q ^ sw] = acc[q];  // leaves as a reduce-add into the values
+          }
+        }
+        vmax_mine = max_abs_bits(v);
+      }
+
+      float4 k[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) k[q] = slot_k[q ^ sw];
+      bool changed = false;
+      if (d.flags & kDescRxLink) {
+        float4 acc[8];
+        if (L == 1) {
+          // one link: what arrived for the values is what arrived on this link, and the slot still holds it
+#pragma unroll
+          for (int q = 0; q < 8; q++) acc[q] = slot_v[q ^ sw];
+        } else {
+          decode_frames(acc, l);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          k[q].x = __fadd_rn(k[q].x, acc[q].x); k[q].y = __fadd_rn(k[q].y, acc[q].y);
+          k[q].z = __fadd_rn(k[q].z, acc[q].z); k[q].w = __fadd_rn(k[q].w, acc[q].w);
+        }
+        changed = true;
+      }
+
+      // ---- quantise values - mirror for link l
+      float xm = residual_maxabs(v, k);
+      if (l == 0) res_max0 = fmaxf(res_max0, xm); else if (l == 1) res_max1 = fmaxf(res_max1, xm); else res_max2 = fmaxf(res_max2, xm);
+      uint32_t vm = vmax_mine;
+      // blocks larger than 32 elements: maximum over lanes (up to 1024), then over the group's warps
+      for (int sft = 0; sft < tpb && sft < 5; sft++) {
+        xm = fmaxf(xm, __shfl_xor_sync(0xffffffffu, xm, 1 << sft));
+        vm = max(vm, __shfl_xor_sync(0xffffffffu, vm, 1 << sft));
+      }
+      if (tpb > 5) {
+        float* red = s_red + (c & 1u) * 8;  // two buffers: a warp may be one step ahead of the slowest one
+        if (lane == 0) {
+          red[wig] = xm;
+          red[4 + wig] = __uint_as_float(vm);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(gsync);
+        if (!mbar_wait_bounded(gsync, gphase, limit_ns)) failed = true;
+        gphase ^= 1u;
+        const float a0 = red[0], a1 = red[1], a2 = red[2], a3 = red[3];
+        const uint32_t b0 = __float_as_uint(red[4]), b1 = __float_as_uint(red[5]);
+        const uint32_t b2 = __float_as_uint(red[6]), b3 = __float_as_uint(red[7]);
+        if (tpb == 6) {  // 2048: warps {0,1} and {2,3}
+          xm = wig < 2 ? fmaxf(a0, a1) : fmaxf(a2, a3);
+          vm = wig < 2 ? max(b0, b1) : max(b2, b3);
+        } else {         // 4096: the whole tile
+          xm = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+          vm = max(max(b0, b1), max(b2, b3));
         }
       }
+      const int code = block_code_dev<Q>(xm, vm, p.min_exp, p.rel_bits);
+      if ((d.flags & kDescTxOk) != 0) {
+        uint8_t* pay = slot + 2 * kTileBytes;
+        if (code) {
+          uint32_t w[Q];
+          if (masked) quantise<Q, true>(v, k, uint32_t(code), w, sw, vmask); else quantise<Q, false>(v, k, uint32_t(code), w, sw, vmask);
+          changed = true;
+          if (Q == 8) {
+            reinterpret_cast<uint4*>(pay)[t * 2] = make_uint4(w[0], w[1 % Q], w[2 % Q], w[3 % Q]);
+            reinterpret_cast<uint4*>(pay)[t * 2 + 1] = make_uint4(w[4 % Q], w[5 % Q], w[6 % Q], w[7 % Q]);
+          } else if (Q == 4) {
+            reinterpret_cast<uint4*>(pay)[t] = make_uint4(w[0], w[1 % Q], w[2 % Q], w[3 % Q]);
+          } else if (Q == 2) {
+            reinterpret_cast<uint2*>(pay)[t] = make_uint2(w[0], w[1 % Q]);
+          } else {
+            reinterpret_cast<uint32_t*>(pay)[t] = w[0];
+          }
+        }
+        if ((t & ((1 << tpb) - 1)) == 0) pay[4 * Q * kWordsPerTile + (t >> tpb)] = uint8_t(code);
+      }
+      if (changed) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) slot_k[q ^ sw] = k[q];
+      }
+      fence_async_smem();  // what this thread wrote into the slot is about to be read by bulk stores
+      {
+        const uint32_t mine = (changed ? kFlagChanged : 0u) | (code ? kFlagNonsilent : 0u) | (failed ? kFlagFailed : 0u);
+        const uint32_t warp_bits = __reduce_or_sync(0xffffffffu, mine);
+        if (lane == 0 && warp_bits) atomicOr(&sflags[s], warp_bits);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(done + s);
+      if (failed) break;
     }
-    if (aborted) break;
-    if (t == 0) {
-      *reinterpret_cast<uint2*>(p.sent + size_t(tile) * 8) = make_uint2(sent_lo, sent_hi);
-      p.tile_state[tile] = uint8_t(pend_tile ? 1 : 0);
-      n_pending += pend_tile ? 1 : 0;
-    }
-    tile_cur = tile_next;
-    tile_next = tile_nn;
-  }
 
-  if (t == 0) bulk_wait_all();  // every store of this thread has landed before the kernel ends
-  if (aborted) {
-    // Leave no copy in flight: give outstanding loads a bounded chance to land before the CTA's shared
-    // memory is released.
-    if (t == 0) {
-      atomicOr(reinterpret_cast<unsigned long long*>(p.status + kStErrors), (unsigned long long)kErrBarrierTimeout);
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStWaitTimeouts), 1ull);
-      const uint64_t t0 = globaltimer_ns();
-      while (globaltimer_ns() - t0 < 2ull * 1000 * 1000) {
+    // ---- statistics: the largest outstanding residual per link
+    {
+      float a0 = res_max0, a1 = res_max1, a2 = res_max2;
+      for (int o = 16; o > 0; o >>= 1) {
+        a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, o));
+        a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, o));
+        a2 = fmaxf(a2, __shfl_xor_sync(0xffffffffu, a2, o));
+      }
+      if (lane == 0) {  // non-negative floats order like their bit patterns
+        unsigned long long* rm = reinterpret_cast<unsigned long long*>(launch_words + kDlResMax);
+        if (a0 != 0.f) atomicMax(rm + 0, (unsigned long long)__float_as_uint(a0));
+        if (a1 != 0.f) atomicMax(rm + 1, (unsigned long long)__float_as_uint(a1));
+        if (a2 != 0.f) atomicMax(rm + 2, (unsigned long long)__float_as_uint(a2));
       }
     }
     return;
   }
 
-  // ---------------- statistics: one atomic per group and counter
-  {
-    float a0 = res_max0, a1 = res_max1, a2 = res_max2;
-    for (int o = 16; o > 0; o >>= 1) {
-      a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, o));
-      a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, o));
-      a2 = fmaxf(a2, __shfl_xor_sync(0xffffffffu, a2, o));
+  // ===========================================================================================
+  // I/O warp.  All 32 lanes run the same control flow; lane 0 issues copies, stores and flags.
+  // ===========================================================================================
+  const int gid = int(blockIdx.x) * kGroups + g;
+  const int gstride = int(gridDim.x) * kGroups;
+  const int my_count = p.n_tiles > gid ? (p.n_tiles - gid + gstride - 1) / gstride : 0;
+  const uint32_t smask = uint32_t(p.ring_slots) - 1u;
+  uint32_t issued = 0, retired = 0;
+  int pub_head = 0, pub_count = 0;
+  unsigned long long n_done = 0, n_tx = 0, n_rx = 0, n_blocked = 0, n_pending = 0, n_sweeps = 0;
+  bool aborted = false, tile_pending = false;
+
+  if (blockIdx.x == 0 && g == 0 && lane == 0) {
+    uint64_t* other = p.status + (p.parity ? kDsLaunch0 : kDsLaunch1);  // the next launch's half
+    for (int i = 0; i < 8; i++) other[i] = 0;
+  }
+
+  // sequence flags and credits of one retired step, once its stores have completed (lane 0)
+  auto publish_oldest = [&]() {
+    if (lane == 0) {
+      const StepDesc e = pubq[pub_head];
+      __threadfence_system();  // the payload is performed before the flag that announces it
+      if (e.sent) {
+        for (int r = 0; r < p.n_out; r++) {
+          if (p.out[r].link != e.link) continue;
+          const uint32_t slot_no = ctrl_byte(e.out_lo, e.out_hi, r) & 63u;
+          const uint32_t seq = ld_cg_u32(p.out[r].tx_seq + e.tile) + 1u;
+          st_relaxed_sys(p.out[r].flags_remote + size_t(slot_no) * p.n_tiles + e.tile, seq);
+          st_cg_u32(p.out[r].tx_seq + e.tile, seq);
+        }
+      }
+      if (e.flags & kDescLast) {
+        for (int r = 0; r < p.n_in; r++) {
+          const uint32_t avail = ctrl_byte(e.in_lo, e.in_hi, r) >> 6;
+          if (!avail) continue;
+          const uint32_t seq = ld_cg_u32(p.in[r].rx_seq + e.tile) + avail;
+          st_cg_u32(p.in[r].rx_seq + e.tile, seq);
+          st_relaxed_sys(p.in[r].credit_remote + e.tile, seq);
+        }
+      }
     }
-    if (lane == 0) {  // non-negative floats order like their bit patterns
-      if (a0 != 0.f) atomicMax(reinterpret_cast<unsigned long long*>(p.status + kStResidualMax0), (unsigned long long)__float_as_uint(a0));
-      if (a1 != 0.f) atomicMax(reinterpret_cast<unsigned long long*>(p.status + kStResidualMax1), (unsigned long long)__float_as_uint(a1));
-      if (a2 != 0.f) atomicMax(reinterpret_cast<unsigned long long*>(p.status + kStResidualMax2), (unsigned long long)__float_as_uint(a2));
+    pub_head = (pub_head + 1) & (kPubQueue - 1);
+    pub_count--;
+  };
+
+  // a finished step: its stores go out, its slot becomes free, the step before the one before it is published
+  auto retire = [&](uint32_t c) -> bool {
+    const int s = int(c % kSlots);
+    const bool ok = mbar_wait_bounded(done + s, (c / kSlots) & 1u, 2 * limit_ns);
+    const uint32_t f = ok ? ld_shared_volatile(sflags + s) : kFlagFailed;
+    if (f & kFlagFailed) return false;
+    if (lane == 0) {
+      const StepDesc d = desc[s];
+      uint8_t* slot = slots + size_t(s) * lay.slot_stride;
+      const bool sent = (d.flags & kDescTxOk) != 0 && (f & kFlagNonsilent) != 0;
+      if ((d.flags & kDescFirst) && (d.flags & kDescRxAny)) bulk_reduce_add_f32(p.values + size_t(d.tile) * kTile, slot, kTileBytes);
+      if (f & kFlagChanged) bulk_s2g(p.mirror[d.link] + size_t(d.tile) * kTile, slot + kTileBytes, kTileBytes);
+      if (sent) {
+        for (int r = 0; r < p.n_out; r++) {
+          if (p.out[r].link != d.link) continue;
+          const uint32_t slot_no = ctrl_byte(d.out_lo, d.out_hi, r) & 63u;
+          bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + d.tile) * pb, slot + 2 * kTileBytes, uint32_t(pb));
+          n_tx++;
+        }
+      }
+      bulk_commit();
+      StepDesc e = d;
+      e.sent = sent ? 1u : 0u;
+      pubq[(pub_head + pub_count) & (kPubQueue - 1)] = e;
+      if (f & kFlagNonsilent) {
+        tile_pending = true;  // more may be left to say (or nothing could be said at all)
+        if (!sent && p.do_tx) n_blocked++;
+      }
+      if (d.flags & kDescLast) {
+        if (tile_pending) {
+          st_cg_u32(p.tile_state + d.tile, 1u);
+          n_pending++;
+        }
+        tile_pending = false;
+        n_done++;
+        for (int r = 0; r < p.n_in; r++) n_rx += ctrl_byte(d.in_lo, d.in_hi, r) >> 6;
+      }
+      bulk_wait_read_all();  // the slot may be refilled
+    }
+    pub_count++;
+    __syncwarp();
+    if (pub_count > 2) {
+      if (lane == 0) bulk_wait_all_but_2();
+      publish_oldest();
+    }
+    return true;
+  };
+
+  for (int sweep = 0; sweep < p.sweeps && !aborted && my_count > 0; sweep++) {
+    const unsigned long long done_before = n_done;
+    int scan_pos = 0;
+    uint32_t pend = 0;                 // lanes whose scouted tile still has to be handed out
+    int sc_tile = 0;                   // what this lane found for its tile
+    uint32_t sc_in_lo = 0, sc_in_hi = 0, sc_out_lo = 0, sc_out_hi = 0;
+    int cur_tile = -1, cur_a = 0;      // the tile whose steps are being handed out
+    uint32_t cur_in_lo = 0, cur_in_hi = 0, cur_out_lo = 0, cur_out_hi = 0;
+    bool exhausted = my_count == 0;
+
+    while (true) {
+      if (!exhausted && issued - retired < uint32_t(kSlots)) {
+        if (cur_tile < 0) {
+          if (pend == 0) {
+            if (scan_pos >= my_count) {
+              exhausted = true;
+              continue;
+            }
+            // ---- look at 32 tiles at once, one per lane
+            const int j = scan_pos + lane;
+            const bool valid = j < my_count;
+            sc_tile = gid + j * gstride;
+            sc_in_lo = sc_in_hi = sc_out_lo = sc_out_hi = 0;
+            bool work = false;
+            if (valid) {
+              uint32_t dirty = ld_cg_u32(p.tile_state + sc_tile);
+              bool any = false;
+              if (p.do_rx) {
+                for (int r = 0; r < p.n_in; r++) {
+                  const uint32_t e = ld_cg_u32(p.in[r].rx_seq + sc_tile);
+                  uint32_t avail = 0;
+                  while (avail < uint32_t(kRxMax)) {
+                    const uint32_t fl = ld_acquire_sys(p.in[r].flags + size_t((e + avail) & smask) * p.n_tiles + sc_tile);
+                    if (fl != e + avail + 1u) break;
+                    avail++;
+                  }
+                  const uint32_t byte = (avail << 6) | (e & smask);
+                  if (r < 4) sc_in_lo |= byte << (r * 8); else sc_in_hi |= byte << ((r - 4) * 8);
+                  any |= avail != 0;
+                }
+              }
+              if (p.do_tx) {
+                for (int r = 0; r < p.n_out; r++) {
+                  const uint32_t tx = ld_cg_u32(p.out[r].tx_seq + sc_tile);
+                  const uint32_t cr = ld_acquire_sys(p.out[r].credit + sc_tile);
+                  const uint32_t room = (tx - cr) < uint32_t(p.ring_slots) ? 1u : 0u;
+                  const uint32_t byte = (room << 6) | (tx & smask);
+                  if (r < 4) sc_out_lo |= byte << (r * 8); else sc_out_hi |= byte << ((r - 4) * 8);
+                }
+              }
+              // The change mark is cleared before the tile's values are read (the copy is issued after this
+              // exchange has returned), and whoever changes the values sets it after the change: a change
+              // that this visit does not see leaves its mark for the next one.
+              if (dirty) dirty = atomicExch(p.tile_state + sc_tile, 0u);
+              work = dirty != 0 || any;
+            }
+            pend = __ballot_sync(0xffffffffu, work);
+            scan_pos += 32;
+            continue;
+          }
+          const int src = __ffs(pend) - 1;
+          pend &= pend - 1;
+          cur_tile = __shfl_sync(0xffffffffu, sc_tile, src);
+          cur_in_lo = __shfl_sync(0xffffffffu, sc_in_lo, src);
+          cur_in_hi = __shfl_sync(0xffffffffu, sc_in_hi, src);
+          cur_out_lo = __shfl_sync(0xffffffffu, sc_out_lo, src);
+          cur_out_hi = __shfl_sync(0xffffffffu, sc_out_hi, src);
+          cur_a = 0;
+        }
+        // ---- hand out step (cur_tile, link cur_a)
+        if (lane == 0) {
+          const int s = int(issued % kSlots);
+          uint8_t* slot = slots + size_t(s) * lay.slot_stride;
+          const int l = cur_a;
+          bool tx_any = false, tx_room = true, rx_link = false;
+          for (int r = 0; r < p.n_out; r++) {
+            if (p.out[r].link != l) continue;
+            tx_any = true;
+            tx_room &= (ctrl_byte(cur_out_lo, cur_out_hi, r) >> 6) != 0;
+          }
+          for (int r = 0; r < p.n_in; r++)
+            if (p.in[r].link == l && (ctrl_byte(cur_in_lo, cur_in_hi, r) >> 6) != 0) rx_link = true;
+          const bool rx_any = ((cur_in_lo | cur_in_hi) & 0xc0c0c0c0u) != 0;
+          StepDesc d;
+          d.tile = cur_tile;
+          d.link = l;
+          d.flags = (cur_a == 0 ? kDescFirst : 0u) | (rx_any ? kDescRxAny : 0u) | (tx_any && tx_room && p.do_tx ? kDescTxOk : 0u) |
+                    (rx_link ? kDescRxLink : 0u) | (cur_a == L - 1 ? kDescLast : 0u);
+          d.sent = 0;
+          d.in_lo = cur_in_lo; d.in_hi = cur_in_hi; d.out_lo = cur_out_lo; d.out_hi = cur_out_hi;
+          desc[s] = d;
+          sflags[s] = 0;
+          uint32_t bytes = (cur_a == 0 ? 2u : 1u) * uint32_t(kTileBytes);
+          if (cur_tile == p.stall_tile) bytes += 16;  // test hook: this barrier never completes
+          mbar_expect_tx(full + s, bytes);
+          if (cur_a == 0) bulk_g2s(slot, p.values + size_t(cur_tile) * kTile, kTileBytes, full + s);
+          bulk_g2s(slot + kTileBytes, p.mirror[l] + size_t(cur_tile) * kTile, kTileBytes, full + s);
+          st_shared_volatile(armed, issued + 1u);
+        }
+        issued++;
+        cur_a++;
+        if (cur_a == L) cur_tile = -1;
+        continue;
+      }
+      if (retired < issued) {
+        if (!retire(retired)) {
+          aborted = true;
+          break;
+        }
+        retired++;
+        continue;
+      }
+      break;  // every tile looked at, every step retired
+    }
+    if (aborted) break;
+    // ---- end of the sweep: every store has landed and is published before the tiles are looked at again
+    if (lane == 0) bulk_wait_all();
+    while (pub_count > 0) publish_oldest();
+    __syncwarp();
+    n_sweeps++;
+    if (n_done == done_before && sweep + 1 < p.sweeps) __nanosleep(1000);
+  }
+
+  if (aborted) {
+    // Stop the group.  The compute warps leave on the abort flag (or on the exit descriptor); copies that are still
+    // on their way get a bounded chance to land before the CTA's shared memory is released; what was stored is
+    // published; every tile of the group is marked for another visit.
+    if (lane == 0) st_shared_volatile(abort_flag, 1u);
+    __syncwarp();
+    for (uint32_t c = retired; c < issued; c++) (void)mbar_wait_bounded(full + int(c % kSlots), (c / kSlots) & 1u, limit_ns);
+    if (lane == 0) bulk_wait_all();
+    while (pub_count > 0) publish_oldest();
+    for (int j = lane; j < my_count; j += 32) st_cg_u32(p.tile_state + gid + j * gstride, 1u);
+    if (lane == 0) {
+      atomicOr(reinterpret_cast<unsigned long long*>(p.status + kDsErrors), (unsigned long long)kErrBarrierTimeout);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsWaitTimeouts), 1ull);
     }
   }
-  if (t == 0) {
-    atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStTilesProcessed), (unsigned long long)my_count);
-    if (n_tx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStFramesSent), (unsigned long long)n_tx);
-    if (n_rx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStFramesRecv), (unsigned long long)n_rx);
-    if (n_blocked) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStBlockedNoCredit), (unsigned long long)n_blocked);
-    if (n_pending) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStPendingTiles), (unsigned long long)n_pending);
+  if (lane == 0) {
+    // tell the compute warps that the launch is over (the slot of step `issued` is free: all earlier steps are retired
+    // or abandoned)
+    const int s = int(issued % kSlots);
+    StepDesc d;
+    d.tile = 0; d.link = 0; d.flags = kDescExit; d.sent = 0;
+    d.in_lo = d.in_hi = d.out_lo = d.out_hi = 0;
+    if (!aborted) {  // (after an abort the compute warps leave on the abort flag)
+      desc[s] = d;
+      mbar_arrive(full + s);
+      st_shared_volatile(armed, issued + 1u);
+    }
+    if (n_done) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsTilesProcessed), n_done);
+    if (n_tx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsFramesSent), n_tx);
+    if (n_rx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsFramesRecv), n_rx);
+    if (n_blocked) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsBlockedNoCredit), n_blocked);
+    if (n_done) atomicAdd(reinterpret_cast<unsigned long long*>(launch_words + kDlWork), n_done);
+    if (n_pending) atomicAdd(reinterpret_cast<unsigned long long*>(launch_words + kDlPending), n_pending);
     if (blockIdx.x == 0 && g == 0) {
-      const unsigned long long r = atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kStRounds), 1ull);
-      p.status[kStLastWorkCount] = uint64_t(count);
-      uint64_t* rec = p.status + kStWords + (r % kTraceEntries) * kTraceWords;  // trace ring, read by stats()
+      const unsigned long long r = atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsSweeps), n_sweeps);
+      uint64_t* rec = p.status + kDsTrace + (uint64_t(p.round) % kTraceEntries) * kTraceWords;  // trace ring, read by stats()
       rec[0] = globaltimer_ns();
-      rec[1] = r;
-      rec[2] = uint64_t(count);
-      rec[3] = p.status[kStFramesSent];
+      rec[1] = uint64_t(p.round);
+      rec[2] = n_done;
+      rec[3] = p.status[kDsFramesSent];
+      (void)r;
     }
   }
 }
 
 // ----------------------------------------------------------------------------------------------
-// launchers
+// launcher
 // ----------------------------------------------------------------------------------------------
-int launch_round_begin(const RoundParams& p, void* stream) {
-  int blocks = (p.n_tiles + 255) / 256;
-  round_begin_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return int(cudaGetLastError());
-}
-int launch_round_publish(const RoundParams& p, void* stream) {
-  int blocks = (p.n_tiles + 255) / 256;
-  round_publish_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return int(cudaGetLastError());
-}
-
-template <int G>
-static int launch_main_t(const RoundParams& p, int ctas, cudaStream_t stream) {
-  const int smem = group_layout(p.payload_bytes, G).total;
+template <int Q>
+static int launch_round_t(const RoundParams& p, int ctas, cudaStream_t stream) {
+  const int smem = smem_layout(p.payload_bytes).total;
   static int configured_for = -1;  // per instantiation
   if (configured_for < smem) {
-    cudaError_t e = cudaFuncSetAttribute(round_main_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(round_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
     configured_for = smem;
   }
-  round_main_kernel<G><<<ctas, G * kGroupThreads, smem, stream>>>(p);
+  round_kernel<Q><<<ctas, kCtaThreads, smem, stream>>>(p);
   return int(cudaGetLastError());
 }
 
-// The rounds `rounds[0..count)` as one executable graph: begin -> main -> publish of each, chained.  The graph is
-// built node by node, not by stream capture: while any stream of a device is capturing, a device-wide
-// synchronisation from any other thread (a user's cudaDeviceSynchronize) fails, and the engine thread builds its
-// graph at times the user cannot know.
-int build_round_graph(const RoundParams* rounds, int count, int ctas, void** exec_out) {
-  *exec_out = nullptr;
-  constexpr int G = 3;
-  cudaGraph_t graph = nullptr;
-  cudaError_t e = cudaGraphCreate(&graph, 0);
-  if (e != cudaSuccess) return int(e);
-  cudaGraphNode_t prev = nullptr;
-  for (int i = 0; i < count && e == cudaSuccess; i++) {
-    RoundParams p = rounds[i];
-    if (p.n_links < 1 || p.n_links > kMaxLinks) {
-      e = cudaErrorInvalidValue;
-      break;
-    }
-    const int smem = group_layout(p.payload_bytes, G).total;
-    e = cudaFuncSetAttribute(round_main_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) break;
-    void* args[1] = {&p};  // copied into the node when it is added
-    const unsigned tile_blocks = unsigned((p.n_tiles + 255) / 256);
-    struct {
-      void* fn;
-      unsigned grid, block, smem;
-    } k[3] = {{reinterpret_cast<void*>(round_begin_kernel), tile_blocks, 256u, 0u},
-              {reinterpret_cast<void*>(round_main_kernel<G>), unsigned(ctas), unsigned(G * kGroupThreads), unsigned(smem)},
-              {reinterpret_cast<void*>(round_publish_kernel), tile_blocks, 256u, 0u}};
-    for (int j = 0; j < 3 && e == cudaSuccess; j++) {
-      cudaKernelNodeParams np = {};
-      np.func = k[j].fn;
-      np.gridDim = dim3(k[j].grid);
-      np.blockDim = dim3(k[j].block);
-      np.sharedMemBytes = k[j].smem;
-      np.kernelParams = args;
-      np.extra = nullptr;
-      cudaGraphNode_t node = nullptr;
-      e = cudaGraphAddKernelNode(&node, graph, prev ? &prev : nullptr, prev ? 1 : 0, &np);
-      prev = node;
-    }
-  }
-  cudaGraphExec_t exec = nullptr;
-  if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
-  cudaGraphDestroy(graph);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return int(e);
-  }
-  *exec_out = exec;
-  return 0;
-}
-
-int launch_round_main(const RoundParams& p, int ctas, void* stream_v) {
+int launch_round(const RoundParams& p, int ctas, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (p.n_links < 1 || p.n_links > kMaxLinks) return int(cudaErrorInvalidValue);
-  // 3 groups of 128 threads: 168 registers per thread (no spills) and 3 x (3 slots + staging) x 16 KB of shared memory
-  return launch_main_t<3>(p, ctas, stream);
+  if (p.n_links < 1 || p.n_links > kMaxLinks || p.sweeps < 1) return int(cudaErrorInvalidValue);
+  if (p.ring_slots < 2 || p.ring_slots > 64 || (p.ring_slots & (p.ring_slots - 1))) return int(cudaErrorInvalidValue);
+  const int needed = (p.n_tiles + kGroups - 1) / kGroups;  // more CTAs than this would have no tile
+  if (ctas > needed) ctas = needed;
+  if (ctas < 1) ctas = 1;
+  switch (p.bits) {
+    case 1: return launch_round_t<1>(p, ctas, stream);
+    case 2: return launch_round_t<2>(p, ctas, stream);
+    case 4: return launch_round_t<4>(p, ctas, stream);
+    case 8: return launch_round_t<8>(p, ctas, stream);
+    default: return int(cudaErrorInvalidValue);
+  }
 }
 
 }  // namespace st

@@ -1,4 +1,4 @@
-// Parameter blocks and launch entry points of the sync-round kernels (host-visible, no CUDA syntax).
+// Parameter blocks and launch entry points of the sync-round kernel (host-visible, no CUDA syntax).
 //
 // One replica on one GPU holds `values` and, per link, a mirror (see ../core/codec.hpp for the
 // state model).  A *link* is a set of neighbours that share one mirror: a tree edge is a link with
@@ -10,15 +10,22 @@
 // live in the SENDER's memory (the receiver writes them).  Every poll is therefore a local load and
 // only stores cross the link.  Each 4096-element tile of the tensor is an independent stream with its
 // own sequence number, so no kernel ever waits for another GPU: a tile whose ring is full or whose
-// frame has not arrived is simply handled in a later round.
+// frame has not arrived is simply handled in a later sweep.
 //
-// A round is three launches on one stream:
-//   round_begin   – per tile: look at flags/credits once and build the work list;
-//   round_main    – per listed tile: stage values, mirrors and arrived frames with TMA bulk copies,
-//                   decode + accumulate + forward + re-quantise + push packed words and scales to the
-//                   neighbours' rings (reference hot loops src/sharedtensor.c:106-111, 124-127, 156-177);
-//   round_publish – per tile: sequence flags for the frames written (to receivers), credits for the
-//                   frames consumed (to senders).
+// A frame carries, per tile, `bits` bits per element (1: the sign of the residual, the reference's
+// format, src/sharedtensor.c:166-174; 2, 4, 8: the residual as a small integer times the block's
+// power-of-two step) and one exponent byte per block of `1 << log2_block` elements.
+//
+// One launch of the round kernel makes up to `sweeps` passes over the tensor.  In a pass every group of
+// the grid looks at its own tiles' flags and credits, and for each tile that has something to do
+//   - stages values and mirrors with TMA bulk copies,
+//   - decodes the frames that arrived, accumulates them into the values (a bulk reduce-add, so that
+//     updates made by other streams at the same time are kept) and into the mirror of the link they
+//     came from (reference hot loops src/sharedtensor.c:106-111, 124-127),
+//   - quantises values - mirror for every link, steps the mirror and pushes the packed codes and
+//     scales straight into the neighbours' ring slots (156-177),
+//   - and, once the stores have landed, publishes sequence flags to the receivers and credits to the
+//     senders.
 #pragma once
 #include <cstdint>
 
@@ -27,7 +34,7 @@ namespace st {
 constexpr int kTile = 4096;         // elements per tile (= per independent stream)
 constexpr int kMaxLinks = 3;        // mirrors per replica
 constexpr int kMaxRings = 8;        // inbound rings, and outbound rings, per replica
-constexpr int kRxMax = 3;           // frames taken per ring per tile per round
+constexpr int kRxMax = 3;           // frames taken per ring per tile per sweep
 constexpr int kWordsPerTile = kTile / 32;
 
 struct InRing {
@@ -55,62 +62,74 @@ struct RoundParams {
   int32_t n_in, n_out;
   InRing in[kMaxRings];
   OutRing out[kMaxRings];
-  int32_t ring_slots;
+  int32_t ring_slots;            // power of two, at most 64
   int32_t log2_block;            // 5..12
   int32_t scales_per_tile;       // kTile >> log2_block
-  int32_t payload_bytes;         // 4*kWordsPerTile + max(16, scales_per_tile)
+  int32_t bits;                  // 1, 2, 4 or 8 bits per element
+  int32_t payload_bytes;         // bits * 4 * kWordsPerTile + max(16, scales_per_tile)
   int32_t min_exp, rel_bits;     // gate, see BlockGate
-  // per-round scratch (all local)
-  uint8_t* ctrl;                 // [tile][16]: bytes 0..7 in-rings (avail<<6 | first slot), 8..15 out-rings (free slots, up to 3, <<6 | slot)
-  uint8_t* sent;                 // [tile][8]: number of frames round_main wrote for out-ring r
-  uint8_t* tile_state;           // [tile]: 1 = something may be left to send
-  int32_t* worklist;             // [n_tiles]
-  int32_t* work_count;           // [2], double buffered by round parity
-  uint64_t* status;              // see StatusWord
-  int32_t round;
-  int32_t do_rx, do_tx;          // receiver-only / sender-only rounds
-  int32_t frames_per_round;      // 1..3 successive 1-bit frames per link, tile and round
+  uint32_t* tile_state;          // [tile]: non-zero = the values of the tile may have changed since its last visit
+  uint64_t* status;              // see DevStatus
+  int32_t round;                 // number of this launch's first sweep (bookkeeping only)
+  int32_t parity;                // which half of the per-launch counters this launch uses
+  int32_t do_rx, do_tx;          // receiver-only / sender-only launches
+  int32_t sweeps;                // passes over the tensor in this launch (>= 1)
+  uint32_t wait_ns;              // upper bound of every wait on one of the kernel's own copies
+  int32_t stall_tile;            // test hook: the copy barrier of this tile expects more bytes than are copied (-1: none)
 };
 
-// indices into the status block (uint64 each)
+// Layout of the device status block (uint64 each).  Counters are cumulative; the per-launch words exist twice and a
+// launch uses the half given by RoundParams::parity (and clears the other half for the launch after it).
+enum DevStatus : int {
+  kDsSweeps = 0,
+  kDsTilesProcessed,
+  kDsFramesSent,       // tile-frames written to out-rings
+  kDsFramesRecv,       // tile-frames decoded from in-rings
+  kDsBlockedNoCredit,  // tile-links that had something to send but no ring space
+  kDsErrors,           // bit mask, see kErr*
+  kDsWaitTimeouts,
+  kDsLaunch0 = 8,      // per-launch words of parity 0: work, pending tiles, residual maxima of links 0..2 (fp32 bits)
+  kDsLaunch1 = 16,     // ... of parity 1
+  kDsTrace = 24,       // ring of kTraceEntries records {globaltimer ns, round, tiles handled by group 0, frames sent so far}
+  kTraceEntries = 64,
+  kTraceWords = 4,
+  kDsTotalWords = kDsTrace + kTraceEntries * kTraceWords
+};
+constexpr int kDlWork = 0, kDlPending = 1, kDlResMax = 2;  // offsets inside a per-launch half
+constexpr uint64_t kErrBarrierTimeout = 1, kErrBadCtrl = 2;
+
+// What GpuReplica::status() hands out: the counters in this order, then the trace ring.
 enum StatusWord : int {
   kStRounds = 0,
   kStTilesProcessed,
-  kStFramesSent,      // tile-frames written to out-rings
-  kStFramesRecv,      // tile-frames decoded from in-rings
-  kStBlockedNoCredit, // tile-links that had something to send but no ring space
-  kStErrors,          // bit mask, see kErr*
-  kStLastWorkCount,
-  kStResidualMax0,    // per link: bits of the largest |values - mirror| (fp32) the last round saw
+  kStFramesSent,
+  kStFramesRecv,
+  kStBlockedNoCredit,
+  kStErrors,
+  kStLastWorkCount,   // tiles handled by the last launch
+  kStResidualMax0,    // per link: bits of the largest |values - mirror| (fp32) the last launch saw
   kStResidualMax1,
   kStResidualMax2,
-  kStPendingTiles,    // tiles still marked pending after the last round
+  kStPendingTiles,    // tiles still marked pending after the last launch
   kStWaitTimeouts,
   kStWords = 16,
-  // after the counters: a ring of kTraceEntries records {globaltimer ns, round, listed tiles, frames sent so far}
-  kTraceEntries = 64,
-  kTraceWords = 4,
   kStTotalWords = kStWords + kTraceEntries * kTraceWords
 };
-constexpr uint64_t kErrBarrierTimeout = 1, kErrBadCtrl = 2;
 
 // Launchers.  `stream` is a cudaStream_t passed as void*.  Return a cudaError_t as int.
-int launch_round_begin(const RoundParams& p, void* stream);
-int launch_round_publish(const RoundParams& p, void* stream);
-int launch_round_main(const RoundParams& p, int ctas, void* stream);
-// `count` rounds chained into one executable graph (a cudaGraphExec_t), built without stream capture.
-int build_round_graph(const RoundParams* rounds, int count, int ctas, void** exec_out);
-int round_main_smem_bytes(int n_links, int n_in, int payload_bytes, int* stages_out);
+int launch_round(const RoundParams& p, int ctas, void* stream);
+int round_smem_bytes(int bits, int payload_bytes);
 
 // Element-wise kernels (copyToTensor / addFromTensor / pushUpdate; src/sharedtensor.c:435-446, 334-344).
 int launch_snapshot_f32(const float* values, float* out, int64_t n, void* stream);
 int launch_snapshot_bf16(const float* values, void* out_bf16, int64_t n, void* stream);
-int launch_add(float* values, const float* delta, int64_t n, uint8_t* tile_state, int n_tiles, int atomic, void* stream);
-int launch_sub_add(float* values, const float* neu, const float* old, int64_t n, uint8_t* tile_state, int n_tiles,
-                   int atomic, void* stream);
-int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, uint8_t* tile_state, int n_tiles,
-                           void* stream);
-int launch_fill_state(uint8_t* tile_state, int n_tiles, int value, void* stream);
+// atomic != 0: every element is added with a reduction at the L2, so the add commutes with whatever else adds into
+// `values` at the same time (the round kernel, other streams).
+int launch_add(float* values, const float* delta, int64_t n, int atomic, void* stream);
+int launch_sub_add(float* values, const float* neu, const float* old, int64_t n, int atomic, void* stream);
+int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, int atomic, void* stream);
+// Marks every tile as changed.  Launched behind an update on the same stream, so the marks become visible after the data.
+int launch_fill_state(uint32_t* tile_state, int n_tiles, uint32_t value, void* stream);
 // Per-segment sum of squares (table sync).  partials: scratch of table_scales_scratch_doubles(...) doubles.
 int64_t table_scales_scratch_doubles(int n_seg, int64_t n_total);
 int launch_table_scales(const float* x, const int64_t* seg_offsets_dev, int n_seg, int64_t n_total, double* partials,
@@ -124,7 +143,7 @@ int launch_snapshot_join(const float* values, float* dst_values, float* mirror, 
 // Tensor-scale frames for TCP edges, encoded/decoded on the device (wire format of the reference).
 int launch_tensor_maxabs(const float* v, const float* k, int64_t n, uint32_t* out2, void* stream);  // bits of max|v-k|, max|v|
 int launch_tensor_encode(const float* v, float* k, int64_t n, float scale, uint32_t* words, void* stream);
-int launch_tensor_decode(const uint32_t* words, float scale, int64_t n, float* v, float* k, uint8_t* tile_state,
-                         void* stream);
+// v += step (with L2 reductions if atomic_v, for the values) and k += step (plain; k may be null)
+int launch_tensor_decode(const uint32_t* words, float scale, int64_t n, float* v, float* k, int atomic_v, void* stream);
 
 }  // namespace st

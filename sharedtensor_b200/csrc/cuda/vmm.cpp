@@ -126,6 +126,22 @@ size_t vmm_granularity(int device) {
   return g;
 }
 
+// Zero-fills fresh memory and returns once that is done.  Not cudaMemset: that runs on the legacy default stream,
+// behind whatever the application has queued there, while the first users of the memory (the comm stream, a peer)
+// are not ordered against that stream at all.
+static void zero_now(void* ptr, size_t bytes) {
+  cudaStream_t s = nullptr;
+  if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    cudaMemset(ptr, 0, bytes);
+    cudaDeviceSynchronize();
+    return;
+  }
+  cudaMemsetAsync(ptr, 0, bytes, s);
+  cudaStreamSynchronize(s);
+  cudaStreamDestroy(s);
+}
+
 VmmBlock vmm_alloc(int device, size_t bytes, bool shareable, std::string* err) {
   VmmBlock b;
   b.device = device;
@@ -145,7 +161,7 @@ VmmBlock vmm_alloc(int device, size_t bytes, bool shareable, std::string* err) {
         b.ptr = ptr;
         b.bytes = rounded;
         b.handle = h;
-        cudaMemset(ptr, 0, rounded);
+        zero_now(ptr, rounded);
         if (prev >= 0) cudaSetDevice(prev);
         return b;
       }
@@ -162,7 +178,7 @@ VmmBlock vmm_alloc(int device, size_t bytes, bool shareable, std::string* err) {
     if (prev >= 0) cudaSetDevice(prev);
     return b;
   }
-  cudaMemset(ptr, 0, bytes);
+  zero_now(ptr, bytes);
   b.ptr = ptr;
   b.bytes = bytes;
   b.plain = true;

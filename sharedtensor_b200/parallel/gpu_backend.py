@@ -27,8 +27,9 @@ def _gpu_config(cfg: Config):
     g.rounds_in_flight = cfg.rounds_in_flight
     g.idle_sleep_us = cfg.idle_sleep_us
     g.round_interval_us = cfg.round_interval_us
-    g.frames_per_round = cfg.frames_per_round
-    g.use_graph = cfg.use_graph
+    g.bits = cfg.bits
+    g.sweeps = cfg.sweeps_per_launch
+    g.poll_deadline_us = cfg.poll_deadline_us
     return g
 
 

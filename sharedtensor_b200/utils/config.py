@@ -31,15 +31,15 @@ class Config:
     min_scale_abs: float = 0.0       # tensor mode cut-offs
     min_scale_rel: float = 2.0 ** -22
     # --- GPU engine -----------------------------------------------------------------------------
-    ring_slots: int = 8              # frames in flight per edge direction
-    frames_per_round: int = 3        # successive 1-bit frames per link and round (refinement in registers)
+    ring_slots: int = 4              # frames in flight per edge direction
+    bits: int = 8                    # bits per element of a GPU frame: 1 (sign frames, the reference's) | 2 | 4 | 8
+    sweeps_per_launch: int = 0       # passes over the tensor per launch of the round kernel (0: chosen from the size)
     engine: str = "thread"           # thread: free-running rounds on a comm stream | manual: caller drives step()
     comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
     rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
     idle_sleep_us: int = 1000        # longest engine pause while nothing moves (backs off from 10 us; doorbells end it)
     round_interval_us: int = 0       # pause after every busy round: caps the round rate (a rate limit for GPU edges)
-    use_graph: bool = True           # engine thread replays pairs of rounds as one CUDA graph
-    poll_deadline_us: int = 1000     # upper bound of every device-side wait
+    poll_deadline_us: int = 1000     # upper bound of every wait inside the round kernel
     use_multimem: bool = False       # reserved: NVLS store fan-out is not built (plain peer stores only)
     # --- TCP edges ------------------------------------------------------------------------------
     max_frames_per_s: float = 0.0    # rate cap per edge (README.md:31 of the reference lists this as a TODO)
@@ -93,8 +93,12 @@ class Config:
             raise ValueError("rel_bits must be in 1..60")
         if self.use_multimem:
             raise ValueError("use_multimem: the NVLS store path is not built; leave it False")
-        if not 1 <= self.frames_per_round <= 3:
-            raise ValueError("frames_per_round must be in 1..3")
+        if self.bits not in (1, 2, 4, 8):
+            raise ValueError("bits must be 1, 2, 4 or 8")
+        if not 0 <= self.sweeps_per_launch <= 64:
+            raise ValueError("sweeps_per_launch must be in 0..64")
+        if not 1 <= self.poll_deadline_us <= 2_000_000:
+            raise ValueError("poll_deadline_us must be in 1..2000000")
         if self.rounds_in_flight < 1:
             raise ValueError("rounds_in_flight must be >= 1")
 

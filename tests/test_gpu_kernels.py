@@ -25,9 +25,10 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, frames=1):
+def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, bits=8, deadline_us=1000):
     cfg = cu.GpuConfig()
-    cfg.frames_per_round = frames
+    cfg.bits = bits
+    cfg.poll_deadline_us = deadline_us
     cfg.block = block
     cfg.ring_slots = slots
     cfg.shareable = shareable
@@ -97,12 +98,17 @@ def test_atomic_add_kernels(cu):
     v = torch.randn(n, device="cuda")
     d = torch.randn(n, device="cuda")
     ref = v + d
-    cu.add(v.data_ptr(), d.data_ptr(), n, 0, 0, True, _stream())
+    cu.add(v.data_ptr(), d.data_ptr(), n, True, _stream())
     torch.cuda.synchronize()
     assert torch.equal(v, ref)
     a, b = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
     ref = v + (a - b)
-    cu.sub_add(v.data_ptr(), a.data_ptr(), b.data_ptr(), n, 0, 0, True, _stream())
+    cu.sub_add(v.data_ptr(), a.data_ptr(), b.data_ptr(), n, True, _stream())
+    torch.cuda.synchronize()
+    assert torch.equal(v, ref)
+    g16 = torch.randn(n, device="cuda").to(torch.bfloat16)
+    ref = v + (-0.5) * g16.float()
+    cu.add_scaled_bf16(v.data_ptr(), g16.data_ptr(), -0.5, n, True, _stream())
     torch.cuda.synchronize()
     assert torch.equal(v, ref)
 
@@ -153,25 +159,68 @@ def test_sample_sqerr_and_delay(cu):
 
 # --------------------------------------------------------------------------------------------------
 class Oracle:
-    """Host model of a replica: values, one mirror per link, frames exchanged as (words, scales)."""
+    """Host model of a replica: values, one mirror per link, frames exchanged as (codes or words, scales)."""
 
-    def __init__(self, core, n, block, n_links, min_exp=-60, rel_bits=22):
-        self.core, self.n, self.block = core, n, block
+    def __init__(self, core, n, block, n_links, bits=8, min_exp=-60, rel_bits=22):
+        self.core, self.n, self.block, self.bits = core, n, block, bits
         self.v = torch.zeros(n)
         self.k = [torch.zeros(n) for _ in range(n_links)]
         self.min_exp, self.rel_bits = min_exp, rel_bits
 
     def encode(self, link):
-        words = torch.zeros(self.core.block_words(self.n), dtype=torch.int32)
         scales = torch.zeros(self.core.block_scales(self.n, self.block), dtype=torch.uint8)
-        self.core.encode_block(self.v.data_ptr(), self.k[link].data_ptr(), self.n, self.block, self.min_exp, self.rel_bits,
-                               words.data_ptr(), scales.data_ptr())
-        return words, scales
+        if self.bits == 1:
+            codes = torch.zeros(self.core.block_words(self.n), dtype=torch.int32)
+            self.core.encode_block(self.v.data_ptr(), self.k[link].data_ptr(), self.n, self.block, self.min_exp, self.rel_bits,
+                                   codes.data_ptr(), scales.data_ptr())
+        else:
+            codes = torch.zeros(self.n, dtype=torch.uint8)
+            self.core.encode_block_int(self.v.data_ptr(), self.k[link].data_ptr(), self.n, self.block, self.min_exp, self.rel_bits,
+                                       self.bits, codes.data_ptr(), scales.data_ptr())
+        return codes, scales
 
-    def decode(self, link, frame):
-        words, scales = frame
-        self.core.decode_block_add(words.data_ptr(), scales.data_ptr(), self.n, self.block, self.v.data_ptr(),
-                                   self.k[link].data_ptr())
+    def steps(self, frame):
+        codes, scales = frame
+        out = torch.zeros(self.n)
+        if self.bits == 1:
+            self.core.block_sign_steps(codes.data_ptr(), scales.data_ptr(), self.n, self.block, out.data_ptr())
+        else:
+            self.core.block_int_steps(codes.data_ptr(), scales.data_ptr(), self.n, self.block, self.bits, out.data_ptr())
+        return out
+
+    def decode(self, link, frames):
+        """What one sweep does with the frames it finds on a link: their steps are added up first (in order), the sum
+        then goes into the values and into the link's mirror."""
+        if not isinstance(frames, list):
+            frames = [frames]
+        if not frames:
+            return
+        acc = torch.zeros(self.n)
+        for fr in frames:
+            acc = acc + self.steps(fr)
+        self.v += acc
+        self.k[link] += acc
+
+    def payload_of_tile(self, frame, tile):
+        """(code words as the ring slot holds them, scale bytes, mask of 32-element chunks whose block is not silent)."""
+        codes, scales = frame
+        lo, hi = tile * 4096, min((tile + 1) * 4096, self.n)
+        if self.bits == 1:
+            unpacked = torch.zeros(4096, dtype=torch.uint8)
+            w = codes[lo // 32:(hi + 31) // 32].to(torch.int64) & 0xFFFFFFFF
+            bits = ((w[:, None] >> torch.arange(32)) & 1).reshape(-1).to(torch.uint8)
+            unpacked[:bits.numel()] = bits
+        else:
+            unpacked = torch.full((4096,), 1 << (self.bits - 1), dtype=torch.uint8)
+            unpacked[:hi - lo] = codes[lo:hi]
+        words = torch.zeros(self.bits * 128, dtype=torch.int32)
+        self.core.pack_tile_codes(unpacked.data_ptr(), self.bits, words.data_ptr())
+        spt = 4096 // self.block
+        sc = torch.zeros(spt, dtype=torch.uint8)
+        mine = scales[tile * spt:(tile + 1) * spt]
+        sc[:mine.numel()] = mine
+        loud = (sc != 0).repeat_interleave(self.block // 32)
+        return words, sc, loud
 
 
 def _state(cu, rep, link):
@@ -183,33 +232,63 @@ def _state(cu, rep, link):
     return v.cpu(), k.cpu()
 
 
-@pytest.mark.parametrize("block", [32, 64, 128, 256, 1024, 4096])
-@pytest.mark.parametrize("n", [1, 31, 4096, 4097, 10000, 3 * 4096 + 77])
-def test_round_bit_exact_two_replicas(cu, core, n, block):
-    """A -> B streaming of A's state plus updates on both sides, compared bit for bit with the host codec."""
-    torch.manual_seed(n * 13 + block)
-    A, B = _replica(cu, n, block), _replica(cu, n, block)
+def _dev_bytes(ptr, nbytes):
+    out = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    _native.cuda().memcpy_d2d(out.data_ptr(), ptr, nbytes)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def _cases():
+    out = []
+    for bits in (1, 2, 4, 8):
+        for block in ((32, 64, 128, 256, 1024, 2048, 4096) if bits in (1, 8) else (32, 256, 4096)):
+            for n in (1, 31, 4096, 4097, 10000, 3 * 4096 + 77):
+                out.append((bits, block, n))
+    return out
+
+
+@pytest.mark.parametrize("bits,block,n", _cases())
+def test_round_bit_exact_two_replicas(cu, core, bits, block, n):
+    """A -> B streaming of A's state plus updates on both sides, compared bit for bit with the host codec: values,
+    mirrors, and the code words and scale bytes in the ring slots."""
+    torch.manual_seed(n * 13 + block + bits)
+    A, B = _replica(cu, n, block, bits=bits), _replica(cu, n, block, bits=bits)
     la, lb = connect_local(A, B)
-    oa, ob = Oracle(core, n, block, 1), Oracle(core, n, block, 1)
+    oa, ob = Oracle(core, n, block, 1, bits), Oracle(core, n, block, 1, bits)
     init = torch.randn(n) * torch.logspace(-2, 1, n)
     oa.v = init.clone()
     A.load_values(init.cuda().data_ptr(), _stream())
-    for it in range(24):
-        if it in (5, 11):
+    lay = B.edge_layout()
+    pb = bits * 512 + max(16, 4096 // block)
+    slots = 4
+    sent_a = 0  # frames A has produced so far
+    rounds = 24 if bits == 1 else 10
+    for it in range(rounds):
+        if it in (3, 7):
             da, db = torch.randn(n) * 1e-2, torch.randn(n) * 1e-1
             oa.v += da
             ob.v += db
             A.add(da.cuda().data_ptr(), _stream())
             B.add(db.cuda().data_ptr(), _stream())
-        # A's round: receives B's previous frame (if any), sends; then B's round
+            torch.cuda.synchronize()
+        # A's sweep: receives B's previous frame (if any), sends; then B's sweep
         A.round()
         A.sync()
-        B.round()
-        B.sync()
-        # host model, same order: A decodes what B sent last time, encodes; B decodes, encodes
+        # host model, same order: A decodes what B sent last time, encodes
         if it > 0:
             oa.decode(0, frame_b)
         frame_a = oa.encode(0)
+        words, sc, loud = oa.payload_of_tile(frame_a, 0)
+        if bool(sc.any()):
+            # what A just pushed into B's ring: tile 0 of the frame, in the slot the tile's sequence number selects
+            raw = _dev_bytes(B.edge_block_ptr(0) + lay["off_payload"] + ((sent_a % slots) * B.tiles() + 0) * pb, pb)
+            got_words = raw[:bits * 512].view(torch.int32).reshape(128, bits)
+            assert torch.equal(got_words[loud], words.reshape(128, bits)[loud]), f"code words differ in round {it}"
+            assert torch.equal(raw[bits * 512:bits * 512 + sc.numel()], sc), f"scale bytes differ in round {it}"
+            sent_a += 1
+        B.round()
+        B.sync()
         ob.decode(0, frame_a)
         frame_b = ob.encode(0)
         va, ka = _state(cu, A, la)
@@ -220,53 +299,41 @@ def test_round_bit_exact_two_replicas(cu, core, n, block):
         assert torch.equal(kb, ob.k[0]), f"B mirror differs in round {it}"
     st = A.status()
     assert st[5] == 0, "no error bits"
+    assert A.check_guards() == 0 and B.check_guards() == 0
 
 
-@pytest.mark.parametrize("frames", [2, 3])
-@pytest.mark.parametrize("block,n", [(32, 3 * 4096 + 77), (256, 4097), (4096, 2 * 4096)])
-def test_round_multi_frame_bit_exact(cu, core, frames, block, n):
-    """Several successive 1-bit frames per round (refinement while the tile is in registers): same stream as
-    encoding that many frames one after the other on the host."""
-    torch.manual_seed(n + frames)
-    A, B = _replica(cu, n, block, 8, frames=frames), _replica(cu, n, block, 8, frames=frames)
-    la, lb = connect_local(A, B)
-    oa, ob = Oracle(core, n, block, 1), Oracle(core, n, block, 1)
-    init = torch.randn(n) * torch.logspace(-2, 1, n)
-    oa.v = init.clone()
-    A.load_values(init.cuda().data_ptr(), _stream())
-    frames_b = []
-    for it in range(12):
-        if it == 5:
-            da, db = torch.randn(n) * 1e-2, torch.randn(n) * 1e-1
-            oa.v += da
-            ob.v += db
-            A.add(da.cuda().data_ptr(), _stream())
-            B.add(db.cuda().data_ptr(), _stream())
-        A.round()
-        A.sync()
-        B.round()
-        B.sync()
-        for fr in frames_b:
-            oa.decode(0, fr)
-        frames_a = [oa.encode(0) for _ in range(frames)]
-        for fr in frames_a:
-            ob.decode(0, fr)
-        frames_b = [ob.encode(0) for _ in range(frames)]
-        va, ka = _state(cu, A, la)
-        vb, kb = _state(cu, B, lb)
-        assert torch.equal(va, oa.v) and torch.equal(ka, oa.k[0]), f"A differs in round {it}"
-        assert torch.equal(vb, ob.v) and torch.equal(kb, ob.k[0]), f"B differs in round {it}"
-    assert A.status()[5] == 0
+@pytest.mark.parametrize("bits", [1, 8])
+def test_one_frame_of_eight_bits_delivers_an_update(cu, bits):
+    """A fresh N(0,1) update: relative error after one 8-bit frame is under one percent; sign frames need many."""
+    n = 64 * 4096
+    torch.manual_seed(2)
+    A, B = _replica(cu, n, bits=bits), _replica(cu, n, bits=bits)
+    connect_local(A, B)
+    d = torch.randn(n, device="cuda")
+    A.add(d.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    A.round()
+    A.sync()
+    B.round()
+    B.sync()
+    out = torch.empty(n, device="cuda")
+    B.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    rel = ((out - d).norm() / d.norm()).item()
+    if bits == 8:
+        assert rel < 1e-2, rel
+    else:
+        assert rel > 0.3, rel
 
 
 def test_several_frames_per_round_and_ring_full(cu, core):
-    """The sender runs ahead: the receiver takes up to three frames per round in order; once the ring is full the
+    """The sender runs ahead: the receiver takes up to three frames per sweep in order; once the ring is full the
     sender skips (nothing is lost, the residual simply stays) and counts it."""
-    n, block, slots = 2 * 4096 + 5, 32, 4
+    n, block, slots, bits = 2 * 4096 + 5, 32, 4, 1
     torch.manual_seed(7)
-    A, B = _replica(cu, n, block, slots), _replica(cu, n, block, slots)
+    A, B = _replica(cu, n, block, slots, bits=bits), _replica(cu, n, block, slots, bits=bits)
     la, lb = connect_local(A, B)
-    oa, ob = Oracle(core, n, block, 1), Oracle(core, n, block, 1)
+    oa, ob = Oracle(core, n, block, 1, bits), Oracle(core, n, block, 1, bits)
     init = torch.randn(n)
     oa.v = init.clone()
     A.load_values(init.cuda().data_ptr(), _stream())
@@ -282,13 +349,12 @@ def test_several_frames_per_round_and_ring_full(cu, core):
     names = cu.status_names()
     assert st[names.index("blocked_no_credit")] == 3 * A.tiles()
     assert st[names.index("frames_sent")] == slots * A.tiles()
-    # B drains up to three frames per round, in order
+    # B drains up to three frames per sweep, in order
     taken = 0
     for take in (3, 1):
         B.round(True, False)  # receiver-only rounds
         B.sync()
-        for fr in frames[taken:taken + take]:
-            ob.decode(0, fr)
+        ob.decode(0, frames[taken:taken + take])
         taken += take
         vb, kb = _state(cu, B, lb)
         assert torch.equal(vb, ob.v) and torch.equal(kb, ob.k[0])
@@ -298,6 +364,83 @@ def test_several_frames_per_round_and_ring_full(cu, core):
     oa.encode(0)
     va, ka = _state(cu, A, la)
     assert torch.equal(ka, oa.k[0])
+    assert A.check_guards() == 0 and B.check_guards() == 0
+
+
+def test_updates_commute_with_rounds(cu):
+    """One stream adds 200 deltas while the engine threads run rounds: both replicas end at the exact fp32 sum
+    (every delta is a multiple of 2^-10 and all partial sums are exactly representable, so any order gives it)."""
+    n = 40 * 4096 + 11
+    torch.manual_seed(9)
+    A, B = _replica(cu, n), _replica(cu, n)
+    connect_local(A, B)
+    init = torch.randint(-1000, 1000, (n,), device="cuda").float() / 16.0
+    A.load_values(init.data_ptr(), _stream())
+    A.start_engine()
+    B.start_engine()
+    side = torch.cuda.Stream()
+    deltas = [torch.randint(-64, 64, (n,), device="cuda").float() / 1024.0 for _ in range(8)]
+    expect = init.clone()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for i in range(200):
+            (A if i % 2 == 0 else B).add(deltas[i % 8].data_ptr(), side.cuda_stream)
+    for i in range(200):
+        expect += deltas[i % 8]
+    side.synchronize()
+    import time
+
+    out = torch.empty(n, device="cuda")
+    ok = False
+    deadline = time.time() + 20
+    while time.time() < deadline and not ok:
+        ok = True
+        for r in (A, B):
+            r.snapshot(out.data_ptr(), _stream())
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(out, expect)
+        time.sleep(0.01)
+    A.stop_engine()
+    B.stop_engine()
+    assert ok, float((out - expect).abs().max())
+    assert A.status()[5] == 0 and B.status()[5] == 0
+    assert A.check_guards() == 0 and B.check_guards() == 0
+
+
+def test_bounded_wait_runs_out_and_the_replica_recovers(cu):
+    """The copy barrier of one tile is told to expect more bytes than are copied: the group that owns the tile gives
+    up after the configured limit, stores nothing of that tile, reports it, and the next ordinary round converges."""
+    n = 2 * 4096
+    torch.manual_seed(3)
+    A, B = _replica(cu, n, deadline_us=200), _replica(cu, n, deadline_us=200)
+    la, lb = connect_local(A, B)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    A.set_test_stall_tile(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cs = torch.cuda.ExternalStream(A.comm_stream())
+    e0.record(cs)
+    A.round()
+    e1.record(cs)
+    A.sync()
+    assert e0.elapsed_time(e1) < 50.0, "the kernel returned"
+    names = cu.status_names()
+    st = A.status()
+    assert st[names.index("wait_timeouts")] >= 1
+    assert st[names.index("errors")] & 1
+    k = _dev_view(A.mirror_ptr(la), n)
+    assert float(k[4096:].abs().max()) == 0.0, "nothing of the stalled tile was stored"
+    A.set_test_stall_tile(-1)
+    out = torch.empty(n, device="cuda")
+    for _ in range(6):
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+    B.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert ((out - init).norm() / init.norm()).item() < 1e-5
+    assert A.check_guards() == 0 and B.check_guards() == 0
 
 
 def test_chain_forwarding_converges_to_the_sum(cu):
@@ -311,7 +454,7 @@ def test_chain_forwarding_converges_to_the_sum(cu):
     reps[0].load_values(init.data_ptr(), _stream())
     # late-join emulation: B and C start from zero and are streamed the state
     expect = init.clone()
-    for it in range(150):  # the 1-bit stream removes ~16 % of the outstanding error per round and hop
+    for it in range(60):
         if it in (10, 20, 30):
             for i, r in enumerate(reps):
                 d = torch.randn(n, device="cuda") * 1e-2 * (i + 1)
@@ -349,7 +492,7 @@ def test_mesh_group_no_forwarding(cu):
         r.load_values(init.data_ptr(), _stream())
         r.copy_mirror_from_values(0)
     expect = init.clone()
-    for it in range(110):
+    for it in range(40):
         if it in (0, 7, 19):
             for i, r in enumerate(reps):
                 d = torch.randn(n, device="cuda") * 1e-2 * (i + 1)
@@ -418,7 +561,7 @@ def test_trace_ring_records_rounds(cu):
     recs = [st[cu.STATUS_WORDS + i * cu.TRACE_WORDS: cu.STATUS_WORDS + (i + 1) * cu.TRACE_WORDS] for i in range(5)]
     assert [r[1] for r in recs] == [0, 1, 2, 3, 4], "round numbers"
     assert all(r[0] > 0 for r in recs) and recs[4][0] > recs[0][0], "GPU clock stamps increase"
-    assert recs[0][2] == A.tiles()
+    assert recs[0][2] >= 1, "tiles handled by the recording group"
 
 
 def test_vmm_blocks_when_available(cu):
