@@ -6,7 +6,7 @@ the client side: it spawns this file with a stack limit large enough for the ref
 frame buffers, which live on thread stacks (src/sharedtensor.c:118, 144).
 
 Operations: create, add (explicit values), add_seeded (torch.randn with a seed), pool (pre-generate
-seeded deltas), add_pool, copy (all values), sample (strided subset of the values), quit.
+seeded deltas), add_pool, copy (all values), sample (strided subset of the values), digest (two numbers), quit.
 """
 from __future__ import annotations
 
@@ -91,6 +91,11 @@ def _serve() -> None:
                 reply(ok=True, count=s.numel(), copy_seconds=t1 - t0)
             else:
                 reply(ok=True, values=s.tolist(), copy_seconds=t1 - t0)
+        elif op == "digest":
+            # a 16-byte result of the replica's state, through the reference's only read call
+            lib.ref_copyToTensor(z, buf.data_ptr(), n)
+            s = buf[:: int(req["stride"])]
+            reply(ok=True, digest=[float(s.double().sum()), float(s.numel())], seconds=time.perf_counter() - t0)
         elif op == "quit":
             reply(ok=True)
             out.flush()

@@ -73,7 +73,7 @@ def _compile_cpp(src: Path, obj: Path, verbose: bool, extra: list[str] | None = 
 def _compile_cu(src: Path, obj: Path, verbose: bool, ptxas_v: bool) -> None:
     cmd = [NVCC, "-std=c++17", "-O3", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden",
            "--fmad=false" if src.name in ("round.cu",) else "--fmad=true",
-           *_includes(), "-c", str(src), "-o", str(obj)]
+           *os.environ.get("ST_NVCC_FLAGS", "").split(), *_includes(), "-c", str(src), "-o", str(obj)]
     if ptxas_v:
         cmd.insert(1, "-Xptxas=-v")
     _run(cmd, verbose or ptxas_v)

@@ -70,6 +70,13 @@ PYBIND11_MODULE(_cuda, m) {
   m.def("sample_sqerr", [](uintptr_t a, int64_t stride, uintptr_t b, int64_t count, uintptr_t out, uintptr_t s) {
     ck(launch_sample_sqerr(ptr<float>(a), stride, ptr<float>(b), count, ptr<double>(out), strm(s)), "sample_sqerr");
   });
+  m.def("probe_converged", [](uintptr_t a, int64_t stride, uintptr_t b, int64_t count, double threshold, uintptr_t scratch, uintptr_t stamp,
+                              uintptr_t last_err, uintptr_t s) {
+    ck(launch_probe_converged(ptr<float>(a), stride, ptr<float>(b), count, threshold, ptr<double>(scratch), ptr<uint64_t>(stamp),
+                              ptr<double>(last_err), strm(s)),
+       "probe_converged");
+  });
+  m.def("stamp", [](uintptr_t out, uintptr_t s) { ck(launch_stamp(ptr<uint64_t>(out), strm(s)), "stamp"); });
   m.def("delay", [](uint64_t ns, uintptr_t s) { ck(launch_delay(ns, strm(s)), "delay"); });
   m.def("tensor_maxabs", [](uintptr_t v, uintptr_t k, int64_t n, uintptr_t out2, uintptr_t s) {
     ck(launch_tensor_maxabs(ptr<float>(v), ptr<float>(k), n, ptr<uint32_t>(out2), strm(s)), "tensor_maxabs");
@@ -95,7 +102,11 @@ PYBIND11_MODULE(_cuda, m) {
       .def_readwrite("round_interval_us", &GpuConfig::round_interval_us)
       .def_readwrite("bits", &GpuConfig::bits)
       .def_readwrite("sweeps", &GpuConfig::sweeps)
-      .def_readwrite("poll_deadline_us", &GpuConfig::poll_deadline_us);
+      .def_readwrite("poll_deadline_us", &GpuConfig::poll_deadline_us)
+      .def_readwrite("shape", &GpuConfig::shape)
+      .def_readwrite("yield_to_updates", &GpuConfig::yield_to_updates)
+      .def_readwrite("comm_high_priority", &GpuConfig::comm_high_priority)
+      .def_readwrite("chunk_tiles", &GpuConfig::chunk_tiles);
 
   py::class_<GpuReplica>(m, "GpuReplica")
       .def(py::init<int, int64_t, const GpuConfig&>())
@@ -136,6 +147,7 @@ PYBIND11_MODULE(_cuda, m) {
       .def("set_test_stall_tile", &GpuReplica::set_test_stall_tile)
       .def("check_guards", [](GpuReplica& r) { py::gil_scoped_release rel; return r.check_guards(); })
       .def("bits", &GpuReplica::bits)
+      .def("debug_crumbs", &GpuReplica::debug_crumbs)
       .def("sync", [](GpuReplica& r) { py::gil_scoped_release rel; r.sync(); })
       .def("start_engine", &GpuReplica::start_engine)
       .def("stop_engine", [](GpuReplica& r) { py::gil_scoped_release rel; r.stop_engine(); })

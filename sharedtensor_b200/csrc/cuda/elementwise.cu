@@ -241,6 +241,11 @@ __global__ void fill_state_kernel(uint32_t* s, int n, uint32_t v) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) s[i] = v;
 }
+__global__ void set_word_kernel(uint32_t* w, uint32_t v) { *w = v; }
+int launch_set_word(uint32_t* word, uint32_t value, void* stream) {
+  set_word_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(word, value);
+  return int(cudaGetLastError());
+}
 int launch_fill_state(uint32_t* tile_state, int n_tiles, uint32_t value, void* stream) {
   fill_state_kernel<<<(n_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tile_state, n_tiles, value);
   return int(cudaGetLastError());
@@ -373,6 +378,59 @@ __global__ void __launch_bounds__(256) sample_sqerr_kernel(const float* __restri
 }
 int launch_sample_sqerr(const float* a, int64_t stride, const float* b, int64_t count, double* out, void* stream) {
   sample_sqerr_kernel<<<ew_blocks(count, 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, stride, b, count, out);
+  return int(cudaGetLastError());
+}
+
+// Convergence probe with a device time stamp: the sampled squared error of `a` against `b`, and when it is at or
+// below `threshold` for the first time, the GPU's clock into *stamp (left alone once it is non-zero).  scratch:
+// one double (the running sum, left at zero for the next launch) and one counter word behind it.
+__global__ void __launch_bounds__(256) probe_converged_kernel(const float* __restrict__ a, int64_t stride_a, const float* __restrict__ b,
+                                                              int64_t count, double threshold, double* __restrict__ scratch,
+                                                              unsigned long long* __restrict__ stamp, double* __restrict__ last_err) {
+  double acc = 0.0;
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < count; i += int64_t(gridDim.x) * 256) {
+    float d = a[i * stride_a] - b[i];
+    acc += double(d) * double(d);
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ double part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < 8; w++) t += part[w];
+    atomicAdd(scratch, t);
+    __threadfence();
+    unsigned int* counter = reinterpret_cast<unsigned int*>(scratch + 1);
+    if (atomicAdd(counter, 1u) == gridDim.x - 1) {  // the last block: every partial sum is in
+      const double total = atomicAdd(scratch, 0.0);
+      *last_err = total;
+      if (total <= threshold && *stamp == 0ull) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        *stamp = now;
+      }
+      *scratch = 0.0;
+      *counter = 0u;
+      __threadfence();
+    }
+  }
+}
+int launch_probe_converged(const float* a, int64_t stride, const float* b, int64_t count, double threshold, double* scratch,
+                           uint64_t* stamp, double* last_err, void* stream) {
+  probe_converged_kernel<<<ew_blocks(count, 2), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, stride, b, count, threshold, scratch, reinterpret_cast<unsigned long long*>(stamp), last_err);
+  return int(cudaGetLastError());
+}
+// The GPU's clock into *out: launched behind an update it marks the moment the update had landed; launched alone and
+// timed from the host it relates the GPU's clock to the host's.
+__global__ void stamp_kernel(unsigned long long* out) {
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  *out = now;
+}
+int launch_stamp(uint64_t* out, void* stream) {
+  stamp_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<unsigned long long*>(out));
   return int(cudaGetLastError());
 }
 

@@ -6,6 +6,7 @@
 
 #include <chrono>
 
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 
@@ -60,7 +61,11 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
   cudaStream_t s;
-  check(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi), "cudaStreamCreate");
+  // The comm stream runs at the priority of ordinary streams unless asked otherwise.  A round kernel that has
+  // given up its SMs for a waiting update is relaunched at once; at a higher priority those relaunches would be
+  // scheduled ahead of the update for ever, so the two options exclude each other.
+  if (cfg_.comm_high_priority) cfg_.yield_to_updates = false;
+  check(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, cfg_.comm_high_priority ? hi : lo), "cudaStreamCreate");
   comm_ = s;
 
   std::string err;
@@ -76,6 +81,8 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   check(cudaMalloc(reinterpret_cast<void**>(&tile_state_), size_t(n_tiles_) * 4), "cudaMalloc tile_state");
   check(cudaMalloc(reinterpret_cast<void**>(&status_), kDsTotalWords * 8), "cudaMalloc status");
   check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), (kDsTotalWords + 16) * 8), "cudaMallocHost status");
+  check(cudaMalloc(reinterpret_cast<void**>(&yield_flag_), 4), "cudaMalloc yield flag");
+  check(cudaMemsetAsync(yield_flag_, 0, 4, s), "memset");
   check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
   check(cudaMemsetAsync(status_, 0, kDsTotalWords * 8, s), "memset");
   std::memset(status_host_, 0, (kDsTotalWords + 16) * 8);
@@ -91,7 +98,11 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   }
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_);
+  sms_ = sms;
   ctas_ = cfg.comm_ctas > 0 ? cfg.comm_ctas : sms;
+  if (const char* e = ::getenv("SHAREDTENSOR_ROUND_SHAPE")) cfg_.shape = std::atoi(e);
+  if (const char* e = ::getenv("SHAREDTENSOR_CHUNK_TILES")) cfg_.chunk_tiles = std::atoi(e);
+  if (cfg_.shape < 0 || cfg_.shape > 1) throw std::invalid_argument("round kernel shape must be 0 or 1");
 
   params_.values = values();
   params_.n = n_;
@@ -108,6 +119,18 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   params_.sweeps = 1;
   params_.wait_ns = uint32_t(cfg.poll_deadline_us < 1 ? 1 : (cfg.poll_deadline_us > 2000000 ? 2000000 : cfg.poll_deadline_us)) * 1000u;
   params_.stall_tile = -1;
+  params_.yield_flag = cfg_.yield_to_updates ? yield_flag_ : nullptr;
+  params_.dbg = nullptr;
+  if (::getenv("SHAREDTENSOR_DEBUG_CRUMBS")) {
+    void* h = nullptr;
+    if (cudaHostAlloc(&h, 4096 * 8 * 4, cudaHostAllocMapped) == cudaSuccess) {
+      std::memset(h, 0, 4096 * 8 * 4);
+      dbg_host_ = static_cast<uint32_t*>(h);
+      void* d = nullptr;
+      cudaHostGetDevicePointer(&d, h, 0);
+      params_.dbg = static_cast<uint32_t*>(d);
+    }
+  }
   check(cudaDeviceSynchronize(), "init");
 }
 
@@ -124,6 +147,7 @@ GpuReplica::~GpuReplica() {
   vmm_free(&values_);
   cudaFree(tile_state_);
   cudaFree(status_);
+  cudaFree(yield_flag_);
   if (status_host_) cudaFreeHost(status_host_);
   if (tcp_words_dev_) cudaFree(tcp_words_dev_);
   if (tcp_stat_dev_) cudaFree(tcp_stat_dev_);
@@ -378,11 +402,21 @@ void GpuReplica::load_values(const float* src, void* user_stream) {
   local_update();
 }
 
+// Around an update, in the order of the caller's stream: a word that asks the round kernel to give up its SMs (it
+// holds all of them, for as long as a pass over the tensor takes), then the update, then the change marks, then the
+// word is cleared.  The update itself never waits for a round; it only wants somewhere to run.
+void GpuReplica::ask_for_sms(void* user_stream, bool on) {
+  if (!cfg_.yield_to_updates) return;
+  if (!stream_write_u32(user_stream, yield_flag_, on ? 1u : 0u)) check(launch_set_word(yield_flag_, on ? 1u : 0u, user_stream), "set_word");
+}
+
 void GpuReplica::add(const float* delta, void* user_stream) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
+  ask_for_sms(user_stream, true);
   check(launch_add(values(), delta, n_, 1, user_stream), "add kernel");
   check(launch_fill_state(tile_state_, n_tiles_, 1u, user_stream), "fill_state");  // marks after the data, in stream order
+  ask_for_sms(user_stream, false);
   epoch_++;
   launches_ += 2;
   local_update();
@@ -391,8 +425,10 @@ void GpuReplica::add(const float* delta, void* user_stream) {
 void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
+  ask_for_sms(user_stream, true);
   check(launch_sub_add(values(), neu, old, n_, 1, user_stream), "sub_add kernel");
   check(launch_fill_state(tile_state_, n_tiles_, 1u, user_stream), "fill_state");
+  ask_for_sms(user_stream, false);
   epoch_++;
   launches_ += 2;
   local_update();
@@ -401,8 +437,10 @@ void GpuReplica::sub_add(const float* neu, const float* old, void* user_stream) 
 void GpuReplica::add_scaled_bf16(const void* g, float alpha, void* user_stream) {
   DeviceGuard gd(device_);
   std::lock_guard<std::mutex> gate(gate_mu_);
+  ask_for_sms(user_stream, true);
   check(launch_add_scaled_bf16(values(), g, alpha, n_, 1, user_stream), "add_scaled_bf16 kernel");
   check(launch_fill_state(tile_state_, n_tiles_, 1u, user_stream), "fill_state");
+  ask_for_sms(user_stream, false);
   epoch_++;
   launches_ += 2;
   local_update();
@@ -444,12 +482,32 @@ void GpuReplica::push_snapshot(int link, float* remote_values) {
   check(cudaStreamSynchronize(S(comm_)), "snapshot_join");
 }
 
+// How a launch covers the tensor: the grid, and how many consecutive tiles a group owns (0: every n-th tile).
+void GpuReplica::grid_for_launch(int* grid, int* chunk, int* tiles_per_group) const {
+  const int groups_per_cta = round_shape_groups(cfg_.shape);
+  if (cfg_.chunk_tiles > 0) {
+    // many short-lived CTAs: a group takes a run of `chunk_tiles` consecutive tiles and leaves, so that kernels of
+    // other streams get SMs between two CTAs of a long launch
+    const int t = cfg_.chunk_tiles;
+    *chunk = t;
+    *grid = (n_tiles_ + t * groups_per_cta - 1) / (t * groups_per_cta);
+    *tiles_per_group = t;
+  } else {
+    // one CTA per SM for the whole launch, a group walks through every n-th tile
+    const int needed = (n_tiles_ + groups_per_cta - 1) / groups_per_cta;
+    const int g = ctas_ < needed ? ctas_ : needed;
+    *chunk = 0;
+    *grid = g < 1 ? 1 : g;
+    *tiles_per_group = (n_tiles_ + *grid * groups_per_cta - 1) / (*grid * groups_per_cta);
+  }
+}
+
 int GpuReplica::auto_sweeps() const {
   if (cfg_.sweeps > 0) return cfg_.sweeps > 64 ? 64 : cfg_.sweeps;
   // Small tensors: a pass takes a few microseconds, so one launch makes several and the host's launch latency is
   // paid once per batch.  Large tensors: a pass is long enough by itself.
-  const int groups = ctas_ * 3;
-  const int per_group = (n_tiles_ + groups - 1) / groups;
+  int grid, chunk, per_group;
+  grid_for_launch(&grid, &chunk, &per_group);
   int sw = 32 / (per_group < 1 ? 1 : per_group);
   return sw < 1 ? 1 : (sw > 16 ? 16 : sw);
 }
@@ -460,7 +518,10 @@ void GpuReplica::launch(bool do_rx, bool do_tx, int sweeps) {
   params_.do_rx = do_rx ? 1 : 0;
   params_.do_tx = do_tx ? 1 : 0;
   params_.sweeps = sweeps < 1 ? 1 : sweeps;
-  check(launch_round(params_, ctas_, comm_), "round kernel");
+  int grid, chunk, per_group;
+  grid_for_launch(&grid, &chunk, &per_group);
+  params_.chunk = chunk;
+  check(launch_round(params_, cfg_.shape, grid, comm_), "round kernel");
   last_parity_ = params_.parity;
   launches_ += 1;
   epoch_++;
@@ -576,6 +637,12 @@ std::vector<uint64_t> GpuReplica::status() {
   out[kStPendingTiles] = lw[kDlPending];
   out[kStWaitTimeouts] = dev[kDsWaitTimeouts];
   std::memcpy(out.data() + kStWords, dev.data() + kDsTrace, size_t(kTraceEntries) * kTraceWords * 8);
+  return out;
+}
+
+std::vector<uint32_t> GpuReplica::debug_crumbs() const {
+  std::vector<uint32_t> out;
+  if (dbg_host_) out.assign(dbg_host_, dbg_host_ + 148 * 8);
   return out;
 }
 

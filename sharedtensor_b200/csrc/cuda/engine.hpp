@@ -41,6 +41,10 @@ struct GpuConfig {
   int bits = 8;              // bits per element of a frame: 1 (sign frames), 2, 4 or 8 (integer frames)
   int sweeps = 0;            // passes over the tensor per launch of the engine thread (0 = chosen from the tensor's size)
   int poll_deadline_us = 1000;  // upper bound of every wait inside the round kernel
+  int shape = 1;             // make-up of the round kernel's CTAs, see launch_round
+  bool yield_to_updates = true;  // a running round kernel gives up its SMs when addFromTensor has an update ready
+  bool comm_high_priority = false;  // comm stream at the highest stream priority (switches yield_to_updates off)
+  int chunk_tiles = 0;       // > 0: short-lived CTAs, a group takes this many consecutive tiles (0: one CTA per SM per launch)
 };
 
 constexpr size_t kGuardBytes = 256;  // canary before and after every mirror, edge block and the values
@@ -124,6 +128,7 @@ class GpuReplica {
   // ---- observation ----
   std::vector<uint64_t> status();      // StatusWord order, then the trace ring; synchronises the comm stream
   int bits() const { return cfg_.bits; }
+  std::vector<uint32_t> debug_crumbs() const;   // debug builds of the round kernel: its progress marks, 8 words per CTA
   uint64_t launches() const { return launches_.load(); }
   uint64_t change_epoch() const { return epoch_.load(); }  // bumped whenever values may have changed
   std::string last_error() const;
@@ -149,7 +154,9 @@ class GpuReplica {
   void publish_pending();              // under mu_
   void launch(bool do_rx, bool do_tx, int sweeps);  // under mu_
   int auto_sweeps() const;
+  void grid_for_launch(int* grid, int* chunk, int* tiles_per_group) const;
   void fill_guards(const VmmBlock& b, size_t used_bytes);
+  void ask_for_sms(void* user_stream, bool on);
   void check(int cuda_err, const char* what);
   void engine_loop();
   void order_after_user(void* user_stream);
@@ -166,6 +173,8 @@ class GpuReplica {
   std::vector<Peer> peers_;
   uint32_t* tile_state_ = nullptr;     // change mark per tile
   uint64_t* status_ = nullptr;         // DevStatus layout
+  uint32_t* yield_flag_ = nullptr;     // non-zero while an update wants the SMs the round kernel holds
+  uint32_t* dbg_host_ = nullptr;       // mapped host memory for the debug build's progress marks
   uint64_t* status_host_ = nullptr;    // pinned
   uint32_t* tcp_words_dev_ = nullptr;  // ceil(n/32) words, staging of TCP frames
   uint32_t* tcp_stat_dev_ = nullptr;   // 2 words
@@ -175,6 +184,7 @@ class GpuReplica {
   int round_no_ = 0;
   int last_parity_ = 0;                // which half of the per-launch status words the last launch used
   int ctas_ = 148;
+  int sms_ = 148;
   void* comm_ = nullptr;               // cudaStream_t
   void* ev_user_ = nullptr;            // cudaEvent_t: user stream -> comm
   void* ev_comm_ = nullptr;            // cudaEvent_t: comm -> user stream

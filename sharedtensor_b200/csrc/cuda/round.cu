@@ -1,7 +1,7 @@
 // The sync-round kernel for sm_100a (see round.h for the protocol and ../core/codec.hpp for the arithmetic).
 //
-// A CTA holds three independent groups; a group is four compute warps and one I/O warp and owns every
-// (3 * gridDim.x)-th tile of the tensor.  The two kinds of warp talk through shared memory and mbarriers only:
+// A CTA holds up to three independent groups and one publisher warp; a group is four compute warps and one I/O warp
+// and owns every n-th tile of the tensor.  The kinds of warp talk through shared memory and mbarriers only:
 //
 //   I/O warp      reads its tiles' sequence flags, credits and change marks (32 tiles at a time, one per lane),
 //                 and for every tile with something to do hands the compute warps one *step* per link: it writes
@@ -13,7 +13,10 @@
 //                 stream adds at the same moment is never overwritten), the stepped mirror, and the packed codes
 //                 and scale bytes into the ring slot of every neighbour on the link (peer stores over NVLink;
 //                 reference src/sharedtensor.c:176-177, two socket writes).  Two steps later, when those stores
-//                 have completed, it fences and publishes: sequence flags to the receivers, credits to the senders.
+//                 have completed, it hands the step to the publisher warp.
+//   publisher     one warp per CTA: takes the completed steps of all groups, executes the system-scope fence (which
+//                 costs microseconds, and would otherwise stall an I/O warp) and writes sequence flags to the
+//                 receivers and credits to the senders, one ring per lane.
 //   compute warps a thread owns 32 consecutive elements of the tile (read from shared memory through an XOR
 //                 swizzle, so no bank conflicts).  It decodes the frames that arrived (reference 106-111, 124-127)
 //                 into one accumulated step, adds it to its values and to the mirror of the link the frames came
@@ -32,16 +35,40 @@
 
 #include "round.h"
 
+#ifdef ST_ROUND_DEBUG
+// progress marks in host memory, readable while a kernel is stuck (debug builds only)
+#define ST_CRUMB(slot, code)                                                                  \
+  do {                                                                                         \
+    if (p.dbg != nullptr && lane == 0) {                                                       \
+      *reinterpret_cast<volatile uint32_t*>(p.dbg + (blockIdx.x * 8 + (slot))) = uint32_t(code); \
+    }                                                                                          \
+  } while (0)
+#else
+#define ST_CRUMB(slot, code)
+#endif
+#ifdef ST_ROUND_TIMING
+#include <cstdio>
+#define ST_T0() const long long st_t0_ = clock64()
+#define ST_ACC(var) var += clock64() - st_t0_
+#define ST_LAP(var) { const long long st_now_ = clock64(); var += st_now_ - st_lap_; st_lap_ = st_now_; }
+#else
+#define ST_T0()
+#define ST_ACC(var)
+#define ST_LAP(var)
+#endif
+
 namespace st {
 
 namespace {
 
 constexpr int kGroupThreads = 128;  // compute threads of a group: one per 32 consecutive elements of a tile
-constexpr int kGroups = 3;
-constexpr int kSlots = 2;           // staging slots per group
 constexpr int kTileBytes = kTile * 4;
-constexpr int kCtaThreads = kGroups * (kGroupThreads + 32);
-constexpr int kPubQueue = 4;
+constexpr int kPubQueue = 8;
+// Shapes of a CTA (groups x staging slots per group); the launcher picks one, see launch_round.
+//   3 x 2: one CTA per SM, 12 compute warps                (fills the SM's shared memory and registers)
+//   2 x 3: one CTA per SM,  8 compute warps, deeper staging (leaves a third of the registers to other kernels)
+// Either way a group takes every n-th tile of the tensor for the whole launch, or (RoundParams::chunk) a run of
+// consecutive tiles, in which case the grid has many short-lived CTAs and other kernels get SMs in between.
 
 // ----------------------------------------------------------------------------------------------
 // small PTX wrappers
@@ -122,6 +149,9 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float* dst_gmem, const void*
                "r"(bytes)
                : "memory");
 }
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all_but_2() { asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); }
@@ -146,26 +176,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
-// A compute warp's wait for a step.  The clock of the limit only runs once the I/O warp has armed the step (while the
-// I/O warp looks for work, or there is none, a compute warp may sit here for the whole launch); a second, generous
-// limit covers an I/O warp that never comes back.
-__device__ __forceinline__ bool wait_step(uint64_t* bar, uint32_t parity, const uint32_t* armed, uint32_t step, const uint32_t* abort,
-                                          uint64_t limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+// A compute warp's wait for the descriptor of a step.  While the I/O warp looks for work, or there is none, a compute
+// warp may sit here for the whole launch, so the limit is generous; it only covers an I/O warp that never comes back.
+__device__ __forceinline__ bool wait_armed(const uint32_t* armed, uint32_t step, const uint32_t* abort) {
+  if (ld_shared_volatile(armed) > step) return true;
   const uint64_t t_start = globaltimer_ns();
-  uint64_t t_armed = 0;
   for (uint32_t it = 0; it < (1u << 28); it++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 7) == 7) {
-      if (ld_shared_volatile(abort)) return false;
-      const uint64_t now = globaltimer_ns();
-      if (ld_shared_volatile(armed) > step) {
-        if (t_armed == 0) t_armed = now;
-        else if (now - t_armed > limit_ns) return false;
-      } else if (now - t_start > 2000ull * 1000 * 1000) {
-        return false;
-      }
-    }
+    if (ld_shared_volatile(armed) > step) return true;
+    if (ld_shared_volatile(abort)) return false;
+    if ((it & 63) == 63 && globaltimer_ns() - t_start > 2000ull * 1000 * 1000) return false;
+    __nanosleep(20);
   }
   return false;
 }
@@ -197,11 +217,11 @@ struct SmemLayout {
   int off_desc;     // StepDesc[kGroups][kSlots]
   int off_pubq;     // StepDesc[kGroups][kPubQueue]
   int off_bar;      // uint64_t[kGroups][2 * kSlots + 1]: full, done, group sync
-  int off_words;    // uint32_t[kGroups][8]: step flags per slot, armed steps, abort
+  int off_words;    // uint32_t[kGroups][16]: step flags per slot, armed steps, abort, publication counters
   int off_red;      // float[kGroups][2][8]: cross-warp partials for blocks of 2048 / 4096 elements
   int total;
 };
-__host__ __device__ inline SmemLayout smem_layout(int payload_bytes) {
+__host__ __device__ inline SmemLayout smem_layout(int payload_bytes, int kGroups, int kSlots) {
   SmemLayout m;
   m.slot_stride = 2 * kTileBytes + ((payload_bytes + 127) & ~127);
   int off = 0;
@@ -214,7 +234,7 @@ __host__ __device__ inline SmemLayout smem_layout(int payload_bytes) {
   m.off_bar = off;
   off += kGroups * (2 * kSlots + 1) * 8;
   m.off_words = off;
-  off += kGroups * 8 * 4;
+  off += kGroups * 16 * 4;
   m.off_red = off;
   off += kGroups * 2 * 8 * 4;
   m.total = (off + 127) & ~127;
@@ -404,18 +424,20 @@ __device__ __forceinline__ uint32_t max_abs_bits(const float4 (&v)[8]) {
 
 }  // namespace
 
-int round_smem_bytes(int, int payload_bytes) { return smem_layout(payload_bytes).total; }
+int round_smem_bytes(int groups, int slots, int payload_bytes) { return smem_layout(payload_bytes, groups, slots).total; }
 
 // ----------------------------------------------------------------------------------------------
 // the kernel
 // ----------------------------------------------------------------------------------------------
-template <int Q>
-__global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_constant__ RoundParams p) {
+template <int Q, int kGroups, int kSlots>
+__global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
+    round_kernel(const __grid_constant__ RoundParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const SmemLayout lay = smem_layout(p.payload_bytes);
+  const SmemLayout lay = smem_layout(p.payload_bytes, kGroups, kSlots);
   const int tid = threadIdx.x;
-  const bool is_io = tid >= kGroups * kGroupThreads;
-  const int g = is_io ? (tid - kGroups * kGroupThreads) >> 5 : tid >> 7;
+  const bool is_pub = tid >= kGroups * (kGroupThreads + 32);
+  const bool is_io = !is_pub && tid >= kGroups * kGroupThreads;
+  const int g = is_pub ? 0 : (is_io ? (tid - kGroups * kGroupThreads) >> 5 : tid >> 7);
   const int lane = tid & 31;
   uint8_t* slots = smem + lay.off_slots + size_t(g) * kSlots * lay.slot_stride;
   StepDesc* desc = reinterpret_cast<StepDesc*>(smem + lay.off_desc) + g * kSlots;
@@ -423,10 +445,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar) + g * (2 * kSlots + 1);
   uint64_t* done = full + kSlots;
   uint64_t* gsync = full + 2 * kSlots;
-  uint32_t* words = reinterpret_cast<uint32_t*>(smem + lay.off_words) + g * 8;
+  uint32_t* words = reinterpret_cast<uint32_t*>(smem + lay.off_words) + g * 16;
   uint32_t* sflags = words;          // [kSlots]
   uint32_t* armed = words + 4;       // steps armed so far
   uint32_t* abort_flag = words + 5;
+  uint32_t* pub_ready = words + 6;   // steps whose stores have completed (I/O warp -> publisher)
+  uint32_t* pub_done = words + 7;    // steps published (publisher -> I/O warp)
+  uint32_t* pub_exit = words + 8;    // the group's I/O warp has nothing more to publish
+  uint32_t* yield_seen = reinterpret_cast<uint32_t*>(smem + lay.off_words) + 9;  // group 0's word: an update is waiting
   float* s_red = reinterpret_cast<float*>(smem + lay.off_red) + g * 16;
 
   if (tid == 0) {
@@ -437,8 +463,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         mbar_init(b + kSlots + s, 4);  // done: one arrive per compute warp
       }
       mbar_init(b + 2 * kSlots, 4);    // group sync of the compute warps
-      uint32_t* wd = reinterpret_cast<uint32_t*>(smem + lay.off_words) + i * 8;
-      for (int j = 0; j < 8; j++) wd[j] = 0;
+      uint32_t* wd = reinterpret_cast<uint32_t*>(smem + lay.off_words) + i * 16;
+      for (int j = 0; j < 16; j++) wd[j] = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -450,6 +476,70 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
   const int tpb = p.log2_block - 5;  // log2(threads per block of the quantiser)
   const uint64_t limit_ns = p.wait_ns;
   uint64_t* const launch_words = p.status + (p.parity ? kDsLaunch1 : kDsLaunch0);
+
+  if (is_pub) {
+    // =========================================================================================
+    // publisher warp: sequence flags and credits of the steps whose stores have completed, for every group of the
+    // CTA.  Lane r serves out-ring r and in-ring r.
+    // =========================================================================================
+    uint32_t published[kGroups];
+#pragma unroll
+    for (int i = 0; i < kGroups; i++) published[i] = 0;
+    const uint64_t t_start = globaltimer_ns();
+    for (uint32_t it = 0;; it++) {
+      ST_CRUMB(3, 20);
+      // An update that is waiting for SMs: the I/O warps read this copy of the flag before they hand out a tile.
+      if (p.yield_flag != nullptr && lane == 0 && ld_cg_u32(p.yield_flag) != 0u) st_shared_volatile(yield_seen, 1u);
+      uint32_t ready[kGroups];
+      bool any = false, all_exit = true;
+#pragma unroll
+      for (int i = 0; i < kGroups; i++) {
+        uint32_t* wd = reinterpret_cast<uint32_t*>(smem + lay.off_words) + i * 16;
+        // These words change under the warp's feet: lane 0 reads them and every lane takes lane 0's answer, so that
+        // the warp decides as one.
+        const uint32_t ex = __shfl_sync(0xffffffffu, ld_shared_volatile(wd + 8), 0);  // read before the counter: an exit
+        all_exit &= ex != 0;                                                           // flag is set after the last hand-over
+        ready[i] = __shfl_sync(0xffffffffu, ld_shared_volatile(wd + 6), 0);
+        any |= ready[i] != published[i];
+      }
+      if (any) {
+        ST_CRUMB(3, 21);
+        __threadfence_block();
+        __threadfence_system();  // the payloads are performed before the flags that announce them
+        ST_CRUMB(3, 22);
+#pragma unroll
+        for (int i = 0; i < kGroups; i++) {
+          const StepDesc* q = reinterpret_cast<const StepDesc*>(smem + lay.off_pubq) + i * kPubQueue;
+          for (; published[i] != ready[i]; published[i]++) {
+            const StepDesc e = q[published[i] & (kPubQueue - 1)];
+            if (e.sent && lane < p.n_out && p.out[lane].link == e.link) {
+              const uint32_t slot_no = ctrl_byte(e.out_lo, e.out_hi, lane) & 63u;
+              const uint32_t seq = ld_cg_u32(p.out[lane].tx_seq + e.tile) + 1u;
+              st_relaxed_sys(p.out[lane].flags_remote + size_t(slot_no) * p.n_tiles + e.tile, seq);
+              st_cg_u32(p.out[lane].tx_seq + e.tile, seq);
+            }
+            if ((e.flags & kDescLast) && lane < p.n_in) {
+              const uint32_t avail = ctrl_byte(e.in_lo, e.in_hi, lane) >> 6;
+              if (avail) {
+                const uint32_t seq = ld_cg_u32(p.in[lane].rx_seq + e.tile) + avail;
+                st_cg_u32(p.in[lane].rx_seq + e.tile, seq);
+                st_relaxed_sys(p.in[lane].credit_remote + e.tile, seq);
+              }
+            }
+          }
+          __syncwarp();
+          __threadfence();  // the sequence counters are read by other warps once the hand-back below is seen
+          if (lane == 0) st_shared_volatile(reinterpret_cast<uint32_t*>(smem + lay.off_words) + i * 16 + 7, published[i]);
+        }
+      } else {
+        if (all_exit) break;
+        __nanosleep(100);
+        if ((it & 1023u) == 1023u && globaltimer_ns() - t_start > 4000ull * 1000 * 1000) break;  // the I/O warps are gone
+      }
+    }
+    ST_CRUMB(3, 23);
+    return;
+  }
 
   if (!is_io) {
     // =========================================================================================
@@ -463,19 +553,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
     uint32_t gphase = 0;
     float4 v[8];
     uint32_t vmax_mine = 0;
+#ifdef ST_ROUND_TIMING
+    long long tm_wait = 0, tm_total0 = clock64(), tm_steps = 0, tm_a = 0, tm_b = 0, tm_c = 0, tm_d = 0, tm_e = 0, st_lap_ = 0;
+#endif
 
     for (uint32_t c = 0;; c++) {
       const int s = int(c % kSlots);
       uint8_t* slot = slots + size_t(s) * lay.slot_stride;
-      if (!wait_step(full + s, (c / kSlots) & 1u, armed, c, abort_flag, limit_ns)) {
-        // Nothing of this step is stored: the warp reports the failure and leaves; the I/O warp then stops the group.
-        if (lane == 0) atomicOr(&sflags[s], kFlagFailed);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(done + s);
-        break;
-      }
+      ST_CRUMB(4 + g, 30);
+      ST_T0();
+      // The step's descriptor first: it says which frames arrived, and their loads go out before the wait for the
+      // tile, so that the two latencies overlap.
+      const bool armed_ok = __all_sync(0xffffffffu, wait_armed(armed, c, abort_flag));  // the warp decides as one
+      __threadfence_block();
       const StepDesc d = desc[s];
-      if (d.flags & kDescExit) break;
+      if (armed_ok && (d.flags & kDescExit)) break;
       const int tile = d.tile, l = d.link;
       float4* slot_v = reinterpret_cast<float4*>(slot) + t * 8;
       float4* slot_k = reinterpret_cast<float4*>(slot + kTileBytes) + t * 8;
@@ -485,47 +577,85 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
       const bool masked = (Q == 1) && !full_chunk;
       bool failed = false;
 
-      // ---- frames: decoded into one accumulated step per element.  `only_link` < 0 takes every ring.
-      auto decode_frames = [&](float4 (&acc)[8], int only_link) {
+      // ---- frames, in ring order and sequence order.  `only_link` < 0 takes every ring.
+      int it_r = -1, it_f = 0, it_avail = 0, it_only = -1;
+      uint32_t it_ib = 0;
+      auto first_frame = [&](int only_link) {
+        it_r = -1; it_f = 0; it_avail = 0; it_only = only_link;
+      };
+      auto next_frame = [&]() -> const uint8_t* {
+        while (true) {
+          if (it_r >= 0 && it_f < it_avail) {
+            const int slot_no = (int(it_ib & 63u) + it_f) & (p.ring_slots - 1);
+            it_f++;
+            return p.in[it_r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
+          }
+          it_r++;
+          if (it_r >= p.n_in) return nullptr;
+          it_ib = ctrl_byte(d.in_lo, d.in_hi, it_r);
+          it_avail = (it_only >= 0 && p.in[it_r].link != it_only) ? 0 : int(it_ib >> 6);
+          it_f = 0;
+        }
+      };
+      // Frames are fetched four at a time, so that four load latencies overlap, and applied in order.
+      constexpr int kBatch = 4;
+      uint32_t bw[kBatch][Q], bc[kBatch];
+      int bn = 0;
+      auto load_batch = [&]() {
+        bn = 0;
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          const uint8_t* fp = bn == i ? next_frame() : nullptr;
+          if (fp) {
+            load_frame<Q>(fp, t, tpb, bw[i], bc[i]);
+            bn = i + 1;
+          }
+        }
+      };
+      // acc = the sum of the frames' steps; the first batch may have been fetched already
+      auto decode_frames = [&](float4 (&acc)[8]) {
 #pragma unroll
         for (int q = 0; q < 8; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        int it_r = -1, it_f = 0, it_avail = 0;
-        uint32_t it_ib = 0;
-        auto next_frame = [&]() -> const uint8_t* {
-          while (true) {
-            if (it_r >= 0 && it_f < it_avail) {
-              const int slot_no = (int(it_ib & 63u) + it_f) & (p.ring_slots - 1);
-              it_f++;
-              return p.in[it_r].payload + (size_t(slot_no) * p.n_tiles + tile) * pb;
-            }
-            it_r++;
-            if (it_r >= p.n_in) return nullptr;
-            it_ib = ctrl_byte(d.in_lo, d.in_hi, it_r);
-            it_avail = (only_link >= 0 && p.in[it_r].link != only_link) ? 0 : int(it_ib >> 6);
-            it_f = 0;
-          }
-        };
-        // one frame is in flight while the one before it is applied
-        uint32_t w_cur[Q], c_cur = 0, w_nxt[Q], c_nxt = 0;
-        const uint8_t* fp = next_frame();
-        if (fp) load_frame<Q>(fp, t, tpb, w_cur, c_cur);
-        while (fp) {
-          const uint8_t* fn = next_frame();
-          if (fn) load_frame<Q>(fn, t, tpb, w_nxt, c_nxt);
-          if (masked) add_frame<Q, true>(acc, w_cur, c_cur, sw, vmask); else add_frame<Q, false>(acc, w_cur, c_cur, sw, vmask);
-          fp = fn;
+        while (bn > 0) {
 #pragma unroll
-          for (int j = 0; j < Q; j++) w_cur[j] = w_nxt[j];
-          c_cur = c_nxt;
+          for (int i = 0; i < kBatch; i++) {
+            if (i < bn) {
+              if (masked) add_frame<Q, true>(acc, bw[i], bc[i], sw, vmask); else add_frame<Q, false>(acc, bw[i], bc[i], sw, vmask);
+            }
+          }
+          if (bn == kBatch) load_batch(); else bn = 0;
         }
       };
 
+      const bool rx_first = armed_ok && (d.flags & kDescFirst) && (d.flags & kDescRxAny);
+      if (rx_first) {
+        first_frame(-1);
+        load_batch();
+      }
+      ST_CRUMB(4 + g, 31);
+      const bool step_ok = __all_sync(0xffffffffu, armed_ok && mbar_wait_bounded(full + s, (c / kSlots) & 1u, limit_ns));
+      ST_CRUMB(4 + g, 32);
+      ST_ACC(tm_wait);
+#ifdef ST_ROUND_TIMING
+      tm_steps++;
+#endif
+      if (!step_ok) {
+        // Nothing of this step is stored: the warp reports the failure and leaves; the I/O warp then stops the group.
+        if (lane == 0) atomicOr(&sflags[s], kFlagFailed);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(done + s);
+        break;
+      }
+
+#ifdef ST_ROUND_TIMING
+      st_lap_ = clock64();
+#endif
       if (d.flags & kDescFirst) {
 #pragma unroll
         for (int q = 0; q < 8; q++) v[q] = slot_v[q ^ sw];
-        if (d.flags & kDescRxAny) {
+        if (rx_first) {
           float4 acc[8];
-          decode_frames(acc, -1);
+          decode_frames(acc);
 #pragma unroll
           for (int q = 0; q < 8; q++) {
             v[q].x = __fadd_rn(v[q].x, acc[q].x); v[q].y = __fadd_rn(v[q].y, acc[q].y);
@@ -536,6 +666,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         vmax_mine = max_abs_bits(v);
       }
 
+      ST_LAP(tm_a);
       float4 k[8];
 #pragma unroll
       for (int q = 0; q < 8; q++) k[q] = slot_k[q ^ sw];
@@ -547,7 +678,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
 #pragma unroll
           for (int q = 0; q < 8; q++) acc[q] = slot_v[q ^ sw];
         } else {
-          decode_frames(acc, l);
+          first_frame(l);
+          load_batch();
+          decode_frames(acc);
         }
 #pragma unroll
         for (int q = 0; q < 8; q++) {
@@ -557,6 +690,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         changed = true;
       }
 
+      ST_LAP(tm_b);
       // ---- quantise values - mirror for link l
       float xm = residual_maxabs(v, k);
       if (l == 0) res_max0 = fmaxf(res_max0, xm); else if (l == 1) res_max1 = fmaxf(res_max1, xm); else res_max2 = fmaxf(res_max2, xm);
@@ -574,7 +708,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(gsync);
-        if (!mbar_wait_bounded(gsync, gphase, limit_ns)) failed = true;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(gsync, gphase, limit_ns))) failed = true;
         gphase ^= 1u;
         const float a0 = red[0], a1 = red[1], a2 = red[2], a3 = red[3];
         const uint32_t b0 = __float_as_uint(red[4]), b1 = __float_as_uint(red[5]);
@@ -588,6 +722,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         }
       }
       const int code = block_code_dev<Q>(xm, vm, p.min_exp, p.rel_bits);
+      ST_LAP(tm_c);
       if ((d.flags & kDescTxOk) != 0) {
         uint8_t* pay = slot + 2 * kTileBytes;
         if (code) {
@@ -607,6 +742,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         }
         if ((t & ((1 << tpb) - 1)) == 0) pay[4 * Q * kWordsPerTile + (t >> tpb)] = uint8_t(code);
       }
+      ST_LAP(tm_d);
       if (changed) {
 #pragma unroll
         for (int q = 0; q < 8; q++) slot_k[q ^ sw] = k[q];
@@ -619,9 +755,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(done + s);
+      ST_LAP(tm_e);
       if (failed) break;
     }
 
+#ifdef ST_ROUND_TIMING
+    if (blockIdx.x == 0 && tid == 0)
+      printf("compute: total %lld cycles, waiting for steps %lld, steps %lld; values+decode %lld, mirror+rx %lld, stats %lld, quantise %lld, store+arrive %lld\n",
+             clock64() - tm_total0, tm_wait, tm_steps, tm_a, tm_b, tm_c, tm_d, tm_e);
+#endif
+    ST_CRUMB(4 + g, 33);
     // ---- statistics: the largest outstanding residual per link
     {
       float a0 = res_max0, a1 = res_max1, a2 = res_max2;
@@ -643,72 +786,105 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
   // ===========================================================================================
   // I/O warp.  All 32 lanes run the same control flow; lane 0 issues copies, stores and flags.
   // ===========================================================================================
-  const int gid = int(blockIdx.x) * kGroups + g;
-  const int gstride = int(gridDim.x) * kGroups;
-  const int my_count = p.n_tiles > gid ? (p.n_tiles - gid + gstride - 1) / gstride : 0;
+  // The group's tiles: a run of `chunk` consecutive tiles, or (chunk == 0) every gstride-th tile of the tensor.
+  const int gidx = int(blockIdx.x) * kGroups + g;
+  const int gid = p.chunk > 0 ? gidx * p.chunk : gidx;
+  const int gstride = p.chunk > 0 ? 1 : int(gridDim.x) * kGroups;
+  const int my_count = p.chunk > 0 ? max(0, min(p.chunk, p.n_tiles - gid))
+                                   : (p.n_tiles > gid ? (p.n_tiles - gid + gstride - 1) / gstride : 0);
   const uint32_t smask = uint32_t(p.ring_slots) - 1u;
   uint32_t issued = 0, retired = 0;
-  int pub_head = 0, pub_count = 0;
   unsigned long long n_done = 0, n_tx = 0, n_rx = 0, n_blocked = 0, n_pending = 0, n_sweeps = 0;
-  bool aborted = false, tile_pending = false;
+  bool aborted = false, tile_pending = false, yielded = false;
+#ifdef ST_ROUND_TIMING
+  long long tm_done = 0, tm_read = 0, tm_pubwait = 0, tm_pub = 0, tm_scout = 0, tm_issue = 0, tm_store = 0, tm_pf = 0, tm_io0 = clock64();
+#endif
 
   if (blockIdx.x == 0 && g == 0 && lane == 0) {
     uint64_t* other = p.status + (p.parity ? kDsLaunch0 : kDsLaunch1);  // the next launch's half
     for (int i = 0; i < 8; i++) other[i] = 0;
   }
 
-  // sequence flags and credits of one retired step, once its stores have completed (lane 0)
-  auto publish_oldest = [&]() {
-    if (lane == 0) {
-      const StepDesc e = pubq[pub_head];
-      __threadfence_system();  // the payload is performed before the flag that announces it
-      if (e.sent) {
-        for (int r = 0; r < p.n_out; r++) {
-          if (p.out[r].link != e.link) continue;
-          const uint32_t slot_no = ctrl_byte(e.out_lo, e.out_hi, r) & 63u;
-          const uint32_t seq = ld_cg_u32(p.out[r].tx_seq + e.tile) + 1u;
-          st_relaxed_sys(p.out[r].flags_remote + size_t(slot_no) * p.n_tiles + e.tile, seq);
-          st_cg_u32(p.out[r].tx_seq + e.tile, seq);
-        }
-      }
-      if (e.flags & kDescLast) {
-        for (int r = 0; r < p.n_in; r++) {
-          const uint32_t avail = ctrl_byte(e.in_lo, e.in_hi, r) >> 6;
-          if (!avail) continue;
-          const uint32_t seq = ld_cg_u32(p.in[r].rx_seq + e.tile) + avail;
-          st_cg_u32(p.in[r].rx_seq + e.tile, seq);
-          st_relaxed_sys(p.in[r].credit_remote + e.tile, seq);
-        }
-      }
+  // Steps whose stores have completed are handed to the publisher warp; `pushed` counts the steps queued so far.
+  uint32_t pushed = 0, handed = 0;
+  auto hand_over = [&](uint32_t upto) {
+    if (lane == 0 && upto != handed) {
+      __threadfence_block();
+      st_shared_volatile(pub_ready, upto);
     }
-    pub_head = (pub_head + 1) & (kPubQueue - 1);
-    pub_count--;
+    handed = upto;
+  };
+  // bounded wait until the publisher has published `upto` steps
+  auto wait_published = [&](uint32_t upto) -> bool {
+    const uint64_t t0 = globaltimer_ns();
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 26); it++) {
+      if (int32_t(ld_shared_volatile(pub_done) - upto) >= 0) {
+        ok = true;
+        break;
+      }
+      if ((it & 15) == 15 && globaltimer_ns() - t0 > 2 * limit_ns + 2000000ull) break;
+      __nanosleep(50);
+    }
+    return __all_sync(0xffffffffu, ok);  // the warp decides as one
   };
 
-  // a finished step: its stores go out, its slot becomes free, the step before the one before it is published
+  // a finished step: its stores go out and its slot becomes free
   auto retire = [&](uint32_t c) -> bool {
     const int s = int(c % kSlots);
-    const bool ok = mbar_wait_bounded(done + s, (c / kSlots) & 1u, 2 * limit_ns);
-    const uint32_t f = ok ? ld_shared_volatile(sflags + s) : kFlagFailed;
+    bool ok;
+    {
+      ST_T0();
+      ST_CRUMB(g, 4);
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(done + s, (c / kSlots) & 1u, 2 * limit_ns));
+      ST_ACC(tm_done);
+    }
+    const uint32_t f = ok ? __shfl_sync(0xffffffffu, ld_shared_volatile(sflags + s), 0) : kFlagFailed;
     if (f & kFlagFailed) return false;
-    if (lane == 0) {
+    if (pushed - __shfl_sync(0xffffffffu, ld_shared_volatile(pub_done), 0) >= uint32_t(kPubQueue)) {  // (never in practice: the queue is 8 steps deep)
+      bulk_wait_all();
+      __syncwarp();
+      hand_over(pushed);
+      if (!wait_published(pushed)) return false;
+    }
+    ST_T0();
+    {
+      // the step's stores, one per lane, issued by as few instructions as possible: lane 0 the reduce-add of what was
+      // received into the values; lane 1 the stepped mirror, lanes 2.. the frame into the ring of out-ring lane-2.
+      // Every lane that issued commits and later waits for its own bulk group.
       const StepDesc d = desc[s];
       uint8_t* slot = slots + size_t(s) * lay.slot_stride;
       const bool sent = (d.flags & kDescTxOk) != 0 && (f & kFlagNonsilent) != 0;
-      if ((d.flags & kDescFirst) && (d.flags & kDescRxAny)) bulk_reduce_add_f32(p.values + size_t(d.tile) * kTile, slot, kTileBytes);
-      if (f & kFlagChanged) bulk_s2g(p.mirror[d.link] + size_t(d.tile) * kTile, slot + kTileBytes, kTileBytes);
-      if (sent) {
-        for (int r = 0; r < p.n_out; r++) {
-          if (p.out[r].link != d.link) continue;
-          const uint32_t slot_no = ctrl_byte(d.out_lo, d.out_hi, r) & 63u;
-          bulk_s2g(p.out[r].payload_remote + (size_t(slot_no) * p.n_tiles + d.tile) * pb, slot + 2 * kTileBytes, uint32_t(pb));
-          n_tx++;
+      if (lane == 0 && (d.flags & kDescFirst) && (d.flags & kDescRxAny))
+        bulk_reduce_add_f32(p.values + size_t(d.tile) * kTile, slot, kTileBytes);
+      {
+        void* dst = nullptr;
+        const uint8_t* src = nullptr;
+        uint32_t bytes = 0;
+        if (lane == 1) {
+          if (f & kFlagChanged) {
+            dst = p.mirror[d.link] + size_t(d.tile) * kTile;
+            src = slot + kTileBytes;
+            bytes = kTileBytes;
+          }
+        } else if (lane >= 2 && lane - 2 < p.n_out && sent && p.out[lane - 2].link == d.link) {
+          const uint32_t slot_no = ctrl_byte(d.out_lo, d.out_hi, lane - 2) & 63u;
+          dst = p.out[lane - 2].payload_remote + (size_t(slot_no) * p.n_tiles + d.tile) * pb;
+          src = slot + 2 * kTileBytes;
+          bytes = uint32_t(pb);
         }
+        if (bytes) bulk_s2g(dst, src, bytes);
       }
       bulk_commit();
+    }
+    if (lane == 0) {
+      const StepDesc d = desc[s];
+      const bool sent = (d.flags & kDescTxOk) != 0 && (f & kFlagNonsilent) != 0;
+      if (sent)
+        for (int r = 0; r < p.n_out; r++) n_tx += p.out[r].link == d.link ? 1 : 0;
       StepDesc e = d;
       e.sent = sent ? 1u : 0u;
-      pubq[(pub_head + pub_count) & (kPubQueue - 1)] = e;
+      pubq[pushed & (kPubQueue - 1)] = e;
       if (f & kFlagNonsilent) {
         tile_pending = true;  // more may be left to say (or nothing could be said at all)
         if (!sent && p.do_tx) n_blocked++;
@@ -722,18 +898,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
         n_done++;
         for (int r = 0; r < p.n_in; r++) n_rx += ctrl_byte(d.in_lo, d.in_hi, r) >> 6;
       }
-      bulk_wait_read_all();  // the slot may be refilled
     }
-    pub_count++;
+    {
+      ST_T0();
+      ST_CRUMB(g, 5);
+      bulk_wait_read_all();  // every lane for its own stores: the slot may be refilled
+      ST_ACC(tm_read);
+    }
+    pushed++;
     __syncwarp();
-    if (pub_count > 2) {
-      if (lane == 0) bulk_wait_all_but_2();
-      publish_oldest();
-    }
+    ST_ACC(tm_store);
     return true;
   };
 
-  for (int sweep = 0; sweep < p.sweeps && !aborted && my_count > 0; sweep++) {
+  ST_CRUMB(g, 1);
+  for (int sweep = 0; sweep < p.sweeps && !aborted && !yielded && my_count > 0; sweep++) {
     const unsigned long long done_before = n_done;
     int scan_pos = 0;
     uint32_t pend = 0;                 // lanes whose scouted tile still has to be handed out
@@ -744,7 +923,17 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
     bool exhausted = my_count == 0;
 
     while (true) {
+      ST_CRUMB(g, 2);
       if (!exhausted && issued - retired < uint32_t(kSlots)) {
+        if (cur_tile < 0 && __shfl_sync(0xffffffffu, ld_shared_volatile(yield_seen), 0) != 0u) {
+          // An update is waiting for the SMs this kernel holds: hand out nothing more.  Tiles that were looked at but
+          // not handed out get their change marks back, everything else is untouched.
+          if ((pend >> lane) & 1u) st_cg_u32(p.tile_state + sc_tile, 1u);
+          pend = 0;
+          exhausted = true;
+          yielded = true;
+          continue;
+        }
         if (cur_tile < 0) {
           if (pend == 0) {
             if (scan_pos >= my_count) {
@@ -752,6 +941,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
               continue;
             }
             // ---- look at 32 tiles at once, one per lane
+            ST_T0();
             const int j = scan_pos + lane;
             const bool valid = j < my_count;
             sc_tile = gid + j * gstride;
@@ -791,6 +981,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
             }
             pend = __ballot_sync(0xffffffffu, work);
             scan_pos += 32;
+            ST_ACC(tm_scout);
             continue;
           }
           const int src = __ffs(pend) - 1;
@@ -803,6 +994,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
           cur_a = 0;
         }
         // ---- hand out step (cur_tile, link cur_a)
+        ST_T0();
+        __syncwarp();
+        ST_ACC(tm_pf);
         if (lane == 0) {
           const int s = int(issued % kSlots);
           uint8_t* slot = slots + size_t(s) * lay.slot_stride;
@@ -825,17 +1019,37 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
           d.in_lo = cur_in_lo; d.in_hi = cur_in_hi; d.out_lo = cur_out_lo; d.out_hi = cur_out_hi;
           desc[s] = d;
           sflags[s] = 0;
+          __threadfence_block();
+          st_shared_volatile(armed, issued + 1u);  // the compute warps may read the descriptor from here on
           uint32_t bytes = (cur_a == 0 ? 2u : 1u) * uint32_t(kTileBytes);
           if (cur_tile == p.stall_tile) bytes += 16;  // test hook: this barrier never completes
           mbar_expect_tx(full + s, bytes);
-          if (cur_a == 0) bulk_g2s(slot, p.values + size_t(cur_tile) * kTile, kTileBytes, full + s);
-          bulk_g2s(slot + kTileBytes, p.mirror[l] + size_t(cur_tile) * kTile, kTileBytes, full + s);
-          st_shared_volatile(armed, issued + 1u);
+        }
+        __syncwarp();
+        {
+          // the step's copies, one per lane, issued by one instruction: lane 0 the link's mirror, lane 1 the values
+          const int s = int(issued % kSlots);
+          uint8_t* slot = slots + size_t(s) * lay.slot_stride;
+          if (lane == 0 || (lane == 1 && cur_a == 0)) {
+            const float* src = (lane == 0 ? p.mirror[cur_a] : p.values) + size_t(cur_tile) * kTile;
+            bulk_g2s(slot + (lane == 0 ? kTileBytes : 0), src, kTileBytes, full + s);
+          }
         }
         issued++;
         cur_a++;
         if (cur_a == L) cur_tile = -1;
+        __syncwarp();
+        ST_ACC(tm_issue);
         continue;
+      }
+      // Nothing can be handed out right now: the steps whose stores have had time to land (all but the two most
+      // recent) go to the publisher warp.
+      if (pushed - handed > 2) {
+        ST_T0();
+        ST_CRUMB(g, 6);
+        bulk_wait_all_but_2();  // every lane for its own stores
+        hand_over(pushed - 2);
+        ST_ACC(tm_pubwait);
       }
       if (retired < issued) {
         if (!retire(retired)) {
@@ -849,9 +1063,19 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
     }
     if (aborted) break;
     // ---- end of the sweep: every store has landed and is published before the tiles are looked at again
-    if (lane == 0) bulk_wait_all();
-    while (pub_count > 0) publish_oldest();
+    ST_CRUMB(g, 7);
+    bulk_wait_all();
     __syncwarp();
+    hand_over(pushed);
+    {
+      ST_T0();
+      ST_CRUMB(g, 8);
+      if (!wait_published(pushed)) aborted = true;  // the next sweep reads the counters the publisher advances
+      ST_ACC(tm_pub);
+    }
+    ST_CRUMB(g, 9);
+    __syncwarp();
+    if (aborted) break;
     n_sweeps++;
     if (n_done == done_before && sweep + 1 < p.sweeps) __nanosleep(1000);
   }
@@ -862,15 +1086,23 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
     // published; every tile of the group is marked for another visit.
     if (lane == 0) st_shared_volatile(abort_flag, 1u);
     __syncwarp();
-    for (uint32_t c = retired; c < issued; c++) (void)mbar_wait_bounded(full + int(c % kSlots), (c / kSlots) & 1u, limit_ns);
-    if (lane == 0) bulk_wait_all();
-    while (pub_count > 0) publish_oldest();
+    for (uint32_t c = retired; c < issued; c++)
+      (void)__all_sync(0xffffffffu, mbar_wait_bounded(full + int(c % kSlots), (c / kSlots) & 1u, limit_ns));
+    bulk_wait_all();
+    __syncwarp();
+    hand_over(pushed);
+    (void)wait_published(pushed);
     for (int j = lane; j < my_count; j += 32) st_cg_u32(p.tile_state + gid + j * gstride, 1u);
     if (lane == 0) {
       atomicOr(reinterpret_cast<unsigned long long*>(p.status + kDsErrors), (unsigned long long)kErrBarrierTimeout);
       atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsWaitTimeouts), 1ull);
     }
   }
+#ifdef ST_ROUND_TIMING
+  if (blockIdx.x == 0 && g == 0 && lane == 0)
+    printf("io: total %lld cycles, wait done %lld, wait read %lld, wait stores %lld, fence+publish %lld, scout %lld, prefetch %lld, issue(incl prefetch) %lld, retire(incl read wait) %lld, steps %u\n",
+           clock64() - tm_io0, tm_done, tm_read, tm_pubwait, tm_pub, tm_scout, tm_pf, tm_issue, tm_store, issued);
+#endif
   if (lane == 0) {
     // tell the compute warps that the launch is over (the slot of step `issued` is free: all earlier steps are retired
     // or abandoned)
@@ -880,9 +1112,13 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
     d.in_lo = d.in_hi = d.out_lo = d.out_hi = 0;
     if (!aborted) {  // (after an abort the compute warps leave on the abort flag)
       desc[s] = d;
-      mbar_arrive(full + s);
+      __threadfence_block();
       st_shared_volatile(armed, issued + 1u);
+      mbar_arrive(full + s);
     }
+    st_shared_volatile(pub_exit, 1u);
+    ST_CRUMB(g, 10);
+    if (yielded) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsYields), 1ull);
     if (n_done) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsTilesProcessed), n_done);
     if (n_tx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsFramesSent), n_tx);
     if (n_rx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsFramesRecv), n_rx);
@@ -904,31 +1140,39 @@ __global__ void __launch_bounds__(kCtaThreads, 1) round_kernel(const __grid_cons
 // ----------------------------------------------------------------------------------------------
 // launcher
 // ----------------------------------------------------------------------------------------------
-template <int Q>
+template <int Q, int G, int S>
 static int launch_round_t(const RoundParams& p, int ctas, cudaStream_t stream) {
-  const int smem = smem_layout(p.payload_bytes).total;
+  const int smem = smem_layout(p.payload_bytes, G, S).total;
   static int configured_for = -1;  // per instantiation
   if (configured_for < smem) {
-    cudaError_t e = cudaFuncSetAttribute(round_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(round_kernel<Q, G, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return int(e);
     configured_for = smem;
   }
-  round_kernel<Q><<<ctas, kCtaThreads, smem, stream>>>(p);
+  round_kernel<Q, G, S><<<ctas, G * (kGroupThreads + 32) + 32, smem, stream>>>(p);
   return int(cudaGetLastError());
 }
 
-int launch_round(const RoundParams& p, int ctas, void* stream_v) {
+template <int Q>
+static int launch_round_q(const RoundParams& p, int shape, int ctas, cudaStream_t stream) {
+  switch (shape) {
+    case 0: return launch_round_t<Q, 3, 2>(p, ctas, stream);
+    case 1: return launch_round_t<Q, 2, 3>(p, ctas, stream);
+    default: return int(cudaErrorInvalidValue);
+  }
+}
+
+int round_shape_groups(int shape) { return shape == 0 ? 3 : 2; }
+
+int launch_round(const RoundParams& p, int shape, int ctas, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (p.n_links < 1 || p.n_links > kMaxLinks || p.sweeps < 1) return int(cudaErrorInvalidValue);
+  if (p.n_links < 1 || p.n_links > kMaxLinks || p.sweeps < 1 || ctas < 1) return int(cudaErrorInvalidValue);
   if (p.ring_slots < 2 || p.ring_slots > 64 || (p.ring_slots & (p.ring_slots - 1))) return int(cudaErrorInvalidValue);
-  const int needed = (p.n_tiles + kGroups - 1) / kGroups;  // more CTAs than this would have no tile
-  if (ctas > needed) ctas = needed;
-  if (ctas < 1) ctas = 1;
   switch (p.bits) {
-    case 1: return launch_round_t<1>(p, ctas, stream);
-    case 2: return launch_round_t<2>(p, ctas, stream);
-    case 4: return launch_round_t<4>(p, ctas, stream);
-    case 8: return launch_round_t<8>(p, ctas, stream);
+    case 1: return launch_round_q<1>(p, shape, ctas, stream);
+    case 2: return launch_round_q<2>(p, shape, ctas, stream);
+    case 4: return launch_round_q<4>(p, shape, ctas, stream);
+    case 8: return launch_round_q<8>(p, shape, ctas, stream);
     default: return int(cudaErrorInvalidValue);
   }
 }

@@ -76,6 +76,9 @@ struct RoundParams {
   int32_t sweeps;                // passes over the tensor in this launch (>= 1)
   uint32_t wait_ns;              // upper bound of every wait on one of the kernel's own copies
   int32_t stall_tile;            // test hook: the copy barrier of this tile expects more bytes than are copied (-1: none)
+  int32_t chunk;                 // > 0: a group owns this many consecutive tiles; 0: every (groups in the grid)-th tile
+  const uint32_t* yield_flag;    // non-zero while an update is waiting for SMs: groups hand out no more tiles and leave
+  uint32_t* dbg;                 // debug builds: progress marks in mapped host memory, 8 words per CTA (else null)
 };
 
 // Layout of the device status block (uint64 each).  Counters are cumulative; the per-launch words exist twice and a
@@ -88,6 +91,7 @@ enum DevStatus : int {
   kDsBlockedNoCredit,  // tile-links that had something to send but no ring space
   kDsErrors,           // bit mask, see kErr*
   kDsWaitTimeouts,
+  kDsYields,           // groups that left early because an update was waiting
   kDsLaunch0 = 8,      // per-launch words of parity 0: work, pending tiles, residual maxima of links 0..2 (fp32 bits)
   kDsLaunch1 = 16,     // ... of parity 1
   kDsTrace = 24,       // ring of kTraceEntries records {globaltimer ns, round, tiles handled by group 0, frames sent so far}
@@ -117,8 +121,11 @@ enum StatusWord : int {
 };
 
 // Launchers.  `stream` is a cudaStream_t passed as void*.  Return a cudaError_t as int.
-int launch_round(const RoundParams& p, int ctas, void* stream);
-int round_smem_bytes(int bits, int payload_bytes);
+// `shape` picks the CTA's make-up: 0 = 3 groups x 2 staging slots, 1 = 2 groups x 3 slots (one CTA per SM either way).
+// A group is 4 compute warps and one I/O warp; a CTA has one more warp that publishes flags and credits.
+int launch_round(const RoundParams& p, int shape, int ctas, void* stream);
+int round_shape_groups(int shape);
+int round_smem_bytes(int groups, int slots, int payload_bytes);
 
 // Element-wise kernels (copyToTensor / addFromTensor / pushUpdate; src/sharedtensor.c:435-446, 334-344).
 int launch_snapshot_f32(const float* values, float* out, int64_t n, void* stream);
@@ -130,12 +137,18 @@ int launch_sub_add(float* values, const float* neu, const float* old, int64_t n,
 int launch_add_scaled_bf16(float* values, const void* g_bf16, float alpha, int64_t n, int atomic, void* stream);
 // Marks every tile as changed.  Launched behind an update on the same stream, so the marks become visible after the data.
 int launch_fill_state(uint32_t* tile_state, int n_tiles, uint32_t value, void* stream);
+int launch_set_word(uint32_t* word, uint32_t value, void* stream);  // one thread; stands in for a stream memory write
 // Per-segment sum of squares (table sync).  partials: scratch of table_scales_scratch_doubles(...) doubles.
 int64_t table_scales_scratch_doubles(int n_seg, int64_t n_total);
 int launch_table_scales(const float* x, const int64_t* seg_offsets_dev, int n_seg, int64_t n_total, double* partials,
                         double* out_sumsq, int8_t* out_exp, void* stream);
 // sum((a[i*stride] - b[i])^2) over count samples, into out[0] (double); out[1] counts NaNs.  Zeroes nothing.
 int launch_sample_sqerr(const float* a, int64_t stride, const float* b, int64_t count, double* out, void* stream);
+// The same sampled error, compared on the device: the first launch that finds it at or below `threshold` writes the
+// GPU's %globaltimer into *stamp.  scratch: 16 zeroed bytes, reused by every launch; last_err: the error it saw.
+int launch_probe_converged(const float* a, int64_t stride, const float* b, int64_t count, double threshold, double* scratch,
+                           uint64_t* stamp, double* last_err, void* stream);
+int launch_stamp(uint64_t* out, void* stream);  // *out = %globaltimer
 // Busy-waits `ns` nanoseconds on the device with one thread (models "compute between updates").
 int launch_delay(uint64_t ns, void* stream);
 // values -> dst (peer or local) and mirror <- values in one pass; used for snapshot-on-join.

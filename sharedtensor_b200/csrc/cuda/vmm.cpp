@@ -28,6 +28,7 @@ struct Api {
   decltype(&cuMemExportToShareableHandle) MemExportToShareableHandle = nullptr;
   decltype(&cuMemImportFromShareableHandle) MemImportFromShareableHandle = nullptr;
   decltype(&cuGetErrorString) GetErrorString = nullptr;
+  decltype(&cuStreamWriteValue32) StreamWriteValue32 = nullptr;  // optional
 };
 
 template <class F>
@@ -63,6 +64,7 @@ Api& api() {
     ok &= load("cuMemExportToShareableHandle", &a.MemExportToShareableHandle);
     ok &= load("cuMemImportFromShareableHandle", &a.MemImportFromShareableHandle);
     ok &= load("cuGetErrorString", &a.GetErrorString);
+    load("cuStreamWriteValue32", &a.StreamWriteValue32);
     a.ok = ok;
   });
   return a;
@@ -117,6 +119,12 @@ bool map_rw(CUmemGenericAllocationHandle h, size_t bytes, int device, void** out
 }  // namespace
 
 bool vmm_available() { return api().ok; }
+
+bool stream_write_u32(void* stream, uint32_t* dev_ptr, uint32_t value) {
+  Api& a = api();
+  if (!a.StreamWriteValue32) return false;
+  return a.StreamWriteValue32(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(dev_ptr), value, 0) == CUDA_SUCCESS;
+}
 
 size_t vmm_granularity(int device) {
   if (!api().ok) return 2u << 20;

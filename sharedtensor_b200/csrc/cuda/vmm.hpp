@@ -31,6 +31,9 @@ int vmm_export_fd(const VmmBlock& b, std::string* err);
 VmmBlock vmm_import_fd(int fd, size_t bytes, int device, std::string* err);
 void vmm_free(VmmBlock* b);
 bool vmm_available();
+// Writes one word of device memory in stream order without occupying an SM (cuStreamWriteValue32).  False if the
+// driver does not offer it; the caller then uses a one-thread kernel.
+bool stream_write_u32(void* stream, uint32_t* dev_ptr, uint32_t value);
 size_t vmm_granularity(int device);
 
 // fd passing

@@ -30,6 +30,8 @@ def _gpu_config(cfg: Config):
     g.bits = cfg.bits
     g.sweeps = cfg.sweeps_per_launch
     g.poll_deadline_us = cfg.poll_deadline_us
+    g.yield_to_updates = cfg.yield_to_updates
+    g.comm_high_priority = cfg.comm_high_priority
     return g
 
 

@@ -40,6 +40,8 @@ class Config:
     idle_sleep_us: int = 1000        # longest engine pause while nothing moves (backs off from 10 us; doorbells end it)
     round_interval_us: int = 0       # pause after every busy round: caps the round rate (a rate limit for GPU edges)
     poll_deadline_us: int = 1000     # upper bound of every wait inside the round kernel
+    yield_to_updates: bool = True    # a running round kernel gives up its SMs when addFromTensor has an update ready
+    comm_high_priority: bool = False # comm stream at the highest stream priority (then rounds do not yield to updates)
     use_multimem: bool = False       # reserved: NVLS store fan-out is not built (plain peer stores only)
     # --- TCP edges ------------------------------------------------------------------------------
     max_frames_per_s: float = 0.0    # rate cap per edge (README.md:31 of the reference lists this as a TODO)
