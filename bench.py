@@ -219,23 +219,8 @@ def run_ours(args) -> dict | None:
     staging = [torch.empty(n, device=dev) for _ in range(2)] if not args.no_e2e else []
     copy_stream = torch.cuda.Stream(device=dev)
 
-    # ---- the GPU's clock against the host's: all ranks share the host's monotonic clock, so device time stamps of
-    # different GPUs become comparable.  The launch with the tightest host bracket gives the offset.
-    stamp_dev = torch.zeros(4, dtype=torch.int64, device=dev)
-    stamp_host = torch.zeros(4, dtype=torch.int64).pin_memory()
-
-    def clock_offset_ns() -> tuple[float, float]:
-        best = None
-        for _ in range(200):
-            torch.cuda.synchronize()
-            t0 = time.monotonic_ns()
-            cu.stamp(stamp_dev.data_ptr(), stream)
-            torch.cuda.synchronize()
-            t1 = time.monotonic_ns()
-            stamp_host.copy_(stamp_dev)
-            if best is None or t1 - t0 < best[1]:
-                best = (int(stamp_host[0]) - (t0 + t1) / 2.0, t1 - t0)
-        return best  # (gpu clock - host clock, width of the bracket)
+    from sharedtensor_b200.utils.probe import ConvergenceProbe
+    probe = ConvergenceProbe(cu, dev)
 
     def measure(topology: str, headline: bool, port: int) -> dict:
         expect_s = init[::SAMPLE_STRIDE].clone()
@@ -256,8 +241,6 @@ def run_ours(args) -> dict | None:
         rep = st._b.rep
         err_buf = torch.zeros(2, dtype=torch.float64, device=dev)
         err_host = torch.zeros(2, dtype=torch.float64).pin_memory()
-        probe_scratch = torch.zeros(2, dtype=torch.float64, device=dev)
-        probe_err = torch.zeros(1, dtype=torch.float64, device=dev)
         extra_launches = 0
 
         def sampled_err2() -> float:
@@ -386,7 +369,8 @@ def run_ours(args) -> dict | None:
         lat_ms = []
         offsets = None
         if world > 1 and args.probes > 0:
-            off, width = clock_offset_ns()
+            probe.launches = 0
+            off, width = probe.calibrate()
             offs = allgather(off)
             widths = allgather(float(width))
             offsets = {"gpu_minus_host_ns": [round(o) for o in offs], "bracket_ns": [round(w) for w in widths]}
@@ -394,24 +378,15 @@ def run_ours(args) -> dict | None:
                 origin, p = i % world, i % POOL
                 add_expected(origin, p)
                 thr = float((pool_s[(origin, p)].double() ** 2).sum()) * TOL * TOL
-                stamp_dev.zero_()
+                probe.arm()
                 barrier()
                 if rank == origin:
                     st.addFromTensor(pool[p])
-                    cu.stamp(stamp_dev.data_ptr() + 8, stream)     # [1]: the update has landed on the origin
-                t0 = time.perf_counter()
-                while True:
-                    for _ in range(8):
-                        cu.probe_converged(rep.values_ptr(), SAMPLE_STRIDE, expect_s.data_ptr(), n_s, thr, probe_scratch.data_ptr(),
-                                           stamp_dev.data_ptr(), probe_err.data_ptr(), stream)
-                    extra_launches += 8
-                    stamp_host.copy_(stamp_dev, non_blocking=True)
-                    torch.cuda.synchronize()
-                    if int(stamp_host[0]) != 0 or time.perf_counter() - t0 > 5.0:
-                        break
-                t_conv = float(stamp_host[0]) - off if int(stamp_host[0]) != 0 else float("inf")    # on the host's clock
-                t_add = allmax(float(stamp_host[1]) - off if rank == origin else -1e30)
+                    probe.stamp_origin()
+                t_conv, t_landed = probe.wait(rep.values_ptr(), SAMPLE_STRIDE, expect_s, thr)
+                t_add = allmax(t_landed if rank == origin else -1e30)
                 lat_ms.append(allmax(t_conv - t_add) / 1e6)
+            extra_launches += probe.launches
 
         # ---- every element of every replica against the exact sum (the polling above looks at every 64th)
         full_rel = None

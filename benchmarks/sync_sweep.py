@@ -6,8 +6,9 @@
 
 For every size and the N ranks of one box it measures, with deltas ~ N(0,1):
   * the compressed path of this framework: device time of one sync round under load (max over ranks), the
-    HBM bytes that round moves per rank and the packed bytes it puts on each edge, and the wall-clock time
-    until one update has reached every replica to 1 % (engine free-running);
+    HBM bytes that round moves per rank and the packed bytes it puts on each edge, and the time until one
+    update has reached every replica to 1 % (engine free-running), taken from GPU clock stamps: the origin's
+    behind its add, every replica's when its probe kernel first finds the error within tolerance;
   * the baseline: an NCCL all-reduce of the uncompressed fp32 delta followed by the local add.
 It prints one JSON object per size on rank 0 and a summary table at the end.
 """
@@ -35,7 +36,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-log4", type=int, default=5)    # 4^5 = 1 Ki
     ap.add_argument("--max-log4", type=int, default=15)   # 4^15 = 1 Gi
-    ap.add_argument("--probes", type=int, default=8)
+    ap.add_argument("--probes", type=int, default=24)
+    ap.add_argument("--topology", default="tree", choices=["tree", "mesh"])
+    ap.add_argument("--bits", type=int, default=0, help="bits per element of a frame (0: the library's default)")
     ap.add_argument("--rounds", type=int, default=20)
     ap.add_argument("--out", default="")
     args = ap.parse_args()
@@ -64,6 +67,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
+    from sharedtensor_b200.utils.probe import ConvergenceProbe
+    probe = ConvergenceProbe(cu, dev)
+    probe.calibrate()
+    kw = {"bits": args.bits} if args.bits else {}
     rows = []
     for i, k in enumerate(range(args.min_log4, args.max_log4 + 1)):
         n = 4 ** k
@@ -75,30 +82,33 @@ def main():
             deltas.append(torch.randn(n, generator=g, device=dev))
         # ---- our path
         st = None
-        for r in range(world):
-            if r == rank:
-                st = sharedtensor.createOrFetch("127.0.0.1", base_port + i, init if rank == 0 else torch.empty(n, device=dev))
+        if args.topology == "mesh":
+            st = sharedtensor.createOrFetch("127.0.0.1", base_port + i, init if rank == 0 else torch.empty(n, device=dev),
+                                            topology="mesh", group_rank=rank, group_size=world, **kw)
             barrier()
+        else:
+            for r in range(world):
+                if r == rank:
+                    st = sharedtensor.createOrFetch("127.0.0.1", base_port + i, init if rank == 0 else torch.empty(n, device=dev), **kw)
+                barrier()
         rep = st._b.rep
-        expect = init.clone()
         out = torch.empty(n, device=dev)
+        stride = max(1, n >> 21)               # the probe looks at up to 2 Mi elements
+        expect_s = init[::stride].clone()
         lat = []
-        st.copyToTensor(out)  # first use of the measuring kernels at this size (lazy module loading) stays untimed
-        float((out - expect).norm())
-        for pr in range(args.probes):
+        for pr in range(args.probes + 2):
             origin = pr % world
-            expect += deltas[origin]
-            upd = float(deltas[origin].norm())
+            expect_s += deltas[origin][::stride]
+            thr = float((deltas[origin][::stride].double() ** 2).sum()) * TOL * TOL
+            probe.arm()
             barrier()
-            t0 = time.perf_counter()
             if rank == origin:
                 st.addFromTensor(deltas[origin])
-            while True:
-                st.copyToTensor(out)
-                torch.cuda.synchronize()
-                if float((out - expect).norm()) <= TOL * upd or time.perf_counter() - t0 > 10:
-                    break
-            lat.append(allmax(time.perf_counter() - t0))
+                probe.stamp_origin()
+            t_conv, t_landed = probe.wait(rep.values_ptr(), stride, expect_s, thr, timeout_s=10.0)
+            t_add = allmax(t_landed if rank == origin else -1e30)
+            if pr >= 2:                           # the first two probes warm the path up
+                lat.append(allmax(t_conv - t_add) / 1e9)
         # device time of a round under load: stop the engine thread and drive rounds by hand
         rep.stop_engine()
         barrier()
@@ -116,7 +126,7 @@ def main():
                 barrier()
         times = sorted(times[3:])
         round_ms = allmax(times[len(times) // 2])
-        links = sum(1 for e in st.stats()["edges"].values() if e["state"] == "connected")
+        links = 1 if args.topology == "mesh" else sum(1 for e in st.stats()["edges"].values() if e["state"] == "connected")
         max_links = int(allmax(float(links)))
         barrier()
         st.close()
@@ -140,18 +150,20 @@ def main():
                 ts.append(e0.elapsed_time(e1))
             ar_ms = allmax(sorted(ts)[len(ts) // 2])
         lat_ms = sorted(x * 1e3 for x in lat)
+        bits = st.cfg.bits
         hbm_bytes = (8 + 8 * max_links) * n  # values + one mirror per link, read and written
-        edge_bytes = 3 * (n / 8 + n / 32)   # three 1-bit frames with block-32 scales per round and edge direction
-        row = {"elements": n, "n_gpus": world, "round_ms": round_ms, "links_max": max_links,
+        edge_bytes = n * bits / 8 + n / 32   # one frame with block-32 scales per round and edge direction
+        row = {"elements": n, "n_gpus": world, "topology": args.topology, "frame_bits": bits, "round_ms": round_ms, "links_max": max_links,
                "round_hbm_GBs": hbm_bytes / round_ms / 1e6, "round_hbm_frac_of_measured": hbm_bytes / round_ms / 1e6 / hbm,
                "edge_bytes_per_round": edge_bytes, "edge_GBs": edge_bytes / round_ms / 1e6,
                "nvlink_roofline_ms": edge_bytes / 770e9 * 1e3, "hbm_roofline_ms": hbm_bytes / (hbm * 1e9) * 1e3,
-               "latency_ms_p50": lat_ms[len(lat_ms) // 2], "latency_ms_max": lat_ms[-1],
+               "latency_ms_p50": lat_ms[len(lat_ms) // 2], "latency_ms_max": lat_ms[-1], "latency_probes": len(lat_ms),
+               "latency_clock": "GPU clock stamps related through the host's monotonic clock",
                "nccl_allreduce_add_ms": ar_ms}
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
-        del init, deltas, expect, out
+        del init, deltas, expect_s, out
         torch.cuda.empty_cache()
     if rank == 0 and args.out:
         Path(args.out).write_text(json.dumps(rows, indent=1))

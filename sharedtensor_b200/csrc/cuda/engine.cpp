@@ -670,8 +670,13 @@ void GpuReplica::stop_engine() {
   engine_on_.store(false);
 }
 
+static uint64_t steady_ns() {
+  return uint64_t(std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count());
+}
+
 bool GpuReplica::wake(bool from_neighbour) {
   (void)from_neighbour;
+  last_wake_ns_.store(steady_ns());
   const bool was_idle = idle_.exchange(false);
   {
     std::lock_guard<std::mutex> g(wake_mu_);
@@ -751,6 +756,9 @@ void GpuReplica::engine_loop() {
         uint64_t shift = idle_rounds - 3 > 10 ? 10 : idle_rounds - 3;
         uint64_t us = 10ull << shift;
         if (us > uint64_t(cfg_.idle_sleep_us)) us = uint64_t(cfg_.idle_sleep_us);
+        // A local update or a neighbour's doorbell announces work that is still on its way (the update's kernel has
+        // to run first, the neighbour's frames have to cross the link): keep looking often for a few milliseconds.
+        if (steady_ns() - last_wake_ns_.load() < 5000000ull && us > 20) us = 20;
         idle_.store(true);
         idle_pause(us);  // a local update or a neighbour's doorbell ends it early
         if (!idle_.load()) idle_rounds = 0;

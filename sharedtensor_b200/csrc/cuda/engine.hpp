@@ -194,6 +194,7 @@ class GpuReplica {
   std::mutex engine_mu_;               // serialises start_engine / stop_engine
   std::thread engine_;
   std::atomic<bool> engine_on_{false}, engine_stop_{false};
+  std::atomic<uint64_t> last_wake_ns_{0};  // when wake() was last called (steady clock)
   std::atomic<bool> idle_{false};      // the engine has seen several rounds without work and pauses between rounds
   std::mutex wake_mu_;
   std::condition_variable wake_cv_;
