@@ -16,8 +16,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REF_DIR = HERE / "_ref"
-# where the reference checkout is mounted (override with SHAREDTENSOR_REFERENCE_DIR)
-REF_SRC = Path(os.environ.get("SHAREDTENSOR_REFERENCE_DIR", "/root/reference")) / "src" / "sharedtensor.c"
+# where the reference checkout lives: SHAREDTENSOR_REFERENCE_DIR, else a directory `reference` next to this repository
+REF_SRC = Path(os.environ.get("SHAREDTENSOR_REFERENCE_DIR", str(HERE.parent.parent / "reference"))) / "src" / "sharedtensor.c"
 LIB = REF_DIR / "libsharedtensor_ref.so"
 
 

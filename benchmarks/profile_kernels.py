@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--block", type=int, default=32)
     ap.add_argument("--shape", type=int, default=-1, help="CTA make-up of the round kernel (default: the library's)")
     ap.add_argument("--chunk", type=int, default=0)
+    ap.add_argument("--ctas", type=int, default=0, help="CTAs of the round kernel (0: one per SM)")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--only-round", action="store_true")
     ap.add_argument("--hub-mode", default="both", choices=["both", "rx", "tx"],
@@ -50,6 +51,7 @@ def main():
     if args.shape >= 0:
         cfg.shape = args.shape
     cfg.chunk_tiles = args.chunk
+    cfg.comm_ctas = args.ctas
     hub = cu.GpuReplica(0, n, cfg)
     if args.mesh:
         others = [cu.GpuReplica(0, n, cfg) for _ in range(args.mesh - 1)]
@@ -112,9 +114,10 @@ def main():
         timed("round(hub)", lambda: hub.round(args.hub_mode != "tx", args.hub_mode != "rx"), ext)
     med = {k: sorted(v)[len(v) // 2] for k, v in times.items()}
     pb = args.bits * 512 + max(16, 4096 // args.block)
-    # values read + reduce-add (read + write at the L2), mirrors read + written, frames read and written (local stand-ins
-    # for the peers' memory)
-    round_bytes = (4 + 8) * n + 8 * n_links * n + 2 * n_rings * (n // 4096) * pb
+    # values read and written back (the reduce-add of what arrived), every mirror read and written, the frames read; the
+    # frames written go to the peers' memory (here, with every replica on one GPU, they land in this GPU's memory too and
+    # are not counted)
+    round_bytes = 8 * n + 8 * n_links * n + n_rings * (n // 4096) * pb
     alg = {"add": 12 * n, "sub_add": 16 * n, "snapshot_f32": 8 * n, "snapshot_bf16": 6 * n, "add_scaled_bf16": 10 * n,
            "table_scales": 4 * n, "round(hub)": round_bytes}
     peaks_file = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"

@@ -18,6 +18,26 @@ from .utils.config import Config
 log = logging.getLogger("sharedtensor")
 
 
+class _Range:
+    """An NVTX range around an API call (``Config.nvtx`` / ``SHAREDTENSOR_NVTX=1``), so that a timeline shows where
+    the training loop talks to the shared tensor.  Costs nothing when switched off."""
+
+    __slots__ = ("on",)
+
+    def __init__(self, on: bool, name: str):
+        self.on = on and torch.cuda.is_available()
+        if self.on:
+            torch.cuda.nvtx.range_push(name)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def _check(t: torch.Tensor, n: int, device: torch.device, what: str) -> torch.Tensor:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{what}: expected a torch.Tensor, got {type(t).__name__}")
@@ -45,19 +65,22 @@ class SharedTensor:
     # --- reference API ---------------------------------------------------------------------
     def copyToTensor(self, t: torch.Tensor) -> torch.Tensor:
         """``t <- values`` (src/sharedtensor.c:435-446).  Per-element consistent snapshot."""
-        self._b.copy_to(_check(t, self._n, self._b.device, "copyToTensor"))
+        with _Range(self.cfg.nvtx, "sharedtensor.copyToTensor"):
+            self._b.copy_to(_check(t, self._n, self._b.device, "copyToTensor"))
         return t
 
     def addFromTensor(self, delta: torch.Tensor) -> None:
         """``values += delta`` locally; the change reaches every other replica asynchronously
         (src/sharedtensor.c:334-344, 448-453)."""
-        self._b.add(_check(delta, self._n, self._b.device, "addFromTensor"))
+        with _Range(self.cfg.nvtx, "sharedtensor.addFromTensor"):
+            self._b.add(_check(delta, self._n, self._b.device, "addFromTensor"))
 
     # --- additions -------------------------------------------------------------------------
     def pushUpdate(self, new: torch.Tensor, old: torch.Tensor) -> None:
         """``values += new - old`` in one pass (the README's ``addFromTensor(new:csub(current))``)."""
         dev = self._b.device
-        self._b.sub_add(_check(new, self._n, dev, "pushUpdate(new)"), _check(old, self._n, dev, "pushUpdate(old)"))
+        with _Range(self.cfg.nvtx, "sharedtensor.pushUpdate"):
+            self._b.sub_add(_check(new, self._n, dev, "pushUpdate(new)"), _check(old, self._n, dev, "pushUpdate(old)"))
 
     def copyToTensorBF16(self, t: torch.Tensor) -> torch.Tensor:
         """``t <- bf16(values)`` in one pass (GPU replicas; bf16 compute over fp32 master weights)."""
@@ -87,7 +110,8 @@ class SharedTensor:
 
     def flush(self, timeout: float = 30.0) -> bool:
         """Waits until this replica has nothing left to send and nothing arriving."""
-        return self._b.flush(timeout)
+        with _Range(self.cfg.nvtx, "sharedtensor.flush"):
+            return self._b.flush(timeout)
 
     def stats(self) -> dict:
         s = self._b.stats()
@@ -105,7 +129,7 @@ class SharedTensor:
         return self._b.trace() if hasattr(self._b, "trace") else []
 
     def state_dict(self) -> dict:
-        """Values plus per-edge mirrors, as CPU tensors (see ``utils.checkpoint``)."""
+        """The replica's values as a CPU tensor (see ``utils.checkpoint`` for why mirrors are not part of the state)."""
         return self._b.state_dict()
 
     def load_state_dict(self, state: dict) -> None:

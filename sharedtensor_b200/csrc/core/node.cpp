@@ -327,12 +327,17 @@ void CpuNode::rx_loop(Edge* e) {
       level = scale;
     } else {
       size_t ns = block_scales(n, B);
-      wtmp.resize(block_words(n));
-      std::memcpy(wtmp.data(), frame.data() + ns, 4 * wtmp.size());
-      decode_block_add_fast(wtmp.data(), frame.data(), n, B, values_.data(), e->mirror.data());
       int maxc = 0;
       for (size_t i = 0; i < ns; i++)
         if (frame[i] > maxc) maxc = frame[i];
+      if (maxc == 255) {  // no encoder emits this code (it would decode to infinity): the peer's stream is broken
+        lk.unlock();
+        edge_failed(e, "malformed frame (scale code)", IoStatus::Error);
+        break;
+      }
+      wtmp.resize(block_words(n));
+      std::memcpy(wtmp.data(), frame.data() + ns, 4 * wtmp.size());
+      decode_block_add_fast(wtmp.data(), frame.data(), n, B, values_.data(), e->mirror.data());
       level = maxc ? exp2i(maxc - 127) : 0.0f;
     }
     e->st.last_scale_recv = level;

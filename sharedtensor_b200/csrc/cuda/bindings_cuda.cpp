@@ -7,7 +7,6 @@
 
 #include "../core/codec.hpp"
 #include "engine.hpp"
-#include "gpu_node.hpp"
 #include "round.h"
 #include "vmm.hpp"
 
@@ -106,7 +105,8 @@ PYBIND11_MODULE(_cuda, m) {
       .def_readwrite("shape", &GpuConfig::shape)
       .def_readwrite("yield_to_updates", &GpuConfig::yield_to_updates)
       .def_readwrite("comm_high_priority", &GpuConfig::comm_high_priority)
-      .def_readwrite("chunk_tiles", &GpuConfig::chunk_tiles);
+      .def_readwrite("chunk_tiles", &GpuConfig::chunk_tiles)
+      .def_readwrite("window_tiles", &GpuConfig::window_tiles);
 
   py::class_<GpuReplica>(m, "GpuReplica")
       .def(py::init<int, int64_t, const GpuConfig&>())
@@ -134,6 +134,7 @@ PYBIND11_MODULE(_cuda, m) {
       .def("edge_block_is_vmm", [](GpuReplica& r, int id) { return !r.edge_block(id).plain; })
       .def("attach_peer", [](GpuReplica& r, int link, int block, uintptr_t remote) { return r.attach_peer(link, block, ptr<void>(remote)); })
       .def("detach_peer", &GpuReplica::detach_peer)
+      .def("unsend_unacknowledged", &GpuReplica::unsend_unacknowledged)
       .def("n_links", &GpuReplica::n_links)
       .def("n_peers", &GpuReplica::n_peers)
       .def("load_values", [](GpuReplica& r, uintptr_t src, uintptr_t s) { r.load_values(ptr<float>(src), strm(s)); })

@@ -260,65 +260,87 @@ constexpr int64_t kTsChunk = 1 << 16;  // elements per pass-1 CTA
 
 int64_t table_scales_scratch_doubles(int n_seg, int64_t n_total) { return n_total / kTsChunk + 2 * int64_t(n_seg) + 2; }
 
-// chunk c of the arena's chunk list: segment s covers chunks [first[s], first[s+1])
+// chunk c of the arena's chunk list: segment s covers chunks [first[s], first[s+1]).  A CTA walks over every
+// gridDim.x-th chunk; a thread keeps four independent 16-byte loads in flight and four independent sums.
 __global__ void __launch_bounds__(256) table_partial_kernel(const float* __restrict__ x, const int64_t* __restrict__ off, int n_seg,
-                                                            const int64_t* __restrict__ first_chunk, double* __restrict__ partials) {
+                                                            const int64_t* __restrict__ first_chunk, double* __restrict__ partials,
+                                                            int64_t max_chunks) {
   __shared__ double red[8];
   __shared__ int s_seg;
-  const int64_t c = blockIdx.x;
-  if (threadIdx.x == 0) {
-    int lo = 0, hi = n_seg - 1;  // last segment whose first chunk is <= c
-    while (lo < hi) {
-      int mid = (lo + hi + 1) / 2;
-      if (first_chunk[mid] <= c) lo = mid; else hi = mid - 1;
+  int64_t n_chunks = first_chunk[n_seg];
+  if (n_chunks > max_chunks) n_chunks = max_chunks;  // an inconsistent table never reaches past the scratch buffer
+  for (int64_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+    if (threadIdx.x == 0) {
+      int lo = 0, hi = n_seg - 1;  // last segment whose first chunk is <= c
+      while (lo < hi) {
+        int mid = (lo + hi + 1) / 2;
+        if (first_chunk[mid] <= c) lo = mid; else hi = mid - 1;
+      }
+      s_seg = lo;
     }
-    s_seg = lo;
-  }
-  __syncthreads();
-  const int seg = s_seg;
-  const int64_t begin = off[seg] + (c - first_chunk[seg]) * kTsChunk;
-  const int64_t end = min(begin + kTsChunk, off[seg + 1]);
-  double acc = 0.0;
-  // 16-byte loads over the aligned middle of the chunk, scalar loads at its ragged ends
-  int64_t a0 = (begin + 3) & ~int64_t(3);
-  if (a0 > end) a0 = end;
-  const int64_t a1 = a0 + ((end - a0) & ~int64_t(3));
-  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-    for (int64_t i = begin + threadIdx.x; i < a0; i += 256) acc += double(x[i]) * double(x[i]);
-    const float4* x4 = reinterpret_cast<const float4*>(x);
-    for (int64_t i = a0 / 4 + threadIdx.x; i < a1 / 4; i += 256) {
-      float4 v = ldg_stream(x4 + i);
-      acc += (double(v.x) * double(v.x) + double(v.y) * double(v.y)) + (double(v.z) * double(v.z) + double(v.w) * double(v.w));
+    __syncthreads();
+    const int seg = s_seg;
+    const int64_t begin = off[seg] + (c - first_chunk[seg]) * kTsChunk;
+    const int64_t end = min(begin + kTsChunk, off[seg + 1]);
+    double acc = 0.0;
+    // 16-byte loads over the aligned middle of the chunk, scalar loads at its ragged ends
+    int64_t a0 = (begin + 3) & ~int64_t(3);
+    if (a0 > end) a0 = end;
+    const int64_t a1 = a0 + ((end - a0) & ~int64_t(3));
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+      for (int64_t i = begin + threadIdx.x; i < a0; i += 256) acc += double(x[i]) * double(x[i]);
+      const float4* x4 = reinterpret_cast<const float4*>(x);
+      const int64_t q1 = a1 / 4;
+      int64_t i = a0 / 4 + threadIdx.x;
+      double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+      for (; i + 768 < q1; i += 1024) {
+        const float4 v0 = ldg_stream(x4 + i), v1 = ldg_stream(x4 + i + 256), v2 = ldg_stream(x4 + i + 512), v3 = ldg_stream(x4 + i + 768);
+        s0 += (double(v0.x) * double(v0.x) + double(v0.y) * double(v0.y)) + (double(v0.z) * double(v0.z) + double(v0.w) * double(v0.w));
+        s1 += (double(v1.x) * double(v1.x) + double(v1.y) * double(v1.y)) + (double(v1.z) * double(v1.z) + double(v1.w) * double(v1.w));
+        s2 += (double(v2.x) * double(v2.x) + double(v2.y) * double(v2.y)) + (double(v2.z) * double(v2.z) + double(v2.w) * double(v2.w));
+        s3 += (double(v3.x) * double(v3.x) + double(v3.y) * double(v3.y)) + (double(v3.z) * double(v3.z) + double(v3.w) * double(v3.w));
+      }
+      for (; i < q1; i += 256) {
+        const float4 v = ldg_stream(x4 + i);
+        s0 += (double(v.x) * double(v.x) + double(v.y) * double(v.y)) + (double(v.z) * double(v.z) + double(v.w) * double(v.w));
+      }
+      acc += (s0 + s1) + (s2 + s3);
+      for (int64_t j = a1 + threadIdx.x; j < end; j += 256) acc += double(x[j]) * double(x[j]);
+    } else {
+      for (int64_t i = begin + threadIdx.x; i < end; i += 256) {
+        float v = x[i];
+        acc += double(v) * double(v);
+      }
     }
-    for (int64_t i = a1 + threadIdx.x; i < end; i += 256) acc += double(x[i]) * double(x[i]);
-  } else {
-    for (int64_t i = begin + threadIdx.x; i < end; i += 256) {
-      float v = x[i];
-      acc += double(v) * double(v);
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double t = 0.0;
+      for (int w = 0; w < 8; w++) t += red[w];
+      partials[c] = t;
     }
-  }
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    double t = 0.0;
-    for (int w = 0; w < 8; w++) t += red[w];
-    partials[c] = t;
+    __syncthreads();  // red and s_seg are reused by the next chunk
   }
 }
 __global__ void table_final_kernel(const int64_t* __restrict__ off, int n_seg, const int64_t* __restrict__ first_chunk,
-                                   const double* __restrict__ partials, double* __restrict__ out_sumsq, int8_t* __restrict__ out_exp) {
+                                   const double* __restrict__ partials, double* __restrict__ out_sumsq, int8_t* __restrict__ out_exp,
+                                   int64_t max_chunks) {
   int seg = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   if (seg >= n_seg) return;
   const int lane = threadIdx.x & 31;
   double acc = 0.0;
-  for (int64_t c = first_chunk[seg] + lane; c < first_chunk[seg + 1]; c += 32) acc += partials[c];
+  const int64_t c0 = first_chunk[seg], c1 = first_chunk[seg + 1];
+  const bool consistent = c0 >= 0 && c0 <= c1 && c1 <= max_chunks;  // offsets that ascend and end where the caller said
+  if (consistent)
+    for (int64_t c = c0 + lane; c < c1; c += 32) acc += partials[c];
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) {
-    out_sumsq[seg] = acc;
     int64_t cnt = off[seg + 1] - off[seg];
     int e = -128;
-    if (cnt > 0 && acc > 0.0) {
+    if (!consistent) {
+      acc = __longlong_as_double(0x7ff8000000000000LL);  // NaN: the table contradicts n_total
+    } else if (cnt > 0 && acc > 0.0) {
       double rms = sqrt(acc / double(cnt));
       int ex;
       frexp(rms, &ex);
@@ -326,6 +348,7 @@ __global__ void table_final_kernel(const int64_t* __restrict__ off, int n_seg, c
       if (e < -126) e = -128;
       if (e > 127) e = 127;
     }
+    out_sumsq[seg] = acc;
     out_exp[seg] = int8_t(e);
   }
 }
@@ -334,7 +357,8 @@ __global__ void table_chunks_kernel(const int64_t* __restrict__ off, int n_seg, 
     int64_t c = 0;
     for (int s = 0; s < n_seg; s++) {
       first_chunk[s] = c;
-      c += (off[s + 1] - off[s] + kTsChunk - 1) / kTsChunk;
+      const int64_t len = off[s + 1] - off[s];
+      c += len > 0 ? (len + kTsChunk - 1) / kTsChunk : 0;
     }
     first_chunk[n_seg] = c;
   }
@@ -346,12 +370,12 @@ int launch_table_scales(const float* x, const int64_t* seg_offsets_dev, int n_se
   // scratch layout: [first_chunk: n_seg+1 int64][partials: up to n_total/chunk + n_seg doubles]
   int64_t* first_chunk = reinterpret_cast<int64_t*>(scratch);
   double* partials = scratch + (n_seg + 1);
-  int64_t max_chunks = n_total / kTsChunk + n_seg;
+  const int64_t max_chunks = n_total / kTsChunk + n_seg;  // holds for offsets that ascend from 0 to n_total
   table_chunks_kernel<<<1, 32, 0, s>>>(seg_offsets_dev, n_seg, first_chunk);
-  // the exact chunk count lives on the device; launching the upper bound is harmless because the
-  // surplus CTAs map to chunks past the end of the last segment and add zero-length ranges
-  table_partial_kernel<<<unsigned(max_chunks), 256, 0, s>>>(x, seg_offsets_dev, n_seg, first_chunk, partials);
-  table_final_kernel<<<(n_seg + 7) / 8, 256, 0, s>>>(seg_offsets_dev, n_seg, first_chunk, partials, out_sumsq, out_exp);
+  // the exact chunk count lives on the device: a grid of at most eight CTAs per SM walks over the chunks there are
+  const int64_t grid = max_chunks < 148 * 8 ? (max_chunks < 1 ? 1 : max_chunks) : 148 * 8;
+  table_partial_kernel<<<unsigned(grid), 256, 0, s>>>(x, seg_offsets_dev, n_seg, first_chunk, partials, max_chunks);
+  table_final_kernel<<<(n_seg + 7) / 8, 256, 0, s>>>(seg_offsets_dev, n_seg, first_chunk, partials, out_sumsq, out_exp, max_chunks);
   return int(cudaGetLastError());
 }
 

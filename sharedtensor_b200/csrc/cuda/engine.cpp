@@ -91,7 +91,7 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   check(cudaEventCreateWithFlags(&e2, cudaEventDisableTiming), "cudaEventCreate");
   ev_user_ = e1;
   ev_comm_ = e2;
-  for (int i = 0; i < (cfg.rounds_in_flight < 1 ? 1 : cfg.rounds_in_flight); i++) {
+  for (int i = 0; i < (cfg.rounds_in_flight < 1 ? 1 : (cfg.rounds_in_flight > 4 ? 4 : cfg.rounds_in_flight)); i++) {
     cudaEvent_t e;
     check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
     ev_round_.push_back(e);
@@ -247,6 +247,28 @@ int GpuReplica::attach_peer(int link, int local_block, void* remote_base) {
     }
   }
   return -1;
+}
+
+uint64_t GpuReplica::unsend_unacknowledged(int peer) {
+  DeviceGuard g(device_);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (peer < 0 || peer >= kMaxRings || !peers_[peer].used) return 0;
+  publish_pending();
+  Peer& p = peers_[peer];
+  uint8_t* local = static_cast<uint8_t*>(blocks_[p.local_block].mem.ptr);
+  uint64_t* dev_count = nullptr;
+  check(cudaMalloc(reinterpret_cast<void**>(&dev_count), 8), "cudaMalloc");
+  check(cudaMemsetAsync(dev_count, 0, 8, S(comm_)), "memset");
+  check(launch_unsend(mirror(p.link), p.remote + layout_.off_payload, p.tx_seq, reinterpret_cast<const uint32_t*>(local + layout_.off_credit),
+                      n_tiles_, cfg_.ring_slots, params_.payload_bytes, params_.log2_block, cfg_.bits, n_, dev_count, comm_),
+        "unsend kernel");
+  uint64_t host = 0;
+  check(cudaMemcpyAsync(status_host_ + kDsTotalWords + 8, dev_count, 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
+  check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
+  host = status_host_[kDsTotalWords + 8];
+  cudaFree(dev_count);
+  launches_ += 1;
+  return host;
 }
 
 void GpuReplica::detach_peer(int peer) {
@@ -454,15 +476,20 @@ void GpuReplica::add_gate_held(const float* delta) {
   launches_ += 2;
 }
 
+// A snapshot sits on the training loop's critical path like an update does: it asks for the SMs too.
 void GpuReplica::snapshot(float* out, void* user_stream) {
   DeviceGuard g(device_);
+  ask_for_sms(user_stream, true);
   check(launch_snapshot_f32(values(), out, n_, user_stream), "snapshot kernel");
+  ask_for_sms(user_stream, false);
   launches_ += 1;
 }
 
 void GpuReplica::snapshot_bf16(void* out, void* user_stream) {
   DeviceGuard g(device_);
+  ask_for_sms(user_stream, true);
   check(launch_snapshot_bf16(values(), out, n_, user_stream), "snapshot kernel");
+  ask_for_sms(user_stream, false);
   launches_ += 1;
 }
 
@@ -482,23 +509,33 @@ void GpuReplica::push_snapshot(int link, float* remote_values) {
   check(cudaStreamSynchronize(S(comm_)), "snapshot_join");
 }
 
-// How a launch covers the tensor: the grid, and how many consecutive tiles a group owns (0: every n-th tile).
-void GpuReplica::grid_for_launch(int* grid, int* chunk, int* tiles_per_group) const {
+// A long pass would hold every SM for its whole duration; the tensor is therefore covered in windows, one launch
+// each, so that kernels of other streams get their turn between two launches.
+int GpuReplica::window_tiles() const {
+  if (cfg_.window_tiles > 0) return cfg_.window_tiles < n_tiles_ ? cfg_.window_tiles : n_tiles_;
+  return n_tiles_ > 8192 ? 6144 : n_tiles_;   // 25 M elements, about 0.15 ms of a one-link pass
+}
+int GpuReplica::n_windows() const {
+  const int w = window_tiles();
+  return (n_tiles_ + w - 1) / w;
+}
+
+// How a launch covers its window: the grid, and how many consecutive tiles a group owns (0: every n-th tile).
+void GpuReplica::grid_for_launch(int tiles, int* grid, int* chunk, int* tiles_per_group) const {
   const int groups_per_cta = round_shape_groups(cfg_.shape);
   if (cfg_.chunk_tiles > 0) {
-    // many short-lived CTAs: a group takes a run of `chunk_tiles` consecutive tiles and leaves, so that kernels of
-    // other streams get SMs between two CTAs of a long launch
+    // many short-lived CTAs: a group takes a run of `chunk_tiles` consecutive tiles and leaves
     const int t = cfg_.chunk_tiles;
     *chunk = t;
-    *grid = (n_tiles_ + t * groups_per_cta - 1) / (t * groups_per_cta);
+    *grid = (tiles + t * groups_per_cta - 1) / (t * groups_per_cta);
     *tiles_per_group = t;
   } else {
-    // one CTA per SM for the whole launch, a group walks through every n-th tile
-    const int needed = (n_tiles_ + groups_per_cta - 1) / groups_per_cta;
+    // one CTA per SM for the whole launch, a group walks through every n-th tile of the window
+    const int needed = (tiles + groups_per_cta - 1) / groups_per_cta;
     const int g = ctas_ < needed ? ctas_ : needed;
     *chunk = 0;
     *grid = g < 1 ? 1 : g;
-    *tiles_per_group = (n_tiles_ + *grid * groups_per_cta - 1) / (*grid * groups_per_cta);
+    *tiles_per_group = (tiles + *grid * groups_per_cta - 1) / (*grid * groups_per_cta);
   }
 }
 
@@ -507,22 +544,30 @@ int GpuReplica::auto_sweeps() const {
   // Small tensors: a pass takes a few microseconds, so one launch makes several and the host's launch latency is
   // paid once per batch.  Large tensors: a pass is long enough by itself.
   int grid, chunk, per_group;
-  grid_for_launch(&grid, &chunk, &per_group);
+  grid_for_launch(window_tiles(), &grid, &chunk, &per_group);
   int sw = 32 / (per_group < 1 ? 1 : per_group);
   return sw < 1 ? 1 : (sw > 16 ? 16 : sw);
 }
 
+// One launch: window `next_window_` of the current cycle.
 void GpuReplica::launch(bool do_rx, bool do_tx, int sweeps) {
+  const int wt = window_tiles(), nw = n_windows();
+  const int w = next_window_;
+  params_.tile_begin = w * wt;
+  params_.tile_count = (w == nw - 1) ? n_tiles_ - w * wt : wt;
   params_.round = round_no_++;
-  params_.parity = params_.round & 1;
+  params_.parity = cycle_no_ & 1;
+  params_.zero_other = w == 0 ? 1 : 0;
   params_.do_rx = do_rx ? 1 : 0;
   params_.do_tx = do_tx ? 1 : 0;
   params_.sweeps = sweeps < 1 ? 1 : sweeps;
   int grid, chunk, per_group;
-  grid_for_launch(&grid, &chunk, &per_group);
+  grid_for_launch(params_.tile_count, &grid, &chunk, &per_group);
   params_.chunk = chunk;
   check(launch_round(params_, cfg_.shape, grid, comm_), "round kernel");
   last_parity_ = params_.parity;
+  next_window_ = (w + 1) % nw;
+  if (next_window_ == 0) cycle_no_++;
   launches_ += 1;
   epoch_++;
 }
@@ -531,7 +576,10 @@ void GpuReplica::round(bool do_rx, bool do_tx, int sweeps) {
   DeviceGuard g(device_);
   std::lock_guard<std::mutex> lk(mu_);
   if (params_.n_in == 0 && params_.n_out == 0) return;
-  launch(do_rx, do_tx, sweeps);
+  // one pass over the whole tensor: the rest of the cycle in progress (if the engine thread left one), or a full cycle
+  do {
+    launch(do_rx, do_tx, sweeps);
+  } while (next_window_ != 0);
 }
 
 float GpuReplica::tcp_encode(int link, uint32_t* words, float min_scale_abs, float min_scale_rel) {
@@ -622,7 +670,9 @@ std::vector<uint64_t> GpuReplica::status() {
   check(cudaMemcpyAsync(status_host_, status_, kDsTotalWords * 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
   check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
   std::memcpy(dev.data(), status_host_, kDsTotalWords * 8);
-  const uint64_t* lw = dev.data() + (last_parity_ ? kDsLaunch1 : kDsLaunch0);
+  // the counters of the last cycle that is complete (a cycle in progress has only seen some windows)
+  const int par = next_window_ == 0 ? last_parity_ : (last_parity_ ^ 1);
+  const uint64_t* lw = dev.data() + (par ? kDsLaunch1 : kDsLaunch0);
   std::vector<uint64_t> out(kStTotalWords, 0);
   out[kStRounds] = dev[kDsSweeps];
   out[kStTilesProcessed] = dev[kDsTilesProcessed];
@@ -718,19 +768,23 @@ void GpuReplica::engine_loop() {
   ::prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);  // 1 us instead of the default 50 us: the idle pauses start at 10 us
   const size_t depth = ev_round_.size();
   // one pinned word per launch in flight: how many tiles that launch handled
-  uint64_t* work_host = status_host_ + kDsTotalWords;  // behind the part status() uses
+  uint64_t* work_host = status_host_ + kDsTotalWords;  // behind the part status() uses: tiles handled so far, after a launch
+  uint64_t* work_before = work_host + 4;               // ... and before it
   uint64_t r = 0;
   uint64_t idle_rounds = 0;
+  uint64_t quiet_launches = 0;   // launches in a row that found nothing to do
   while (!engine_stop_.load()) {
     bool launched = false;
+    int windows = 1;
     try {
       std::lock_guard<std::mutex> lk(mu_);
       if (params_.n_in + params_.n_out > 0) {
         // One launch makes several passes over a small tensor and returns; nothing on the device waits for this
         // thread, which only starts the next launch and reads how much the last one found to do.
+        windows = n_windows();
+        cudaMemcpyAsync(work_before + (r % depth), status_ + kDsTilesProcessed, 8, cudaMemcpyDeviceToHost, S(comm_));
         launch(true, true, auto_sweeps());
-        cudaMemcpyAsync(work_host + (r % depth), status_ + (last_parity_ ? kDsLaunch1 : kDsLaunch0) + kDlWork, 8, cudaMemcpyDeviceToHost,
-                        S(comm_));
+        cudaMemcpyAsync(work_host + (r % depth), status_ + kDsTilesProcessed, 8, cudaMemcpyDeviceToHost, S(comm_));
         cudaEventRecord(E(ev_round_[r % depth]), S(comm_));
         launched = true;
       }
@@ -745,9 +799,11 @@ void GpuReplica::engine_loop() {
     uint64_t work = 1;
     if (r >= depth) {
       cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
-      work = work_host[(r - depth) % depth];
+      work = work_host[(r - depth) % depth] - work_before[(r - depth) % depth];
     }
     if (work != 0) epoch_++;
+    quiet_launches = work == 0 ? quiet_launches + 1 : 0;
+    if (work == 0 && quiet_launches < uint64_t(windows)) continue;  // the other windows of the tensor have not been looked at yet
     if (work == 0) {
       // nothing moved: back off from 10 us up to idle_sleep_us, so that a fresh update is picked up quickly after a
       // burst and an idle replica costs next to nothing
@@ -762,6 +818,7 @@ void GpuReplica::engine_loop() {
         idle_.store(true);
         idle_pause(us);  // a local update or a neighbour's doorbell ends it early
         if (!idle_.load()) idle_rounds = 0;
+        quiet_launches = 0;  // after a pause the whole tensor is looked at again before the next one
       }
     } else {
       idle_.store(false);

@@ -45,6 +45,7 @@ struct GpuConfig {
   bool yield_to_updates = true;  // a running round kernel gives up its SMs when addFromTensor has an update ready
   bool comm_high_priority = false;  // comm stream at the highest stream priority (switches yield_to_updates off)
   int chunk_tiles = 0;       // > 0: short-lived CTAs, a group takes this many consecutive tiles (0: one CTA per SM per launch)
+  int window_tiles = 0;      // tiles a launch covers (0: 6144 for tensors above 8192 tiles, else the whole tensor)
 };
 
 constexpr size_t kGuardBytes = 256;  // canary before and after every mirror, edge block and the values
@@ -79,6 +80,9 @@ class GpuReplica {
   // at `remote_base` in this process (same layout).  Returns a peer id.
   int attach_peer(int link, int local_block, void* remote_base);
   void detach_peer(int peer);
+  // The neighbour behind `peer` is gone: the frames it never acknowledged (they are still in its ring, which stays
+  // mapped) are taken off the link's mirror again.  Returns how many tile-frames that were.  Call before detach_peer.
+  uint64_t unsend_unacknowledged(int peer);
   int n_links() const;
   int n_peers() const;
 
@@ -154,7 +158,9 @@ class GpuReplica {
   void publish_pending();              // under mu_
   void launch(bool do_rx, bool do_tx, int sweeps);  // under mu_
   int auto_sweeps() const;
-  void grid_for_launch(int* grid, int* chunk, int* tiles_per_group) const;
+  void grid_for_launch(int tiles, int* grid, int* chunk, int* tiles_per_group) const;
+  int window_tiles() const;
+  int n_windows() const;
   void fill_guards(const VmmBlock& b, size_t used_bytes);
   void ask_for_sms(void* user_stream, bool on);
   void check(int cuda_err, const char* what);
@@ -182,7 +188,9 @@ class GpuReplica {
   RoundParams params_{};
   int map_link_[kMaxLinks] = {0, 0, 0};  // dense link index of each link id
   int round_no_ = 0;
-  int last_parity_ = 0;                // which half of the per-launch status words the last launch used
+  int last_parity_ = 0;                // which half of the per-cycle status words the last launch used
+  int next_window_ = 0;                // the window of the tensor the next launch covers
+  int cycle_no_ = 0;                   // passes over the whole tensor started so far
   int ctas_ = 148;
   int sms_ = 148;
   void* comm_ = nullptr;               // cudaStream_t

@@ -14,7 +14,9 @@
  * passes every input and output.
  *
  * Limits (checked, see the error codes): at most ST_NOALLOC_MAX_SEGMENTS tensors and
- * ST_NOALLOC_MAX_ELEMENTS elements in total.
+ * ST_NOALLOC_MAX_ELEMENTS elements in total.  The offsets live on the device, so the host cannot check them:
+ * n_total has to be the last offset and the offsets have to ascend.  A table that contradicts n_total never
+ * makes the kernels reach past the scratch array; the tensors concerned come back with NaN as their energy.
  *
  * First call on a device: the address of the array on the CURRENT device is looked up once
  * (cudaGetSymbolAddress) and remembered.  Make that first call with the right device current and before

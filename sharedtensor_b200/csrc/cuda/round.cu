@@ -787,11 +787,13 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
   // I/O warp.  All 32 lanes run the same control flow; lane 0 issues copies, stores and flags.
   // ===========================================================================================
   // The group's tiles: a run of `chunk` consecutive tiles, or (chunk == 0) every gstride-th tile of the tensor.
+  // (of the launch's window of the tensor, tiles tile_begin .. tile_begin + tile_count - 1)
   const int gidx = int(blockIdx.x) * kGroups + g;
-  const int gid = p.chunk > 0 ? gidx * p.chunk : gidx;
+  const int gid0 = p.chunk > 0 ? gidx * p.chunk : gidx;
   const int gstride = p.chunk > 0 ? 1 : int(gridDim.x) * kGroups;
-  const int my_count = p.chunk > 0 ? max(0, min(p.chunk, p.n_tiles - gid))
-                                   : (p.n_tiles > gid ? (p.n_tiles - gid + gstride - 1) / gstride : 0);
+  const int my_count = p.chunk > 0 ? max(0, min(p.chunk, p.tile_count - gid0))
+                                   : (p.tile_count > gid0 ? (p.tile_count - gid0 + gstride - 1) / gstride : 0);
+  const int gid = p.tile_begin + gid0;
   const uint32_t smask = uint32_t(p.ring_slots) - 1u;
   uint32_t issued = 0, retired = 0;
   unsigned long long n_done = 0, n_tx = 0, n_rx = 0, n_blocked = 0, n_pending = 0, n_sweeps = 0;
@@ -800,8 +802,8 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
   long long tm_done = 0, tm_read = 0, tm_pubwait = 0, tm_pub = 0, tm_scout = 0, tm_issue = 0, tm_store = 0, tm_pf = 0, tm_io0 = clock64();
 #endif
 
-  if (blockIdx.x == 0 && g == 0 && lane == 0) {
-    uint64_t* other = p.status + (p.parity ? kDsLaunch0 : kDsLaunch1);  // the next launch's half
+  if (p.zero_other && blockIdx.x == 0 && g == 0 && lane == 0) {
+    uint64_t* other = p.status + (p.parity ? kDsLaunch0 : kDsLaunch1);  // the next cycle's half
     for (int i = 0; i < 8; i++) other[i] = 0;
   }
 
@@ -1135,6 +1137,61 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
       (void)r;
     }
   }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Taking frames back.  When a neighbour is lost, the frames it never acknowledged (sequence numbers from its last
+// credit up to what was sent) are still in its ring, which stays mapped here; their steps come off the mirror again,
+// so that what they said counts as not yet told (the TCP edges do the same with a frame whose write fails).
+// One CTA per tile, thread t its 32 elements, the same element order as the round kernel.
+// ----------------------------------------------------------------------------------------------
+template <int Q>
+__global__ void __launch_bounds__(kGroupThreads) unsend_kernel(float* __restrict__ mirror, const uint8_t* __restrict__ payload,
+                                                               uint32_t* __restrict__ tx_seq, const uint32_t* __restrict__ credit,
+                                                               int n_tiles, int ring_slots, int pb, int log2_block, int64_t n,
+                                                               unsigned long long* __restrict__ taken_back) {
+  const int tile = blockIdx.x, t = threadIdx.x, sw = t & 7, tpb = log2_block - 5;
+  const uint32_t c = ld_acquire_sys(credit + tile), tx = ld_cg_u32(tx_seq + tile);
+  const uint32_t count = tx - c;
+  if (count == 0 || count > uint32_t(ring_slots)) return;
+  const int64_t left = n - (int64_t(tile) * kTile + int64_t(t) * 32);
+  const uint32_t vmask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << int(left)) - 1u));
+  const bool masked = (Q == 1) && left < 32;
+  float4 acc[8];
+#pragma unroll
+  for (int q = 0; q < 8; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t f = 0; f < count; f++) {
+    const uint8_t* fp = payload + (size_t((c + f) & uint32_t(ring_slots - 1)) * n_tiles + tile) * pb;
+    uint32_t w[Q], code;
+    load_frame<Q>(fp, t, tpb, w, code);
+    if (masked) add_frame<Q, true>(acc, w, code, sw, vmask); else add_frame<Q, false>(acc, w, code, sw, vmask);
+  }
+  float4* k4 = reinterpret_cast<float4*>(mirror + size_t(tile) * kTile) + t * 8;
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    float4 k = k4[q ^ sw];
+    k.x = __fsub_rn(k.x, acc[q].x); k.y = __fsub_rn(k.y, acc[q].y); k.z = __fsub_rn(k.z, acc[q].z); k.w = __fsub_rn(k.w, acc[q].w);
+    k4[q ^ sw] = k;
+  }
+  __syncthreads();
+  if (t == 0) {
+    st_cg_u32(tx_seq + tile, c);
+    atomicAdd(taken_back, (unsigned long long)count);
+  }
+}
+
+int launch_unsend(float* mirror, const uint8_t* payload_remote, uint32_t* tx_seq, const uint32_t* credit, int n_tiles, int ring_slots,
+                  int payload_bytes, int log2_block, int bits, int64_t n, uint64_t* taken_back, void* stream_v) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream_v);
+  unsigned long long* tb = reinterpret_cast<unsigned long long*>(taken_back);
+  switch (bits) {
+    case 1: unsend_kernel<1><<<n_tiles, kGroupThreads, 0, s>>>(mirror, payload_remote, tx_seq, credit, n_tiles, ring_slots, payload_bytes, log2_block, n, tb); break;
+    case 2: unsend_kernel<2><<<n_tiles, kGroupThreads, 0, s>>>(mirror, payload_remote, tx_seq, credit, n_tiles, ring_slots, payload_bytes, log2_block, n, tb); break;
+    case 4: unsend_kernel<4><<<n_tiles, kGroupThreads, 0, s>>>(mirror, payload_remote, tx_seq, credit, n_tiles, ring_slots, payload_bytes, log2_block, n, tb); break;
+    case 8: unsend_kernel<8><<<n_tiles, kGroupThreads, 0, s>>>(mirror, payload_remote, tx_seq, credit, n_tiles, ring_slots, payload_bytes, log2_block, n, tb); break;
+    default: return int(cudaErrorInvalidValue);
+  }
+  return int(cudaGetLastError());
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -71,7 +71,9 @@ struct RoundParams {
   uint32_t* tile_state;          // [tile]: non-zero = the values of the tile may have changed since its last visit
   uint64_t* status;              // see DevStatus
   int32_t round;                 // number of this launch's first sweep (bookkeeping only)
-  int32_t parity;                // which half of the per-launch counters this launch uses
+  int32_t tile_begin, tile_count; // the window of the tensor this launch covers
+  int32_t parity;                // which half of the per-cycle counters this launch uses (a cycle = one pass over all windows)
+  int32_t zero_other;            // first launch of a cycle: clear the other half for the cycle after this one
   int32_t do_rx, do_tx;          // receiver-only / sender-only launches
   int32_t sweeps;                // passes over the tensor in this launch (>= 1)
   uint32_t wait_ns;              // upper bound of every wait on one of the kernel's own copies
@@ -81,8 +83,9 @@ struct RoundParams {
   uint32_t* dbg;                 // debug builds: progress marks in mapped host memory, 8 words per CTA (else null)
 };
 
-// Layout of the device status block (uint64 each).  Counters are cumulative; the per-launch words exist twice and a
-// launch uses the half given by RoundParams::parity (and clears the other half for the launch after it).
+// Layout of the device status block (uint64 each).  Counters are cumulative; the per-cycle words exist twice, the
+// launches of a cycle (one launch per window of the tensor) use the half given by RoundParams::parity and the first of
+// them clears the other half for the cycle after it.
 enum DevStatus : int {
   kDsSweeps = 0,
   kDsTilesProcessed,
@@ -125,6 +128,10 @@ enum StatusWord : int {
 // A group is 4 compute warps and one I/O warp; a CTA has one more warp that publishes flags and credits.
 int launch_round(const RoundParams& p, int shape, int ctas, void* stream);
 int round_shape_groups(int shape);
+// Takes back the frames of one out-ring that the receiver never acknowledged: their steps are subtracted from the
+// link's mirror and the ring's send counters fall back to the credits.  *taken_back (device) counts the tile-frames.
+int launch_unsend(float* mirror, const uint8_t* payload_remote, uint32_t* tx_seq, const uint32_t* credit, int n_tiles, int ring_slots,
+                  int payload_bytes, int log2_block, int bits, int64_t n, uint64_t* taken_back, void* stream);
 int round_smem_bytes(int groups, int slots, int payload_bytes);
 
 // Element-wise kernels (copyToTensor / addFromTensor / pushUpdate; src/sharedtensor.c:435-446, 334-344).

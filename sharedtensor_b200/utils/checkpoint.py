@@ -16,7 +16,9 @@ import torch
 
 
 def save(shared: Any, path: str, extra: dict | None = None) -> None:
-    """Writes ``shared.state_dict()`` (values, and mirrors where the backend exposes them) atomically."""
+    """Writes ``shared.state_dict()`` atomically.  The state is the replica's values.  Mirrors are not part of it: a
+    mirror says what one particular neighbour holds, and a replica that comes back from a file meets new neighbours,
+    whose links start from a snapshot (GPU edges) or from zero (TCP edges, as in the reference)."""
     state = {"state": shared.state_dict(), "numel": shared.numel, "shape": tuple(shared.shape), "extra": extra or {}}
     d = os.path.dirname(os.path.abspath(path))
     fd, tmp = tempfile.mkstemp(dir=d, suffix=".tmp")

@@ -43,6 +43,7 @@ class Config:
     yield_to_updates: bool = True    # a running round kernel gives up its SMs when addFromTensor has an update ready
     comm_high_priority: bool = False # comm stream at the highest stream priority (then rounds do not yield to updates)
     use_multimem: bool = False       # reserved: NVLS store fan-out is not built (plain peer stores only)
+    nvtx: bool = False               # NVTX ranges around the API calls (copyToTensor, addFromTensor, pushUpdate, flush)
     # --- TCP edges ------------------------------------------------------------------------------
     max_frames_per_s: float = 0.0    # rate cap per edge (README.md:31 of the reference lists this as a TODO)
     idle_keepalive_ms: int = 0

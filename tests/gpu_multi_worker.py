@@ -13,6 +13,14 @@ import torch  # noqa: E402
 import sharedtensor  # noqa: E402
 
 
+
+def emit(res: dict) -> None:
+    """One result line per worker; it also says which physical GPU the rank ran on."""
+    d = torch.cuda.current_device()
+    res["device"] = d
+    res["device_uuid"] = str(torch.cuda.get_device_properties(d).uuid)
+    print(json.dumps(res), flush=True)
+
 def _touch_and_wait(sync_dir, name, wanted, timeout=100.0):
     """File rendezvous between the worker processes: start-up time (first CUDA context on a fresh machine) varies by
     seconds, so ordering by sleeps alone is not enough."""
@@ -53,8 +61,8 @@ def train(rank, world, port, sync_dir, dev):
     st.copyToTensor(out)
     torch.cuda.synchronize()
     s = st.stats()
-    print(json.dumps({"rank": rank, "loss_first": log.loss[0], "loss_last": log.loss[-1], "checksum": float(out.double().sum()),
-                      "norm": float(out.double().norm()), "errors": s["device"]["errors"], "rounds": s["device"]["rounds"]}), flush=True)
+    emit({"rank": rank, "loss_first": log.loss[0], "loss_last": log.loss[-1], "checksum": float(out.double().sum()),
+                      "norm": float(out.double().norm()), "errors": s["device"]["errors"], "rounds": s["device"]["rounds"]})
     _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(world)])
     time.sleep(0.2 + 0.3 * (world - rank))
     st.close()
@@ -104,7 +112,7 @@ def rejoin(rank, world, port, n, sync_dir, dev):
     res["errors"] = s["device"]["errors"]
     res["edge_failures"] = s.get("edge_failures", 0)
     res["edges"] = {k: v["state"] for k, v in s["edges"].items()}
-    print(json.dumps(res), flush=True)
+    emit(res)
     _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(world)])
     time.sleep(0.2 + 0.3 * (world - rank))
     st.close()
@@ -145,7 +153,7 @@ def master_leaves(rank, world, port, n, sync_dir, dev):
         time.sleep(0.3)
         st.close()  # nothing in flight: leaves between steps
         (Path(sync_dir) / "left").touch()
-        print(json.dumps({"rank": 0, "left": True}), flush=True)
+        emit({"rank": 0, "left": True})
         return
     res = {"rank": rank, "rel_before": wait_for(init + d[0], 30)}
     st.flush(10.0)
@@ -165,7 +173,7 @@ def master_leaves(rank, world, port, n, sync_dir, dev):
     res["master"] = bool(s["master"])
     res["errors"] = s["device"]["errors"]
     res["rejoins"] = s["rejoins"]
-    print(json.dumps(res), flush=True)
+    emit(res)
     _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(1, world)])
     time.sleep(0.2 + (0.0 if res["master"] else 0.0) + (0.6 if res["master"] else 0.0))  # the new master leaves last
     st.close()
@@ -210,7 +218,7 @@ def main():
         st.flush(10.0)
         time.sleep(0.5)
         res["exiting"] = True
-        print(json.dumps(res), flush=True)
+        emit(res)
         os._exit(0)
     deadline = time.time() + 30
     rel = None
@@ -244,7 +252,7 @@ def main():
     res["members_alive"] = s.get("members_alive")
     res["errors"] = s["device"]["errors"]
     res["frames_sent"] = s["device"]["frames_sent"]
-    print(json.dumps(res), flush=True)
+    emit(res)
     alive = world - 1 if scenario == "kill_leaf" else world
     _touch_and_wait(sync_dir, f"done_{rank}", [f"done_{r}" for r in range(alive)])  # nobody leaves before all have looked
     time.sleep(0.2 + 0.3 * (world - rank))  # leaves first

@@ -2,7 +2,7 @@
 """Builds the host core with ThreadSanitizer or AddressSanitizer and runs a multi-node scenario in it.
 
     python tests/sanitize_core.py thread      # data races in the node / tree / TCP-edge threads
-    python tests/sanitize_core.py address     # heap errors, leaks off (CPython leaks by design)
+    python tests/sanitize_core.py address     # heap errors and undefined behaviour (ASan + UBSan), leaks off (CPython leaks by design)
 
 The reference is racy by construction (every shared array is touched by up to seven unsynchronised threads); this
 is the check that the re-implementation is not.  The sanitised module is built under build/sanitize/ and loaded in
@@ -66,13 +66,17 @@ def main():
     out.mkdir(parents=True, exist_ok=True)
     so = out / f"_core_{kind}.so"
     src = [ROOT / "sharedtensor_b200" / "csrc" / "core" / f for f in ("codec.cpp", "codec_fast.cpp", "tree.cpp", "node.cpp", "bindings.cpp")]
-    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fPIC", "-shared", f"-fsanitize={kind}", "-fno-omit-frame-pointer", "-ffp-contract=off",
+    flags = "thread" if kind == "thread" else "address,undefined"
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fPIC", "-shared", f"-fsanitize={flags}", "-fno-omit-frame-pointer", "-ffp-contract=off",
            "-pthread", f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{ROOT / 'sharedtensor_b200' / 'csrc'}",
            *map(str, src), "-o", str(so)]
     subprocess.run(cmd, check=True)
-    lib = subprocess.run(["g++", f"-print-file-name=lib{'tsan' if kind == 'thread' else 'asan'}.so"], capture_output=True, text=True).stdout.strip()
+    def runtime(name):
+        return subprocess.run(["g++", f"-print-file-name=lib{name}.so"], capture_output=True, text=True).stdout.strip()
+
+    lib = runtime("tsan") if kind == "thread" else runtime("asan") + ":" + runtime("ubsan")
     env = dict(os.environ, LD_PRELOAD=lib, TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0 exitcode=66",
-               ASAN_OPTIONS="detect_leaks=0 exitcode=66")
+               ASAN_OPTIONS="detect_leaks=0 exitcode=66", UBSAN_OPTIONS="print_stacktrace=1")
     import socket
 
     with socket.socket() as s:
@@ -85,7 +89,7 @@ def main():
         # close() once showed up exactly like this); reported to the caller as exit code 75
         print(f"sanitizer={kind} timeout")
         sys.exit(75)
-    reports = res.stderr.count("WARNING: ThreadSanitizer") + res.stderr.count("ERROR: AddressSanitizer")
+    reports = res.stderr.count("WARNING: ThreadSanitizer") + res.stderr.count("ERROR: AddressSanitizer") + res.stderr.count("runtime error:")
     print(res.stdout[-500:])
     print(f"sanitizer={kind} exit={res.returncode} reports={reports}")
     if reports:

@@ -367,6 +367,32 @@ def test_several_frames_per_round_and_ring_full(cu, core):
     assert A.check_guards() == 0 and B.check_guards() == 0
 
 
+@pytest.mark.parametrize("bits", [1, 8])
+def test_unacknowledged_frames_are_taken_back(cu, bits):
+    """A sender whose neighbour never consumed (never acknowledged) two frames takes their steps off its mirror again
+    and its ring counters fall back, so that what the frames said counts as not yet told."""
+    n = 3 * 4096 + 70
+    torch.manual_seed(21)
+    A, B = _replica(cu, n, bits=bits), _replica(cu, n, bits=bits)
+    la, lb = connect_local(A, B)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    for _ in range(2):
+        A.round()
+        A.sync()
+    k = _dev_view(A.mirror_ptr(la), n)
+    assert float(k.abs().max()) > 0.0
+    assert A.unsend_unacknowledged(0) == 2 * A.tiles()
+    k = _dev_view(A.mirror_ptr(la), n)
+    assert float(k.abs().max()) == 0.0, "the mirror is back where it was before the two frames"
+    names = cu.status_names()
+    sent_before = A.status()[names.index("frames_sent")]
+    A.round()
+    A.sync()
+    assert A.status()[names.index("frames_sent")] == sent_before + A.tiles(), "the ring has room again"
+    assert A.check_guards() == 0 and B.check_guards() == 0
+
+
 def test_updates_commute_with_rounds(cu):
     """One stream adds 200 deltas while the engine threads run rounds: both replicas end at the exact fp32 sum
     (every delta is a multiple of 2^-10 and all partial sums are exactly representable, so any order gives it)."""
@@ -405,6 +431,43 @@ def test_updates_commute_with_rounds(cu):
     assert ok, float((out - expect).abs().max())
     assert A.status()[5] == 0 and B.status()[5] == 0
     assert A.check_guards() == 0 and B.check_guards() == 0
+
+
+def test_join_while_the_default_stream_is_busy(cu):
+    """Links, edge blocks and sequence counters are created while the legacy default stream holds a long queue:
+    they are zeroed on the streams that use them, not behind that queue, so the first rounds see clean memory and
+    nothing is wiped after the fact."""
+    n = 3 * 4096 + 5
+    torch.manual_seed(12)
+    A, B = _replica(cu, n), _replica(cu, n)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    for _ in range(60):
+        cu.delay(5_000_000, _stream())          # 0.3 s of queued work on the default stream
+    side = torch.cuda.Stream()
+    connect_local(A, B)
+    out = torch.empty(n, device="cuda")
+    for _ in range(6):
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+    B.snapshot(out.data_ptr(), side.cuda_stream)
+    side.synchronize()
+    still_busy = not torch.cuda.current_stream().query()
+    assert ((out - init).norm() / init.norm()).item() < 1e-5
+    assert still_busy, "the default stream was meant to be busy for the whole test"
+    torch.cuda.synchronize()
+    for _ in range(3):                           # nothing is zeroed late: the replicas stay where they are
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+    B.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert ((out - init).norm() / init.norm()).item() < 1e-5
+    assert A.status()[5] == 0 and B.status()[5] == 0
 
 
 def test_bounded_wait_runs_out_and_the_replica_recovers(cu):

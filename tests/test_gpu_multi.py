@@ -36,6 +36,10 @@ def _run(world, port, n, scenario):
             raise AssertionError(f"a worker produced no result\n{report}")
         results.append(json.loads(lines[-1]))
     shutil.rmtree(sync_dir, ignore_errors=True)
+    # which physical GPUs the ranks ran on (pytest -s / -rP shows it): on a box with fewer GPUs than ranks some share one
+    used = sorted({r.get("device_uuid", "?") for r in results})
+    print(f"[{scenario}] {world} ranks on {len(used)} GPU(s): {used}")
+    assert len(used) == min(world, torch.cuda.device_count()), "ranks are spread over the GPUs that exist"
     return results
 
 

@@ -1,4 +1,5 @@
-"""Race detection: the host core under ThreadSanitizer (five nodes, concurrent adds, an injected edge loss)."""
+"""Race detection and memory checking of the host core: the same scenario (five nodes, concurrent adds, an injected
+edge loss, a master that leaves) under ThreadSanitizer and under AddressSanitizer + UndefinedBehaviorSanitizer."""
 import subprocess
 import sys
 from pathlib import Path
@@ -17,6 +18,16 @@ def _have(lib):
 def test_core_is_race_free_under_tsan():
     for attempt in range(2):  # exit code 75 = the scenario stalled; a second stall in a row fails the test
         res = subprocess.run([sys.executable, str(HERE / "sanitize_core.py"), "thread"], capture_output=True, text=True, timeout=500)
+        if res.returncode != 75:
+            break
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
+    assert "reports=0" in res.stdout
+
+
+@pytest.mark.skipif(not (_have("libasan.so") and _have("libubsan.so")), reason="AddressSanitizer / UBSan runtimes not installed")
+def test_core_is_clean_under_asan_and_ubsan():
+    for attempt in range(2):
+        res = subprocess.run([sys.executable, str(HERE / "sanitize_core.py"), "address"], capture_output=True, text=True, timeout=500)
         if res.returncode != 75:
             break
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]

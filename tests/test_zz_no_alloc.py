@@ -31,8 +31,8 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.st_noalloc_strerror.restype = ctypes.c_char_p
-    stream = torch.cuda.current_stream().cuda_stream
     torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
 
     for seed, sizes in ((1, [5, 70000, 1, 300000, 4096, 0, 65536]), (2, [200000, 3, 131072])):
         x, offs, total = _table(seed, sizes)
@@ -45,9 +45,13 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
         # allocation-free entry point: outputs are still ours, scratch is the library's
         out_sum = torch.full((n_seg,), -1.0, dtype=torch.float64, device="cuda")
         out_exp = torch.full((n_seg,), 99, dtype=torch.int8, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(x.data_ptr(), offs.data_ptr(), n_seg, total, out_sum.data_ptr(), out_exp.data_ptr(), stream)
         assert rc == 0, lib.st_noalloc_strerror(rc)
         torch.cuda.synchronize()
+        if seed == 2:  # (the first call on a device may load the library's device image; the second must leave memory alone)
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call allocated device memory"
         assert torch.allclose(out_sum, ref_sum, rtol=1e-9, atol=0.0)
         assert torch.equal(out_exp, ref_exp)
         seg = [float((x[offs[i]:offs[i + 1]].double() ** 2).sum()) for i in range(n_seg)]
@@ -60,3 +64,11 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
     assert fn(x.data_ptr(), offs.data_ptr(), 5000, total, o1.data_ptr(), o2.data_ptr(), stream) == -1
     assert fn(x.data_ptr(), offs.data_ptr(), 1, (1 << 31) + 1, o1.data_ptr(), o2.data_ptr(), stream) == -2
     assert b"scratch" in lib.st_noalloc_strerror(-2)
+
+    # a table whose offsets go further than the total the caller gave: no read past the scratch array, NaN instead
+    x, offs, total = _table(4, [70000, 200000])
+    o1 = torch.zeros(2, dtype=torch.float64, device="cuda")
+    o2 = torch.zeros(2, dtype=torch.int8, device="cuda")
+    assert fn(x.data_ptr(), offs.data_ptr(), 2, 65536, o1.data_ptr(), o2.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(o1[1]))
