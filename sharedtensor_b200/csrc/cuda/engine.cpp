@@ -692,7 +692,7 @@ std::vector<uint64_t> GpuReplica::status() {
 
 std::vector<uint32_t> GpuReplica::debug_crumbs() const {
   std::vector<uint32_t> out;
-  if (dbg_host_) out.assign(dbg_host_, dbg_host_ + 148 * 8);
+  if (dbg_host_) out.assign(dbg_host_, dbg_host_ + 2048);
   return out;
 }
 

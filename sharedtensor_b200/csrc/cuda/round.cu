@@ -46,6 +46,16 @@
 #else
 #define ST_CRUMB(slot, code)
 #endif
+#ifdef ST_ROUND_TIMELINE
+// time stamps (ns, low 32 bits) of the first steps of CTA 0 / group 0 in the debug buffer: [1024 + step * 8 + event]
+#define ST_STAMP(step, ev)                                                                                   \
+  do {                                                                                                       \
+    if (p.dbg != nullptr && blockIdx.x == 0 && g == 0 && lane == 0 && (step) < 24u)                          \
+      *reinterpret_cast<volatile uint32_t*>(p.dbg + 1024 + (step) * 8 + (ev)) = uint32_t(globaltimer_ns()); \
+  } while (0)
+#else
+#define ST_STAMP(step, ev)
+#endif
 #ifdef ST_ROUND_TIMING
 #include <cstdio>
 #define ST_T0() const long long st_t0_ = clock64()
@@ -63,7 +73,7 @@ namespace {
 
 constexpr int kGroupThreads = 128;  // compute threads of a group: one per 32 consecutive elements of a tile
 constexpr int kTileBytes = kTile * 4;
-constexpr int kPubQueue = 8;
+constexpr int kPubQueue = 32;
 // Shapes of a CTA (groups x staging slots per group); the launcher picks one, see launch_round.
 //   3 x 2: one CTA per SM, 12 compute warps                (fills the SM's shared memory and registers)
 //   2 x 3: one CTA per SM,  8 compute warps, deeper staging (leaves a third of the registers to other kernels)
@@ -635,6 +645,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
       ST_CRUMB(4 + g, 31);
       const bool step_ok = __all_sync(0xffffffffu, armed_ok && mbar_wait_bounded(full + s, (c / kSlots) & 1u, limit_ns));
       ST_CRUMB(4 + g, 32);
+      if (wig == 0) ST_STAMP(c, 1);
       ST_ACC(tm_wait);
 #ifdef ST_ROUND_TIMING
       tm_steps++;
@@ -755,6 +766,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(done + s);
+      if (wig == 0) ST_STAMP(c, 2);
       ST_LAP(tm_e);
       if (failed) break;
     }
@@ -841,9 +853,10 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(done + s, (c / kSlots) & 1u, 2 * limit_ns));
       ST_ACC(tm_done);
     }
+    ST_STAMP(c, 3);
     const uint32_t f = ok ? __shfl_sync(0xffffffffu, ld_shared_volatile(sflags + s), 0) : kFlagFailed;
     if (f & kFlagFailed) return false;
-    if (pushed - __shfl_sync(0xffffffffu, ld_shared_volatile(pub_done), 0) >= uint32_t(kPubQueue)) {  // (never in practice: the queue is 8 steps deep)
+    if (pushed - __shfl_sync(0xffffffffu, ld_shared_volatile(pub_done), 0) >= uint32_t(kPubQueue)) {  // (the publisher has fallen behind: its fence takes tens of microseconds under load)
       bulk_wait_all();
       __syncwarp();
       hand_over(pushed);
@@ -909,6 +922,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
     }
     pushed++;
     __syncwarp();
+    ST_STAMP(c, 4);
     ST_ACC(tm_store);
     return true;
   };
@@ -1037,6 +1051,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
             bulk_g2s(slot + (lane == 0 ? kTileBytes : 0), src, kTileBytes, full + s);
           }
         }
+        ST_STAMP(issued, 0);
         issued++;
         cur_a++;
         if (cur_a == L) cur_tile = -1;
