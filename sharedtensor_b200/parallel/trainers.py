@@ -161,14 +161,16 @@ def random_token_batches(vocab: int, batch: int, seq: int, device, seed: int):
         yield x[:, :-1].contiguous(), x[:, 1:].contiguous()
 
 
-def structured_token_batches(vocab: int, batch: int, seq: int, device, seed: int, period: int = 7):
-    """Learnable synthetic data: token t+1 = (token t + step) mod vocab with a per-sequence step in 1..period, so a
-    model has to look at the previous two tokens.  Used to compare async and sync loss curves on something that
-    can actually be learnt (uniform-random tokens cannot)."""
+def structured_token_batches(vocab: int, batch: int, seq: int, device, seed: int, period: int = 7, active: int = 512):
+    """Learnable synthetic data: token t+1 = (token t + step) mod m with a per-sequence step in 1..period, so a
+    model has to look at the previous two tokens; m = min(vocab, active), so that a large vocabulary first has to
+    be narrowed down to the tokens that occur (a loss of ln m) and the arithmetic comes on top.  Used to compare async
+    and sync loss curves on something that can actually be learnt (uniform-random tokens cannot)."""
     g = torch.Generator(device=device).manual_seed(seed)
     ar = torch.arange(seq + 1, device=device)
+    m = min(vocab, active)
     while True:
-        start = torch.randint(0, vocab, (batch, 1), generator=g, device=device)
+        start = torch.randint(0, m, (batch, 1), generator=g, device=device)
         step = torch.randint(1, period + 1, (batch, 1), generator=g, device=device)
-        x = (start + step * ar) % vocab
+        x = (start + step * ar) % m
         yield x[:, :-1].contiguous(), x[:, 1:].contiguous()

@@ -25,8 +25,9 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, bits=8, deadline_us=1000):
+def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, bits=8, deadline_us=1000, window=0):
     cfg = cu.GpuConfig()
+    cfg.window_tiles = window
     cfg.bits = bits
     cfg.poll_deadline_us = deadline_us
     cfg.block = block
@@ -431,6 +432,56 @@ def test_updates_commute_with_rounds(cu):
     assert ok, float((out - expect).abs().max())
     assert A.status()[5] == 0 and B.status()[5] == 0
     assert A.check_guards() == 0 and B.check_guards() == 0
+
+
+def test_windowed_launches_cover_the_tensor(cu):
+    """A tensor that is covered in several launches per pass (windows of 16 tiles here): manual rounds make whole
+    passes, the engine thread goes from window to window, and both see every tile."""
+    n = 40 * 4096 + 11
+    torch.manual_seed(31)
+    A, B = _replica(cu, n, window=16), _replica(cu, n, window=16)
+    connect_local(A, B)
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    out = torch.empty(n, device="cuda")
+    for _ in range(4):
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+    B.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert ((out - init).norm() / init.norm()).item() < 1e-5
+    names = cu.status_names()
+    quiet = False
+    for _ in range(10):     # the refinements die down: a pass that finds nothing to do on either side
+        A.round()
+        A.sync()
+        B.round()
+        B.sync()
+        sa, sb = A.status(), B.status()
+        if all(s[names.index(k)] == 0 for s in (sa, sb) for k in ("last_work_count", "pending_tiles")):
+            quiet = True
+            break
+    assert quiet, "the counters of a whole pass (all windows) are zero once nothing moves"
+    assert A.status()[names.index("tiles_processed")] >= A.tiles()
+    A.start_engine()
+    B.start_engine()
+    d = torch.randn(n, device="cuda")
+    B.add(d.data_ptr(), _stream())
+    import time
+
+    deadline = time.time() + 10
+    ok = False
+    while time.time() < deadline and not ok:
+        A.snapshot(out.data_ptr(), _stream())
+        torch.cuda.synchronize()
+        ok = ((out - (init + d)).norm() / init.norm()).item() < 1e-5
+        time.sleep(0.005)
+    A.stop_engine()
+    B.stop_engine()
+    assert ok
+    assert A.status()[5] == 0 and B.status()[5] == 0
 
 
 def test_join_while_the_default_stream_is_busy(cu):
