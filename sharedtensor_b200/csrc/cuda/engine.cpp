@@ -95,6 +95,13 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
     cudaEvent_t e;
     check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
     ev_round_.push_back(e);
+    check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+    ev_kernel_.push_back(e);
+  }
+  {
+    cudaStream_t st;
+    check(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate");
+    stat_ = st;
   }
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_);
@@ -153,6 +160,8 @@ GpuReplica::~GpuReplica() {
   if (tcp_stat_dev_) cudaFree(tcp_stat_dev_);
   if (tcp_pinned_) cudaFreeHost(tcp_pinned_);
   for (void* e : ev_round_) cudaEventDestroy(E(e));
+  for (void* e : ev_kernel_) cudaEventDestroy(E(e));
+  if (stat_) cudaStreamDestroy(S(stat_));
   if (ev_user_) cudaEventDestroy(E(ev_user_));
   if (ev_comm_) cudaEventDestroy(E(ev_comm_));
   if (comm_) cudaStreamDestroy(S(comm_));
@@ -262,6 +271,7 @@ uint64_t GpuReplica::unsend_unacknowledged(int peer) {
   check(launch_unsend(mirror(p.link), p.remote + layout_.off_payload, p.tx_seq, reinterpret_cast<const uint32_t*>(local + layout_.off_credit),
                       n_tiles_, cfg_.ring_slots, params_.payload_bytes, params_.log2_block, cfg_.bits, n_, dev_count, comm_),
         "unsend kernel");
+  check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");  // the link has something to hear again
   uint64_t host = 0;
   check(cudaMemcpyAsync(status_host_ + kDsTotalWords + 8, dev_count, 8, cudaMemcpyDeviceToHost, S(comm_)), "cudaMemcpyAsync");
   check(cudaStreamSynchronize(S(comm_)), "cudaStreamSynchronize");
@@ -767,9 +777,11 @@ void GpuReplica::engine_loop() {
   cudaSetDevice(device_);
   ::prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);  // 1 us instead of the default 50 us: the idle pauses start at 10 us
   const size_t depth = ev_round_.size();
-  // one pinned word per launch in flight: how many tiles that launch handled
-  uint64_t* work_host = status_host_ + kDsTotalWords;  // behind the part status() uses: tiles handled so far, after a launch
-  uint64_t* work_before = work_host + 4;               // ... and before it
+  // One pinned word per launch in flight: tiles handled so far, read once that launch has finished.  The read runs on
+  // a stream of its own behind an event, so that the comm stream goes from one launch straight to the next; a later
+  // launch may already have added to the count by then, which only moves work from one difference to the next.
+  uint64_t* work_host = status_host_ + kDsTotalWords;  // behind the part status() uses
+  uint64_t work_seen = 0;
   uint64_t r = 0;
   uint64_t idle_rounds = 0;
   uint64_t quiet_launches = 0;   // launches in a row that found nothing to do
@@ -782,10 +794,11 @@ void GpuReplica::engine_loop() {
         // One launch makes several passes over a small tensor and returns; nothing on the device waits for this
         // thread, which only starts the next launch and reads how much the last one found to do.
         windows = n_windows();
-        cudaMemcpyAsync(work_before + (r % depth), status_ + kDsTilesProcessed, 8, cudaMemcpyDeviceToHost, S(comm_));
         launch(true, true, auto_sweeps());
-        cudaMemcpyAsync(work_host + (r % depth), status_ + kDsTilesProcessed, 8, cudaMemcpyDeviceToHost, S(comm_));
-        cudaEventRecord(E(ev_round_[r % depth]), S(comm_));
+        cudaEventRecord(E(ev_kernel_[r % depth]), S(comm_));
+        cudaStreamWaitEvent(S(stat_), E(ev_kernel_[r % depth]), 0);
+        cudaMemcpyAsync(work_host + (r % depth), status_ + kDsTilesProcessed, 8, cudaMemcpyDeviceToHost, S(stat_));
+        cudaEventRecord(E(ev_round_[r % depth]), S(stat_));
         launched = true;
       }
     } catch (const std::exception&) {
@@ -799,7 +812,9 @@ void GpuReplica::engine_loop() {
     uint64_t work = 1;
     if (r >= depth) {
       cudaEventSynchronize(E(ev_round_[(r - depth) % depth]));
-      work = work_host[(r - depth) % depth] - work_before[(r - depth) % depth];
+      const uint64_t now = work_host[(r - depth) % depth];
+      work = now > work_seen ? now - work_seen : 0;
+      work_seen = now > work_seen ? now : work_seen;
     }
     if (work != 0) epoch_++;
     quiet_launches = work == 0 ? quiet_launches + 1 : 0;
@@ -828,6 +843,7 @@ void GpuReplica::engine_loop() {
     }
   }
   cudaStreamSynchronize(S(comm_));
+  cudaStreamSynchronize(S(stat_));
 }
 
 }  // namespace st

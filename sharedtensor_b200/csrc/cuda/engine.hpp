@@ -196,7 +196,9 @@ class GpuReplica {
   void* comm_ = nullptr;               // cudaStream_t
   void* ev_user_ = nullptr;            // cudaEvent_t: user stream -> comm
   void* ev_comm_ = nullptr;            // cudaEvent_t: comm -> user stream
-  std::vector<void*> ev_round_;
+  std::vector<void*> ev_round_;       // per launch in flight: its work count has been read back
+  std::vector<void*> ev_kernel_;      // per launch in flight: the kernel has finished (comm stream)
+  void* stat_ = nullptr;               // cudaStream_t: reads work counts back beside the comm stream, so that launches follow each other without a copy in between
   mutable std::mutex mu_;
   std::mutex gate_mu_;                 // taken before mu_ by every update from outside the rounds
   std::mutex engine_mu_;               // serialises start_engine / stop_engine

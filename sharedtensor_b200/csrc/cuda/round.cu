@@ -217,6 +217,7 @@ constexpr uint32_t kDescRxAny = 4;   // at least one frame arrived for the tile
 constexpr uint32_t kDescTxOk = 8;    // every out-ring of the link has room
 constexpr uint32_t kDescRxLink = 16; // at least one frame arrived on this step's link
 constexpr uint32_t kDescLast = 32;   // the tile's last step
+constexpr uint32_t kDescTxWant = 64; // the link may have something to hear: the tile changed here, or frames arrived on another link
 constexpr uint32_t kFlagChanged = 1, kFlagNonsilent = 2, kFlagFailed = 4;  // what the compute warps report about a step
 
 __device__ __forceinline__ uint32_t ctrl_byte(uint32_t lo, uint32_t hi, int r) { return ((r < 4 ? lo : hi) >> ((r & 3) * 8)) & 0xffu; }
@@ -703,7 +704,9 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
 
       ST_LAP(tm_b);
       // ---- quantise values - mirror for link l
+      const bool want = (d.flags & kDescTxWant) != 0;  // (a step that only receives says nothing back, whatever rounding left)
       float xm = residual_maxabs(v, k);
+      if (!want) xm = 0.f;
       if (l == 0) res_max0 = fmaxf(res_max0, xm); else if (l == 1) res_max1 = fmaxf(res_max1, xm); else res_max2 = fmaxf(res_max2, xm);
       uint32_t vm = vmax_mine;
       // blocks larger than 32 elements: maximum over lanes (up to 1024), then over the group's warps
@@ -933,9 +936,9 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
     int scan_pos = 0;
     uint32_t pend = 0;                 // lanes whose scouted tile still has to be handed out
     int sc_tile = 0;                   // what this lane found for its tile
-    uint32_t sc_in_lo = 0, sc_in_hi = 0, sc_out_lo = 0, sc_out_hi = 0;
+    uint32_t sc_in_lo = 0, sc_in_hi = 0, sc_out_lo = 0, sc_out_hi = 0, sc_dirty = 0;
     int cur_tile = -1, cur_a = 0;      // the tile whose steps are being handed out
-    uint32_t cur_in_lo = 0, cur_in_hi = 0, cur_out_lo = 0, cur_out_hi = 0;
+    uint32_t cur_in_lo = 0, cur_in_hi = 0, cur_out_lo = 0, cur_out_hi = 0, cur_dirty = 0;
     bool exhausted = my_count == 0;
 
     while (true) {
@@ -944,7 +947,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
         if (cur_tile < 0 && __shfl_sync(0xffffffffu, ld_shared_volatile(yield_seen), 0) != 0u) {
           // An update is waiting for the SMs this kernel holds: hand out nothing more.  Tiles that were looked at but
           // not handed out get their change marks back, everything else is untouched.
-          if ((pend >> lane) & 1u) st_cg_u32(p.tile_state + sc_tile, 1u);
+          if (((pend >> lane) & 1u) && sc_dirty) st_cg_u32(p.tile_state + sc_tile, 1u);
           pend = 0;
           exhausted = true;
           yielded = true;
@@ -961,7 +964,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
             const int j = scan_pos + lane;
             const bool valid = j < my_count;
             sc_tile = gid + j * gstride;
-            sc_in_lo = sc_in_hi = sc_out_lo = sc_out_hi = 0;
+            sc_in_lo = sc_in_hi = sc_out_lo = sc_out_hi = sc_dirty = 0;
             bool work = false;
             if (valid) {
               uint32_t dirty = ld_cg_u32(p.tile_state + sc_tile);
@@ -993,6 +996,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
               // exchange has returned), and whoever changes the values sets it after the change: a change
               // that this visit does not see leaves its mark for the next one.
               if (dirty) dirty = atomicExch(p.tile_state + sc_tile, 0u);
+              sc_dirty = dirty;
               work = dirty != 0 || any;
             }
             pend = __ballot_sync(0xffffffffu, work);
@@ -1007,6 +1011,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
           cur_in_hi = __shfl_sync(0xffffffffu, sc_in_hi, src);
           cur_out_lo = __shfl_sync(0xffffffffu, sc_out_lo, src);
           cur_out_hi = __shfl_sync(0xffffffffu, sc_out_hi, src);
+          cur_dirty = __shfl_sync(0xffffffffu, sc_dirty, src);
           cur_a = 0;
         }
         // ---- hand out step (cur_tile, link cur_a)
@@ -1023,14 +1028,21 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
             tx_any = true;
             tx_room &= (ctrl_byte(cur_out_lo, cur_out_hi, r) >> 6) != 0;
           }
-          for (int r = 0; r < p.n_in; r++)
-            if (p.in[r].link == l && (ctrl_byte(cur_in_lo, cur_in_hi, r) >> 6) != 0) rx_link = true;
+          // A frame that arrived on link l changes the values and l's mirror alike: it leaves nothing to say on l, and
+          // what rounding makes of it (or a cut-off that moved with the values) is not worth a frame back.  The link
+          // gets a frame when the tile changed here (its mark) or when another link brought something to pass on.
+          bool rx_other = false;
+          for (int r = 0; r < p.n_in; r++) {
+            if ((ctrl_byte(cur_in_lo, cur_in_hi, r) >> 6) == 0) continue;
+            if (p.in[r].link == l) rx_link = true; else rx_other = true;
+          }
+          const bool tx_want = cur_dirty != 0 || rx_other;
           const bool rx_any = ((cur_in_lo | cur_in_hi) & 0xc0c0c0c0u) != 0;
           StepDesc d;
           d.tile = cur_tile;
           d.link = l;
-          d.flags = (cur_a == 0 ? kDescFirst : 0u) | (rx_any ? kDescRxAny : 0u) | (tx_any && tx_room && p.do_tx ? kDescTxOk : 0u) |
-                    (rx_link ? kDescRxLink : 0u) | (cur_a == L - 1 ? kDescLast : 0u);
+          d.flags = (cur_a == 0 ? kDescFirst : 0u) | (rx_any ? kDescRxAny : 0u) | (tx_any && tx_room && tx_want && p.do_tx ? kDescTxOk : 0u) |
+                    (rx_link ? kDescRxLink : 0u) | (tx_want ? kDescTxWant : 0u) | (cur_a == L - 1 ? kDescLast : 0u);
           d.sent = 0;
           d.in_lo = cur_in_lo; d.in_hi = cur_in_hi; d.out_lo = cur_out_lo; d.out_hi = cur_out_hi;
           desc[s] = d;

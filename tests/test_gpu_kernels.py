@@ -160,15 +160,39 @@ def test_sample_sqerr_and_delay(cu):
 
 # --------------------------------------------------------------------------------------------------
 class Oracle:
-    """Host model of a replica: values, one mirror per link, frames exchanged as (codes or words, scales)."""
+    """Host model of a replica: values, one mirror per link, frames exchanged as (codes or words, scales), and the
+    change mark of every 4096-element tile.  A link is told about a tile only while the tile carries a mark: set by
+    whatever changes the values or a mirror from outside the rounds, kept while a visit still found something to say;
+    a frame that merely arrives (it moves values and mirror alike) does not make the tile speak."""
 
     def __init__(self, core, n, block, n_links, bits=8, min_exp=-60, rel_bits=22):
         self.core, self.n, self.block, self.bits = core, n, block, bits
         self.v = torch.zeros(n)
         self.k = [torch.zeros(n) for _ in range(n_links)]
         self.min_exp, self.rel_bits = min_exp, rel_bits
+        self.dirty = torch.ones((n + 4095) // 4096, dtype=torch.bool)  # a fresh replica, a new edge: everything is looked at
+
+    def mark(self):
+        self.dirty[:] = True
 
     def encode(self, link):
+        k_before = self.k[link].clone()
+        codes, scales = self._encode_all(link)
+        spt = 4096 // self.block
+        for t in range(self.dirty.numel()):
+            lo, hi = t * 4096, min((t + 1) * 4096, self.n)
+            if not bool(self.dirty[t]):
+                self.k[link][lo:hi] = k_before[lo:hi]
+                scales[t * spt:(t + 1) * spt] = 0
+                if self.bits == 1:
+                    codes[lo // 32:(hi + 31) // 32] = 0
+                else:
+                    codes[lo:hi] = 1 << (self.bits - 1)
+            else:
+                self.dirty[t] = bool(scales[t * spt:(t + 1) * spt].any())
+        return codes, scales
+
+    def _encode_all(self, link):
         scales = torch.zeros(self.core.block_scales(self.n, self.block), dtype=torch.uint8)
         if self.bits == 1:
             codes = torch.zeros(self.core.block_words(self.n), dtype=torch.int32)
@@ -270,6 +294,8 @@ def test_round_bit_exact_two_replicas(cu, core, bits, block, n):
             da, db = torch.randn(n) * 1e-2, torch.randn(n) * 1e-1
             oa.v += da
             ob.v += db
+            oa.mark()
+            ob.mark()
             A.add(da.cuda().data_ptr(), _stream())
             B.add(db.cuda().data_ptr(), _stream())
             torch.cuda.synchronize()
@@ -325,6 +351,38 @@ def test_one_frame_of_eight_bits_delivers_an_update(cu, bits):
         assert rel < 1e-2, rel
     else:
         assert rel > 0.3, rel
+
+
+def test_a_received_frame_is_not_answered(cu):
+    """A frame moves the receiver's values and its mirror of the sender by the same step, so it leaves nothing to say
+    to the sender; the two additions round differently and the cut-off moves with the values, which must not make
+    the receiver send a frame back for every tile it received."""
+    n = 16 * 4096
+    torch.manual_seed(31)
+    A, B = _replica(cu, n), _replica(cu, n)
+    connect_local(A, B)
+    names = cu.status_names()
+    i_sent = names.index("frames_sent")
+    init = torch.randn(n, device="cuda")
+    A.load_values(init.data_ptr(), _stream())
+    db = torch.randn(n, device="cuda")
+    B.add(db.data_ptr(), _stream())     # B's values and its mirror of A differ in their low bits from here on
+    torch.cuda.synchronize()
+    for _ in range(12):
+        A.round(); A.sync(); B.round(); B.sync()
+    da = torch.randn(n, device="cuda")  # large enough to move the cut-off of many blocks
+    A.add(da.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    sent_b = B.status()[i_sent]
+    for _ in range(6):
+        A.round(); A.sync(); B.round(); B.sync()
+    assert B.status()[i_sent] == sent_b, "the receiver answered frames it had only received"
+    out = torch.empty(n, device="cuda")
+    expect = init + db + da
+    for r in (A, B):
+        r.snapshot(out.data_ptr(), _stream())
+        torch.cuda.synchronize()
+        assert ((out - expect).norm() / expect.norm()).item() < 1e-5
 
 
 def test_several_frames_per_round_and_ring_full(cu, core):
