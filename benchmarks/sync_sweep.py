@@ -93,7 +93,7 @@ def main():
                 barrier()
         rep = st._b.rep
         out = torch.empty(n, device=dev)
-        stride = max(1, n >> 21)               # the probe looks at up to 2 Mi elements
+        stride = max(1, n >> 17)               # the probe looks at up to 128 Ki elements: a heavier one slows the kernels it watches
         expect_s = init[::stride].clone()
         lat = []
         for pr in range(args.probes + 2):
