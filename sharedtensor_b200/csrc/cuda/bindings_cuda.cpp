@@ -113,8 +113,6 @@ PYBIND11_MODULE(_cuda, m) {
       .def("size", &GpuReplica::size)
       .def("padded", &GpuReplica::padded)
       .def("tiles", &GpuReplica::tiles)
-      .def("launches_per_pass", &GpuReplica::launches_per_pass)
-      .def("budget_per_group", &GpuReplica::budget_per_group)
       .def("values_ptr", [](GpuReplica& r) { return reinterpret_cast<uintptr_t>(r.values()); })
       .def("mirror_ptr", [](GpuReplica& r, int link) { return reinterpret_cast<uintptr_t>(r.mirror(link)); })
       .def("comm_stream", [](GpuReplica& r) { return reinterpret_cast<uintptr_t>(r.comm_stream()); })

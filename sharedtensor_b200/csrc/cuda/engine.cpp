@@ -82,8 +82,6 @@ GpuReplica::GpuReplica(int device, int64_t n, const GpuConfig& cfg) : device_(de
   check(cudaMalloc(reinterpret_cast<void**>(&status_), kDsTotalWords * 8), "cudaMalloc status");
   check(cudaMallocHost(reinterpret_cast<void**>(&status_host_), (kDsTotalWords + 16) * 8), "cudaMallocHost status");
   check(cudaMalloc(reinterpret_cast<void**>(&yield_flag_), 4), "cudaMalloc yield flag");
-  check(cudaMalloc(reinterpret_cast<void**>(&resume_), 4096), "cudaMalloc resume");
-  check(cudaMemsetAsync(resume_, 0, 4096, s), "memset");
   check(cudaMemsetAsync(yield_flag_, 0, 4, s), "memset");
   check(launch_fill_state(tile_state_, n_tiles_, 1u, comm_), "fill_state");
   check(cudaMemsetAsync(status_, 0, kDsTotalWords * 8, s), "memset");
@@ -157,7 +155,6 @@ GpuReplica::~GpuReplica() {
   cudaFree(tile_state_);
   cudaFree(status_);
   cudaFree(yield_flag_);
-  cudaFree(resume_);
   if (status_host_) cudaFreeHost(status_host_);
   if (tcp_words_dev_) cudaFree(tcp_words_dev_);
   if (tcp_stat_dev_) cudaFree(tcp_stat_dev_);
@@ -522,36 +519,15 @@ void GpuReplica::push_snapshot(int link, float* remote_values) {
   check(cudaStreamSynchronize(S(comm_)), "snapshot_join");
 }
 
-// A long pass would hold every SM for its whole duration, so a launch over a large tensor handles a bounded number of
-// tiles and kernels of other streams get their turn between two launches.  Every launch looks at the whole tensor
-// (wherever there is something to do, it is found at once) and each group of the kernel stops after its share of the
-// bound; the next launch goes on where it stopped.  With many short-lived CTAs (chunk_tiles) the tensor is covered in
-// windows instead, one launch each.
-int GpuReplica::launch_tiles() const {
+// A long pass would hold every SM for its whole duration; the tensor is therefore covered in windows, one launch
+// each, so that kernels of other streams get their turn between two launches.
+int GpuReplica::window_tiles() const {
   if (cfg_.window_tiles > 0) return cfg_.window_tiles < n_tiles_ ? cfg_.window_tiles : n_tiles_;
-  return n_tiles_ > 8192 ? 6144 : n_tiles_;   // 25 M elements, about 0.1 ms of a one-link pass
+  return n_tiles_ > 8192 ? 6144 : n_tiles_;   // 25 M elements, about 0.15 ms of a one-link pass
 }
-int GpuReplica::window_tiles() const { return cfg_.chunk_tiles > 0 ? launch_tiles() : n_tiles_; }
 int GpuReplica::n_windows() const {
   const int w = window_tiles();
   return (n_tiles_ + w - 1) / w;
-}
-int GpuReplica::budget_per_group() const {
-  if (cfg_.chunk_tiles > 0 || launch_tiles() >= n_tiles_) return 0;
-  int grid, chunk, per_group;
-  grid_for_launch(n_tiles_, &grid, &chunk, &per_group);
-  const int groups = grid * round_shape_groups(cfg_.shape);
-  if (groups > 1024) return 0;  // (the resume words)
-  const int b = (launch_tiles() + groups - 1) / groups;
-  return b < 1 ? 1 : b;
-}
-// launches that take every group once through all of its tiles when every tile has something to do
-int GpuReplica::launches_per_pass() const {
-  const int b = budget_per_group();
-  if (b == 0) return n_windows();
-  int grid, chunk, per_group;
-  grid_for_launch(n_tiles_, &grid, &chunk, &per_group);
-  return (per_group + b - 1) / b;
 }
 
 // How a launch covers its window: the grid, and how many consecutive tiles a group owns (0: every n-th tile).
@@ -579,8 +555,6 @@ int GpuReplica::auto_sweeps() const {
   // paid once per batch.  Large tensors: a pass is long enough by itself.
   int grid, chunk, per_group;
   grid_for_launch(window_tiles(), &grid, &chunk, &per_group);
-  const int b = budget_per_group();
-  if (b > 0 && b < per_group) per_group = b;
   int sw = 32 / (per_group < 1 ? 1 : per_group);
   return sw < 1 ? 1 : (sw > 16 ? 16 : sw);
 }
@@ -600,8 +574,6 @@ void GpuReplica::launch(bool do_rx, bool do_tx, int sweeps) {
   int grid, chunk, per_group;
   grid_for_launch(params_.tile_count, &grid, &chunk, &per_group);
   params_.chunk = chunk;
-  params_.budget = budget_per_group();
-  params_.resume = resume_;
   check(launch_round(params_, cfg_.shape, grid, comm_), "round kernel");
   last_parity_ = params_.parity;
   next_window_ = (w + 1) % nw;
@@ -615,10 +587,6 @@ void GpuReplica::round(bool do_rx, bool do_tx, int sweeps) {
   std::lock_guard<std::mutex> lk(mu_);
   if (params_.n_in == 0 && params_.n_out == 0) return;
   // one pass over the whole tensor: the rest of the cycle in progress (if the engine thread left one), or a full cycle
-  if (budget_per_group() > 0) {
-    for (int i = launches_per_pass(); i > 0; i--) launch(do_rx, do_tx, sweeps);
-    return;
-  }
   do {
     launch(do_rx, do_tx, sweeps);
   } while (next_window_ != 0);

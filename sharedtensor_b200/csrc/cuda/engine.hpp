@@ -45,7 +45,7 @@ struct GpuConfig {
   bool yield_to_updates = true;  // a running round kernel gives up its SMs when addFromTensor has an update ready
   bool comm_high_priority = false;  // comm stream at the highest stream priority (switches yield_to_updates off)
   int chunk_tiles = 0;       // > 0: short-lived CTAs, a group takes this many consecutive tiles (0: one CTA per SM per launch)
-  int window_tiles = 0;      // tiles a launch handles at most (0: 6144 for tensors above 8192 tiles, else the whole tensor)
+  int window_tiles = 0;      // tiles a launch covers (0: 6144 for tensors above 8192 tiles, else the whole tensor)
 };
 
 constexpr size_t kGuardBytes = 256;  // canary before and after every mirror, edge block and the values
@@ -137,9 +137,6 @@ class GpuReplica {
   uint64_t change_epoch() const { return epoch_.load(); }  // bumped whenever values may have changed
   std::string last_error() const;
 
-  int budget_per_group() const;   // tiles a group of the round kernel hands out per launch at most (0: no bound)
-  int launches_per_pass() const;  // launches round() makes to take every group once through all of its tiles
-
  private:
   struct Link {
     bool used = false;
@@ -162,7 +159,6 @@ class GpuReplica {
   void launch(bool do_rx, bool do_tx, int sweeps);  // under mu_
   int auto_sweeps() const;
   void grid_for_launch(int tiles, int* grid, int* chunk, int* tiles_per_group) const;
-  int launch_tiles() const;
   int window_tiles() const;
   int n_windows() const;
   void fill_guards(const VmmBlock& b, size_t used_bytes);
@@ -202,7 +198,6 @@ class GpuReplica {
   void* ev_comm_ = nullptr;            // cudaEvent_t: comm -> user stream
   std::vector<void*> ev_round_;       // per launch in flight: its work count has been read back
   std::vector<void*> ev_kernel_;      // per launch in flight: the kernel has finished (comm stream)
-  uint32_t* resume_ = nullptr;         // device: per group of the round kernel, where its next launch goes on looking
   void* stat_ = nullptr;               // cudaStream_t: reads work counts back beside the comm stream, so that launches follow each other without a copy in between
   mutable std::mutex mu_;
   std::mutex gate_mu_;                 // taken before mu_ by every update from outside the rounds

@@ -814,14 +814,6 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
   uint32_t issued = 0, retired = 0;
   unsigned long long n_done = 0, n_tx = 0, n_rx = 0, n_blocked = 0, n_pending = 0, n_sweeps = 0;
   bool aborted = false, tile_pending = false, yielded = false;
-  // A launch over a large tensor has a budget: a group hands out at most that many tiles and leaves, so that a launch
-  // stays short whatever it finds; the next launch looks on from where this one stopped (one word per group).
-  int start_j = 0, handed_tiles = 0;
-  bool budget_hit = false;
-  if (p.budget > 0 && p.resume != nullptr && my_count > 0) {
-    start_j = int(ld_cg_u32(p.resume + gidx));
-    if (start_j >= my_count) start_j = 0;
-  }
 #ifdef ST_ROUND_TIMING
   long long tm_done = 0, tm_read = 0, tm_pubwait = 0, tm_pub = 0, tm_scout = 0, tm_issue = 0, tm_store = 0, tm_pf = 0, tm_io0 = clock64();
 #endif
@@ -940,13 +932,12 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
   };
 
   ST_CRUMB(g, 1);
-  for (int sweep = 0; sweep < p.sweeps && !aborted && !yielded && !budget_hit && my_count > 0; sweep++) {
+  for (int sweep = 0; sweep < p.sweeps && !aborted && !yielded && my_count > 0; sweep++) {
     const unsigned long long done_before = n_done;
     int scan_pos = 0;
     uint32_t pend = 0;                 // lanes whose scouted tile still has to be handed out
     int sc_tile = 0;                   // what this lane found for its tile
     uint32_t sc_in_lo = 0, sc_in_hi = 0, sc_out_lo = 0, sc_out_hi = 0, sc_dirty = 0;
-    int sc_j = 0;                      // ... and its position among the group's tiles
     int cur_tile = -1, cur_a = 0;      // the tile whose steps are being handed out
     uint32_t cur_in_lo = 0, cur_in_hi = 0, cur_out_lo = 0, cur_out_hi = 0, cur_dirty = 0;
     bool exhausted = my_count == 0;
@@ -963,18 +954,6 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
           yielded = true;
           continue;
         }
-        if (cur_tile < 0 && p.budget > 0 && handed_tiles >= p.budget && (pend != 0 || scan_pos < my_count)) {
-          // The budget is spent and the group has not seen all of its tiles: the rest waits for the next launch.
-          if (((pend >> lane) & 1u) && sc_dirty) st_cg_u32(p.tile_state + sc_tile, 1u);
-          int next = start_j + scan_pos;  // nothing scouted is left over: go on behind what was looked at
-          if (pend != 0) next = __shfl_sync(0xffffffffu, sc_j, __ffs(pend) - 1);
-          if (next >= my_count) next -= my_count;
-          if (lane == 0 && p.resume != nullptr) st_cg_u32(p.resume + gidx, uint32_t(next));
-          pend = 0;
-          exhausted = true;
-          budget_hit = true;
-          continue;
-        }
         if (cur_tile < 0) {
           if (pend == 0) {
             if (scan_pos >= my_count) {
@@ -985,9 +964,7 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
             ST_T0();
             const int j = scan_pos + lane;
             const bool valid = j < my_count;
-            sc_j = start_j + j;
-            if (sc_j >= my_count) sc_j -= my_count;
-            sc_tile = gid + sc_j * gstride;
+            sc_tile = gid + j * gstride;
             sc_in_lo = sc_in_hi = sc_out_lo = sc_out_hi = sc_dirty = 0;
             bool work = false;
             if (valid) {
@@ -1036,7 +1013,6 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
           cur_out_lo = __shfl_sync(0xffffffffu, sc_out_lo, src);
           cur_out_hi = __shfl_sync(0xffffffffu, sc_out_hi, src);
           cur_dirty = __shfl_sync(0xffffffffu, sc_dirty, src);
-          handed_tiles++;
           cur_a = 0;
         }
         // ---- hand out step (cur_tile, link cur_a)
@@ -1176,7 +1152,6 @@ __global__ void __launch_bounds__(kGroups * (kGroupThreads + 32) + 32, 1)
     st_shared_volatile(pub_exit, 1u);
     ST_CRUMB(g, 10);
     if (yielded) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsYields), 1ull);
-    if (budget_hit) n_pending++;  // tiles that were not looked at count as outstanding: the pass is not over
     if (n_done) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsTilesProcessed), n_done);
     if (n_tx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsFramesSent), n_tx);
     if (n_rx) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + kDsFramesRecv), n_rx);

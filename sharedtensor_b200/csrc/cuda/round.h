@@ -79,8 +79,6 @@ struct RoundParams {
   uint32_t wait_ns;              // upper bound of every wait on one of the kernel's own copies
   int32_t stall_tile;            // test hook: the copy barrier of this tile expects more bytes than are copied (-1: none)
   int32_t chunk;                 // > 0: a group owns this many consecutive tiles; 0: every (groups in the grid)-th tile
-  int32_t budget;                // > 0: a group hands out at most this many tiles in this launch and leaves the rest to the next
-  uint32_t* resume;              // one word per group: where among its tiles the next launch goes on looking (used with a budget)
   const uint32_t* yield_flag;    // non-zero while an update is waiting for SMs: groups hand out no more tiles and leave
   uint32_t* dbg;                 // debug builds: progress marks in mapped host memory, 8 words per CTA (else null)
 };

@@ -25,10 +25,9 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, bits=8, deadline_us=1000, window=0, ctas=0):
+def _replica(cu, n, block=32, slots=4, shareable=True, rel_bits=22, bits=8, deadline_us=1000, window=0):
     cfg = cu.GpuConfig()
     cfg.window_tiles = window
-    cfg.comm_ctas = ctas
     cfg.bits = bits
     cfg.poll_deadline_us = deadline_us
     cfg.block = block
@@ -494,13 +493,11 @@ def test_updates_commute_with_rounds(cu):
 
 
 def test_windowed_launches_cover_the_tensor(cu):
-    """A tensor whose launches handle a bounded number of tiles (16 here, four per group of the kernel's two CTAs, of
-    which each owns eleven): manual rounds make whole passes of several launches, the engine thread's launches go on
-    where the last one stopped, and both see every tile."""
+    """A tensor that is covered in several launches per pass (windows of 16 tiles here): manual rounds make whole
+    passes, the engine thread goes from window to window, and both see every tile."""
     n = 40 * 4096 + 11
     torch.manual_seed(31)
-    A, B = _replica(cu, n, window=16, ctas=2), _replica(cu, n, window=16, ctas=2)
-    assert A.launches_per_pass() == 3
+    A, B = _replica(cu, n, window=16), _replica(cu, n, window=16)
     connect_local(A, B)
     init = torch.randn(n, device="cuda")
     A.load_values(init.data_ptr(), _stream())
@@ -524,7 +521,7 @@ def test_windowed_launches_cover_the_tensor(cu):
         if all(s[names.index(k)] == 0 for s in (sa, sb) for k in ("last_work_count", "pending_tiles")):
             quiet = True
             break
-    assert quiet, "the counters of a launch that saw the whole tensor are zero once nothing moves"
+    assert quiet, "the counters of a whole pass (all windows) are zero once nothing moves"
     assert A.status()[names.index("tiles_processed")] >= A.tiles()
     A.start_engine()
     B.start_engine()
