@@ -260,9 +260,12 @@ def run_ours(args) -> dict | None:
             expect_s.add_(pool_s[(r, p)], alpha=float(times))
             counts[(r, p)] = counts.get((r, p), 0) + times
 
-        def cadence_ns() -> int:
-            u = float(torch.rand(1, generator=rng_cad))
-            return int((CADENCE_MS[0] + u * (CADENCE_MS[1] - CADENCE_MS[0])) * 1e6)
+        def cadences_ns(steps: int) -> list:
+            """The pauses before the updates of one region: uniform over the cadence range, stratified (one value from
+            each of `steps` equal slices, in this rank's random order), so that every region offers the same load and
+            regions differ by what the system does, not by the draw."""
+            u = (torch.randperm(steps, generator=rng_cad).double() + 0.5) / steps
+            return [int((CADENCE_MS[0] + float(x) * (CADENCE_MS[1] - CADENCE_MS[0])) * 1e6) for x in u]
 
         def run_steps(k0: int, steps: int, e2e: bool, pool_mod: int = POOL) -> dict:
             """Issues `steps` updates on this rank (all ranks do the same), waits until the replica holds everybody's.
@@ -305,9 +308,10 @@ def run_ours(args) -> dict | None:
 
             if e2e:
                 issue_h2d(0)
+            cads = cadences_ns(steps)
             for j in range(steps):
                 p = (k0 + j) % pool_mod
-                cu.delay(cadence_ns(), stream)
+                cu.delay(cads[j], stream)
                 extra_launches += 1
                 if e2e:
                     if j + 1 < steps:
@@ -548,9 +552,9 @@ def run_reference(args) -> dict | None:
             upd2 = float((total.double() ** 2).sum())
             barrier()
             t0 = time.perf_counter()
+            cad = (torch.randperm(steps, generator=rng).double() + 0.5) / steps   # stratified, as in the other arm
             for j in range(steps):
-                u = float(torch.rand(1, generator=rng))
-                time.sleep((CADENCE_MS[0] + u * (CADENCE_MS[1] - CADENCE_MS[0])) / 1e3)
+                time.sleep((CADENCE_MS[0] + float(cad[j]) * (CADENCE_MS[1] - CADENCE_MS[0])) / 1e3)
                 w.call(op="add_pool", seed=seed_of(rank, (k0 + j) % POOL))
                 if e2e:
                     w.call(op="digest", stride=SAMPLE_STRIDE)
