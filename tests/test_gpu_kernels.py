@@ -385,6 +385,36 @@ def test_a_received_frame_is_not_answered(cu):
         assert ((out - expect).norm() / expect.norm()).item() < 1e-5
 
 
+def test_several_passes_in_one_launch(cu):
+    """One launch can make several passes over the tensor: the second and third frame of an update follow the first
+    without the host, and a receiver's launch takes all of them."""
+    n = 9 * 4096 + 100
+    torch.manual_seed(17)
+    A, B = _replica(cu, n), _replica(cu, n)
+    connect_local(A, B)
+    names = cu.status_names()
+    d = torch.randn(n, device="cuda")
+    A.add(d.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    before = A.launches()
+    A.round(True, True, 6)
+    A.sync()
+    assert A.launches() - before == 1
+    st = A.status()
+    sent = st[names.index("frames_sent")]
+    assert sent >= 3 * A.tiles() - 3, "it takes three frames per tile to bring fp32 values below the cut-off"
+    B.round(True, True, 6)
+    B.sync()
+    A.round()
+    A.sync()
+    assert A.status()[names.index("frames_sent")] == sent, "the one launch had said everything"
+    out = torch.empty(n, device="cuda")
+    B.snapshot(out.data_ptr(), _stream())
+    torch.cuda.synchronize()
+    assert ((out - d).norm() / d.norm()).item() < 1e-6
+    assert A.status()[names.index("errors")] == 0 and B.status()[names.index("errors")] == 0
+
+
 def test_several_frames_per_round_and_ring_full(cu, core):
     """The sender runs ahead: the receiver takes up to three frames per sweep in order; once the ring is full the
     sender skips (nothing is lost, the residual simply stays) and counts it."""
