@@ -53,6 +53,20 @@ def test_gpt2_tiny_forward_backward_and_parameter_count():
     assert n == 124_439_808
 
 
+def test_structured_batches_follow_their_rule():
+    """Token t+1 = (token t + step) mod m with one step per sequence; a large vocabulary is narrowed to m active
+    tokens, a small one is used whole."""
+    from sharedtensor_b200.parallel.trainers import structured_token_batches
+
+    for vocab, m in ((13, 13), (50257, 512)):
+        x, y = next(structured_token_batches(vocab, 6, 20, torch.device("cpu"), seed=3, period=7))
+        assert x.shape == (6, 20) and y.shape == (6, 20)
+        assert int(x.max()) < m and int(y.max()) < m and int(x.min()) >= 0
+        assert torch.equal(x[:, 1:], y[:, :-1])
+        step = (y - x) % m
+        assert bool((step == step[:, :1]).all()) and 1 <= int(step.min()) and int(step.max()) <= 7
+
+
 def test_two_async_replicas_learn_together(free_port):
     """Two replicas train on different shards of a learnable task through one shared tensor; both losses fall and
     the replicas end up with the same parameters."""
