@@ -39,7 +39,7 @@ struct GpuConfig {
   int idle_sleep_us = 1000;  // longest pause of the engine thread between rounds while nothing moves
   int round_interval_us = 0; // pause after every busy round (0 = run rounds back to back)
   int bits = 8;              // bits per element of a frame: 1 (sign frames), 2, 4 or 8 (integer frames)
-  int sweeps = 0;            // passes over the tensor per launch of the engine thread (0 = chosen from the tensor's size)
+  int sweeps = 0;            // passes over the tensor per launch of the engine thread (0 = one)
   int poll_deadline_us = 1000;  // upper bound of every wait inside the round kernel
   int shape = 1;             // make-up of the round kernel's CTAs, see launch_round
   bool yield_to_updates = true;  // a running round kernel gives up its SMs when addFromTensor has an update ready

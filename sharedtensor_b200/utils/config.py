@@ -33,7 +33,7 @@ class Config:
     # --- GPU engine -----------------------------------------------------------------------------
     ring_slots: int = 4              # frames in flight per edge direction
     bits: int = 8                    # bits per element of a GPU frame: 1 (sign frames, the reference's) | 2 | 4 | 8
-    sweeps_per_launch: int = 0       # passes over the tensor per launch of the round kernel (0: chosen from the size)
+    sweeps_per_launch: int = 0       # passes over the tensor per launch of the round kernel (0: one; more saves launches but delays a fresh update)
     engine: str = "thread"           # thread: free-running rounds on a comm stream | manual: caller drives step()
     comm_ctas: int = 0               # CTAs of the round kernel (0 = one per SM)
     rounds_in_flight: int = 2        # how far the engine thread runs ahead of the GPU
