@@ -38,6 +38,8 @@ def main():
     ap.add_argument("--ctas", type=int, default=0, help="CTAs of the round kernel (0: one per SM)")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--only-round", action="store_true")
+    ap.add_argument("--hub-quiet", action="store_true",
+                    help="the hub makes no update of its own: its tiles carry no change mark, so a pass only receives")
     ap.add_argument("--hub-mode", default="both", choices=["both", "rx", "tx"],
                     help="what the timed round does: receive and send, receive only, send only")
     args = ap.parse_args()
@@ -103,7 +105,7 @@ def main():
             timed("add_scaled_bf16", lambda: hub.add_scaled_bf16(g16.data_ptr(), -1e-3, s))
             timed("table_scales", lambda: cu.table_scales(hub.values_ptr(), offs.data_ptr(), 3, n, scratch.data_ptr(), sums.data_ptr(),
                                                           exps.data_ptr(), s))
-        else:
+        elif not args.hub_quiet:
             hub.add(d.data_ptr(), s)
         for leaf in others:  # the others have something to say to the hub as well
             leaf.add(d.data_ptr(), s)
