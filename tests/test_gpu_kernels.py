@@ -6,6 +6,8 @@ import torch
 from sharedtensor_b200 import _native
 from sharedtensor_b200.parallel.local_wiring import connect_local, connect_mesh
 
+from replica_model import Oracle
+
 pytestmark = pytest.mark.gpu
 
 
@@ -159,95 +161,6 @@ def test_sample_sqerr_and_delay(cu):
 
 
 # --------------------------------------------------------------------------------------------------
-class Oracle:
-    """Host model of a replica: values, one mirror per link, frames exchanged as (codes or words, scales), and the
-    change mark of every 4096-element tile.  A link is told about a tile only while the tile carries a mark: set by
-    whatever changes the values or a mirror from outside the rounds, kept while a visit still found something to say;
-    a frame that merely arrives (it moves values and mirror alike) does not make the tile speak."""
-
-    def __init__(self, core, n, block, n_links, bits=8, min_exp=-60, rel_bits=22):
-        self.core, self.n, self.block, self.bits = core, n, block, bits
-        self.v = torch.zeros(n)
-        self.k = [torch.zeros(n) for _ in range(n_links)]
-        self.min_exp, self.rel_bits = min_exp, rel_bits
-        self.dirty = torch.ones((n + 4095) // 4096, dtype=torch.bool)  # a fresh replica, a new edge: everything is looked at
-
-    def mark(self):
-        self.dirty[:] = True
-
-    def encode(self, link):
-        k_before = self.k[link].clone()
-        codes, scales = self._encode_all(link)
-        spt = 4096 // self.block
-        for t in range(self.dirty.numel()):
-            lo, hi = t * 4096, min((t + 1) * 4096, self.n)
-            if not bool(self.dirty[t]):
-                self.k[link][lo:hi] = k_before[lo:hi]
-                scales[t * spt:(t + 1) * spt] = 0
-                if self.bits == 1:
-                    codes[lo // 32:(hi + 31) // 32] = 0
-                else:
-                    codes[lo:hi] = 1 << (self.bits - 1)
-            else:
-                self.dirty[t] = bool(scales[t * spt:(t + 1) * spt].any())
-        return codes, scales
-
-    def _encode_all(self, link):
-        scales = torch.zeros(self.core.block_scales(self.n, self.block), dtype=torch.uint8)
-        if self.bits == 1:
-            codes = torch.zeros(self.core.block_words(self.n), dtype=torch.int32)
-            self.core.encode_block(self.v.data_ptr(), self.k[link].data_ptr(), self.n, self.block, self.min_exp, self.rel_bits,
-                                   codes.data_ptr(), scales.data_ptr())
-        else:
-            codes = torch.zeros(self.n, dtype=torch.uint8)
-            self.core.encode_block_int(self.v.data_ptr(), self.k[link].data_ptr(), self.n, self.block, self.min_exp, self.rel_bits,
-                                       self.bits, codes.data_ptr(), scales.data_ptr())
-        return codes, scales
-
-    def steps(self, frame):
-        codes, scales = frame
-        out = torch.zeros(self.n)
-        if self.bits == 1:
-            self.core.block_sign_steps(codes.data_ptr(), scales.data_ptr(), self.n, self.block, out.data_ptr())
-        else:
-            self.core.block_int_steps(codes.data_ptr(), scales.data_ptr(), self.n, self.block, self.bits, out.data_ptr())
-        return out
-
-    def decode(self, link, frames):
-        """What one sweep does with the frames it finds on a link: their steps are added up first (in order), the sum
-        then goes into the values and into the link's mirror."""
-        if not isinstance(frames, list):
-            frames = [frames]
-        if not frames:
-            return
-        acc = torch.zeros(self.n)
-        for fr in frames:
-            acc = acc + self.steps(fr)
-        self.v += acc
-        self.k[link] += acc
-
-    def payload_of_tile(self, frame, tile):
-        """(code words as the ring slot holds them, scale bytes, mask of 32-element chunks whose block is not silent)."""
-        codes, scales = frame
-        lo, hi = tile * 4096, min((tile + 1) * 4096, self.n)
-        if self.bits == 1:
-            unpacked = torch.zeros(4096, dtype=torch.uint8)
-            w = codes[lo // 32:(hi + 31) // 32].to(torch.int64) & 0xFFFFFFFF
-            bits = ((w[:, None] >> torch.arange(32)) & 1).reshape(-1).to(torch.uint8)
-            unpacked[:bits.numel()] = bits
-        else:
-            unpacked = torch.full((4096,), 1 << (self.bits - 1), dtype=torch.uint8)
-            unpacked[:hi - lo] = codes[lo:hi]
-        words = torch.zeros(self.bits * 128, dtype=torch.int32)
-        self.core.pack_tile_codes(unpacked.data_ptr(), self.bits, words.data_ptr())
-        spt = 4096 // self.block
-        sc = torch.zeros(spt, dtype=torch.uint8)
-        mine = scales[tile * spt:(tile + 1) * spt]
-        sc[:mine.numel()] = mine
-        loud = (sc != 0).repeat_interleave(self.block // 32)
-        return words, sc, loud
-
-
 def _state(cu, rep, link):
     n = rep.size()
     v = torch.empty(n, device="cuda")
