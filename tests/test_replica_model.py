@@ -87,3 +87,36 @@ def test_a_receiver_does_not_answer(core):
     assert 1 in out and int(B.tiles_of(out[1]).sum()) == n // 4096, "and passes it on to C at once"
     C.visit({0: [out[1]]})
     assert ((C.v - (B.v)).norm() / da.norm()).item() < 1e-2, "one 8-bit frame per hop delivers the update to under 1 %"
+
+
+def test_mesh_group_one_hop_no_forwarding(core):
+    """Four replicas as a fully connected group: one link and one mirror each, a member's frame goes to every peer and
+    what arrives from the peers is not passed on.  Everybody ends at the exact sum, and a member that only received
+    sends nothing."""
+    n = 2 * 4096 + 300
+    torch.manual_seed(9)
+    members = [Oracle(core, n, 32, 1) for _ in range(4)]
+    init = torch.randn(n)
+    for o in members:
+        o.v = init.clone()
+        o.k = [init.clone()]
+    deltas = {0: torch.randn(n), 2: torch.randn(n) * 1e-3}
+    inbox = [[] for _ in members]
+    sent = [0] * 4
+    for r in range(12):
+        if r == 1:
+            for i, d in deltas.items():
+                members[i].v += d
+                members[i].mark()
+        for i, o in enumerate(members):
+            arrived, inbox[i] = inbox[i], []
+            out = o.visit({0: arrived})
+            if 0 in out:
+                sent[i] += 1
+                for j in range(4):
+                    if j != i:
+                        inbox[j].append(out[0])
+    expect = init + deltas[0] + deltas[2]
+    for o in members:
+        assert ((o.v - expect).norm() / expect.norm()).item() < 5e-6
+    assert sent[1] == 0 and sent[3] == 0 and sent[0] >= 3 and sent[2] >= 1
