@@ -105,12 +105,18 @@ class Oracle:
         links that were told something (frames that say nothing anywhere are left out).  What arrived goes into the
         values and into the mirror of the link it came on; a link then hears about a tile if the tile carries a
         change mark or if something for it arrived on another link."""
-        arrived = {l: fr for l, fr in (arrived or {}).items() if fr}
+        arrived = {l: fr for l, fr in sorted((arrived or {}).items()) if fr}
         came = {l: torch.zeros_like(self.dirty) for l in arrived}
-        for l, frames in arrived.items():
+        total = torch.zeros(self.n)   # everything that arrived, added up ring by ring and frame by frame, goes into
+        for l, frames in arrived.items():  # the values as one sum; what arrived on a link goes into that link's mirror
+            acc = torch.zeros(self.n)
             for fr in frames:
                 came[l] |= self.tiles_of(fr)
-            self.decode(l, frames)
+                st = self.steps(fr)
+                acc = acc + st
+                total = total + st
+            self.k[l] += acc
+        self.v += total
         marks = self.dirty.clone()
         still = torch.zeros_like(self.dirty)
         out = {}

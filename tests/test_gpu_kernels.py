@@ -558,6 +558,47 @@ def test_bounded_wait_runs_out_and_the_replica_recovers(cu):
     assert A.check_guards() == 0 and B.check_guards() == 0
 
 
+@pytest.mark.parametrize("bits", [8, 1])
+def test_chain_bit_exact_with_the_host_model(cu, core, bits):
+    """A - B - C with B forwarding: values and every mirror of all three replicas, pass by pass, against the host model
+    (what arrives on one link is passed on over the other in the same pass, is not answered on its own link, and two
+    links that deliver in the same pass are added up before they go into the values)."""
+    n = 2 * 4096 + 333
+    torch.manual_seed(40 + bits)
+    reps = [_replica(cu, n, bits=bits) for _ in range(3)]
+    la, lb0 = connect_local(reps[0], reps[1])
+    lb1, lc = connect_local(reps[1], reps[2])
+    links = [[la], [lb0, lb1], [lc]]
+    models = [Oracle(core, n, 32, 1, bits), Oracle(core, n, 32, 2, bits), Oracle(core, n, 32, 1, bits)]
+    init = torch.randn(n)
+    models[0].v = init.clone()
+    reps[0].load_values(init.cuda().data_ptr(), _stream())     # B and C start from zero and are streamed the state
+    peer = {(0, 0): (1, 0), (1, 0): (0, 0), (1, 1): (2, 0), (2, 0): (1, 1)}
+    inbox = {key: [] for key in peer}
+    for it in range(12 if bits == 8 else 30):
+        if it in (3, 8):
+            for i, scale in ((0, 1e-1), (2, 1.0)):
+                d = torch.randn(n) * scale
+                models[i].v += d
+                models[i].mark()
+                reps[i].add(d.cuda().data_ptr(), _stream())
+            torch.cuda.synchronize()
+        for i in range(3):
+            reps[i].round()
+            reps[i].sync()
+            arrived = {l: inbox[(i, l)] for l in range(len(models[i].k))}
+            for l in arrived:
+                inbox[(i, l)] = []
+            for l, frame in models[i].visit(arrived).items():
+                inbox[peer[(i, l)]].append(frame)
+            for l, dev_link in enumerate(links[i]):
+                v, k = _state(cu, reps[i], dev_link)
+                assert torch.equal(v, models[i].v), f"values of replica {i} differ in pass {it}"
+                assert torch.equal(k, models[i].k[l]), f"mirror {l} of replica {i} differs in pass {it}"
+    for r in reps:
+        assert r.status()[5] == 0 and r.check_guards() == 0
+
+
 def test_chain_forwarding_converges_to_the_sum(cu):
     """A - B - C: updates made at the ends reach the other end through B's forwarding."""
     n = 5 * 4096 + 123
