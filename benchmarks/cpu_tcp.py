@@ -33,16 +33,20 @@ def main() -> None:
     ap.add_argument("--tcp-scale-mode", default="tensor",
                     help="tensor = the reference's wire format (one scale per frame); block32 ... block4096 = one exponent "
                          "byte per block, between nodes of this framework only")
+    ap.add_argument("--tcp-bits", type=int, default=1,
+                    help="bits per element of a frame in a block mode: 1 = sign frames, 8 = integer frames (one frame delivers "
+                         "an update to under 1 %%)")
     args = ap.parse_args()
     n = int(args.elements)
+    kw = {"tcp_scale_mode": args.tcp_scale_mode, "tcp_bits": args.tcp_bits}
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     torch.manual_seed(0)
     init = torch.randn(n)
-    a = sharedtensor.createOrFetch("127.0.0.1", port, init.clone(), tcp_scale_mode=args.tcp_scale_mode)
+    a = sharedtensor.createOrFetch("127.0.0.1", port, init.clone(), **kw)
     t0 = time.perf_counter()
-    b = sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), tcp_scale_mode=args.tcp_scale_mode)
+    b = sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), **kw)
     out = torch.empty(n)
     b.flush(args.timeout)
     join_s = time.perf_counter() - t0
@@ -77,7 +81,7 @@ def main() -> None:
     print(json.dumps({"metric": "applied_updates_per_s", "impl": "ours, CPU node, loopback TCP", "value": args.steps / secs,
                       "elements": n, "steps": args.steps, "seconds": secs, "final_rel_err": rel, "converged": rel <= args.tol,
                       "late_join_state_transfer_s": join_s, "frames_sent": st["frames_sent"], "bytes_sent": st["bytes_sent"],
-                      "tol": args.tol, "tcp_scale_mode": args.tcp_scale_mode, "checked": f"every {SAMPLE}th element"}))
+                      "tol": args.tol, "tcp_scale_mode": args.tcp_scale_mode, "tcp_bits": args.tcp_bits, "checked": f"every {SAMPLE}th element"}))
     b.close()
     a.close()
 

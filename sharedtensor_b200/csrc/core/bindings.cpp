@@ -91,6 +91,23 @@ void bind_core(py::module_& m) {
     g.rel_bits = rel_bits;
     return encode_block_int(ptr<float>(v), ptr<float>(k), n, block, g, bits, ptr<uint8_t>(codes), ptr<uint8_t>(scales));
   });
+  m.def("encode_block_int8_fast", [](uintptr_t v, uintptr_t k, size_t n, int block, int min_exp, int rel_bits, uintptr_t codes,
+                                     uintptr_t scales) {
+    BlockGate g;
+    g.min_exp = min_exp;
+    g.rel_bits = rel_bits;
+    return encode_block_int8_fast(ptr<float>(v), ptr<float>(k), n, block, g, ptr<uint8_t>(codes), ptr<uint8_t>(scales));
+  });
+  m.def("decode_block_int_add", [](uintptr_t codes, uintptr_t scales, size_t n, int block, int bits, float sign, uintptr_t dst,
+                                   uintptr_t dst2) {
+    decode_block_int_add(ptr<uint8_t>(codes), ptr<uint8_t>(scales), n, block, bits, sign, ptr<float>(dst),
+                         dst2 ? ptr<float>(dst2) : nullptr);
+  });
+  m.def("decode_block_int8_add_fast", [](uintptr_t codes, uintptr_t scales, size_t n, int block, float sign, uintptr_t dst,
+                                         uintptr_t dst2) {
+    decode_block_int8_add_fast(ptr<uint8_t>(codes), ptr<uint8_t>(scales), n, block, sign, ptr<float>(dst),
+                               dst2 ? ptr<float>(dst2) : nullptr);
+  });
   m.def("block_int_steps", [](uintptr_t codes, uintptr_t scales, size_t n, int block, int bits, uintptr_t steps) {
     block_int_steps(ptr<uint8_t>(codes), ptr<uint8_t>(scales), n, block, bits, ptr<float>(steps));
   });
@@ -135,6 +152,7 @@ void bind_core(py::module_& m) {
   py::class_<NodeConfig>(m, "NodeConfig")
       .def(py::init<>())
       .def_readwrite("tcp_block", &NodeConfig::tcp_block)
+      .def_readwrite("tcp_bits", &NodeConfig::tcp_bits)
       .def_readwrite("tcp_rule", &NodeConfig::tcp_rule)
       .def_readwrite("min_scale_abs", &NodeConfig::min_scale_abs)
       .def_readwrite("min_scale_rel", &NodeConfig::min_scale_rel)

@@ -255,6 +255,24 @@ void block_int_steps(const uint8_t* codes, const uint8_t* scales, size_t n, int 
   }
 }
 
+void decode_block_int_add(const uint8_t* codes, const uint8_t* scales, size_t n, int block, int bits, float sign, float* dst,
+                          float* dst2) {
+  const size_t nb = block_scales(n, block);
+  const float M = 8388608.0f + float(1 << (bits - 1));
+  for (size_t b = 0; b < nb; b++) {
+    const int code = scales[b];
+    if (code == 0 || code == 255) continue;
+    const size_t base = b * size_t(block);
+    const size_t end = base + size_t(block) < n ? base + size_t(block) : n;
+    const float s = exp2i(code - 127), neg_ms = -(M * s);
+    for (size_t i = base; i < end; i++) {
+      const float step = sign * std::fmaf(bits_f32(0x4b000000u | codes[i]), s, neg_ms);
+      dst[i] += step;
+      if (dst2) dst2[i] += step;
+    }
+  }
+}
+
 void block_sign_steps(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* steps) {
   const size_t nb = block_scales(n, block);
   for (size_t b = 0; b < nb; b++) {

@@ -147,6 +147,16 @@ void block_int_steps(const uint8_t* codes, const uint8_t* scales, size_t n, int 
 // ... and for sign frames (`words` as produced by encode_block).
 void block_sign_steps(const uint32_t* words, const uint8_t* scales, size_t n, int block, float* steps);
 
+// Adds sign * (the steps of one integer frame) to dst and, if given, dst2 (sign = +1 applies a frame, -1 takes it back).
+void decode_block_int_add(const uint8_t* codes, const uint8_t* scales, size_t n, int block, int bits, float sign, float* dst,
+                          float* dst2);
+// 8-bit integer frames with one code byte per element, as TCP edges between nodes of this framework can carry them
+// (AVX2 + FMA and several threads where available; bit for bit what encode_block_int / decode_block_int_add give).
+double encode_block_int8_fast(const float* v, float* k, size_t n, int block, const BlockGate& gate, uint8_t* codes,
+                              uint8_t* scales);
+void decode_block_int8_add_fast(const uint8_t* codes, const uint8_t* scales, size_t n, int block, float sign, float* dst,
+                                float* dst2);
+
 // Layout of one tile (4096 elements) in a GPU ring slot: `bits` * 128 words of codes, then the scale bytes.
 // Codes are packed little-endian, `bits` per element, in the order the kernel's threads hold them: within
 // the c-th run of 32 elements the g-th group of four elements sits at position g ^ (c & 7).  `codes` holds

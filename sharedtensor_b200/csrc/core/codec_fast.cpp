@@ -305,7 +305,127 @@ __attribute__((target("avx2"))) void decode_blocks_avx2(const uint32_t* words, c
   }
 }
 
+// ---- 8-bit integer frames, full blocks only (block a multiple of 32) ----
+__attribute__((target("avx2,fma"))) double encode_blocks_int8_avx2(const float* v, float* k, size_t n, int block,
+                                                                   const BlockGate& gate, uint8_t* codes, uint8_t* scales) {
+  const __m256 absmask = _mm256_castsi256_ps(_mm256_set1_epi32(0x7fffffff));
+  const __m256i bytemask = _mm256_set1_epi32(0xff);
+  const __m256i order = _mm256_setr_epi32(0, 4, 1, 5, 2, 6, 3, 7);
+  const float M = 8388608.0f + 128.0f;
+  const __m256 vM = _mm256_set1_ps(M);
+  double worst = 0.0;
+  const size_t nb = n / size_t(block);
+  for (size_t b = 0; b < nb; b++) {
+    const float* vb = v + b * size_t(block);
+    float* kb = k + b * size_t(block);
+    uint8_t* cb = codes + b * size_t(block);
+    __m256 xm = _mm256_setzero_ps();
+    __m256i vm = _mm256_setzero_si256();
+    for (int j = 0; j < block; j += 8) {
+      const __m256 vv = _mm256_loadu_ps(vb + j);
+      const __m256 x = _mm256_sub_ps(vv, _mm256_loadu_ps(kb + j));
+      xm = _mm256_max_ps(_mm256_and_ps(x, absmask), xm);
+      vm = _mm256_max_epu32(vm, _mm256_castps_si256(_mm256_and_ps(vv, absmask)));
+    }
+    float tx[8];
+    uint32_t tv[8];
+    _mm256_storeu_ps(tx, xm);
+    _mm256_storeu_si256(reinterpret_cast<__m256i*>(tv), vm);
+    float xmax = 0.0f;
+    uint32_t vmax = 0;
+    for (int j = 0; j < 8; j++) {
+      if (tx[j] > xmax) xmax = tx[j];
+      if (tv[j] > vmax) vmax = tv[j];
+    }
+    if (double(xmax) > worst) worst = double(xmax);
+    const int code = block_code_int(xmax, vmax, gate, 8);
+    scales[b] = uint8_t(code);
+    if (!code) {
+      std::memset(cb, 0x80, size_t(block));
+      continue;
+    }
+    const float s = exp2i(code - 127);
+    const __m256 vs = _mm256_set1_ps(s), vinv = _mm256_set1_ps(exp2i(127 - code)), vneg = _mm256_set1_ps(-(M * s));
+    for (int j = 0; j < block; j += 32) {
+      __m256i zb[4];
+      for (int q = 0; q < 4; q++) {
+        const int o = j + q * 8;
+        const __m256 kk = _mm256_loadu_ps(kb + o);
+        const __m256 z = _mm256_fmadd_ps(_mm256_sub_ps(_mm256_loadu_ps(vb + o), kk), vinv, vM);
+        zb[q] = _mm256_and_si256(_mm256_castps_si256(z), bytemask);
+        _mm256_storeu_ps(kb + o, _mm256_add_ps(kk, _mm256_fmadd_ps(z, vs, vneg)));
+      }
+      // 4 x 8 values below 256 -> 32 bytes in element order (the packs work within 128-bit halves)
+      const __m256i p = _mm256_packus_epi16(_mm256_packus_epi32(zb[0], zb[1]), _mm256_packus_epi32(zb[2], zb[3]));
+      _mm256_storeu_si256(reinterpret_cast<__m256i*>(cb + j), _mm256_permutevar8x32_epi32(p, order));
+    }
+  }
+  return worst;
+}
+
+__attribute__((target("avx2,fma"))) void decode_blocks_int8_avx2(const uint8_t* codes, const uint8_t* scales, size_t n,
+                                                                 int block, float sign, float* dst, float* dst2) {
+  const float M = 8388608.0f + 128.0f;
+  const __m256i expo = _mm256_set1_epi32(0x4b000000);
+  const __m256 vsign = _mm256_set1_ps(sign);
+  const size_t nb = n / size_t(block);
+  for (size_t b = 0; b < nb; b++) {
+    const int code = scales[b];
+    if (code == 0 || code == 255) continue;
+    const float s = exp2i(code - 127);
+    const __m256 vs = _mm256_set1_ps(s), vneg = _mm256_set1_ps(-(M * s));
+    const size_t base = b * size_t(block);
+    for (int j = 0; j < block; j += 8) {
+      const size_t i = base + size_t(j);
+      const __m256i c = _mm256_cvtepu8_epi32(_mm_loadl_epi64(reinterpret_cast<const __m128i*>(codes + i)));
+      const __m256 step = _mm256_mul_ps(vsign, _mm256_fmadd_ps(_mm256_castsi256_ps(_mm256_or_si256(c, expo)), vs, vneg));
+      _mm256_storeu_ps(dst + i, _mm256_add_ps(_mm256_loadu_ps(dst + i), step));
+      if (dst2) _mm256_storeu_ps(dst2 + i, _mm256_add_ps(_mm256_loadu_ps(dst2 + i), step));
+    }
+  }
+}
+
+bool have_fma() {
+  static const bool ok = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
+  return ok;
+}
+
 }  // namespace
+
+double encode_block_int8_fast(const float* v, float* k, size_t n, int block, const BlockGate& gate, uint8_t* codes,
+                              uint8_t* scales) {
+  const bool avx = have_fma();
+  double worst[64];
+  for (int i = 0; i < 64; i++) worst[i] = 0.0;
+  parallel_chunks(n, size_t(block), [&](size_t b, size_t e, int idx) {
+    const size_t full = avx ? (e - b) / size_t(block) * size_t(block) : 0;
+    double w = 0.0;
+    if (full) w = encode_blocks_int8_avx2(v + b, k + b, full, block, gate, codes + b, scales + b / size_t(block));
+    if (b + full < e) {
+      const size_t o = b + full;
+      double w2 = encode_block_int(v + o, k + o, e - o, block, gate, 8, codes + o, scales + o / size_t(block));
+      if (w2 > w) w = w2;
+    }
+    worst[idx] = w;
+  });
+  double w = 0.0;
+  for (int i = 0; i < 64; i++)
+    if (worst[i] > w) w = worst[i];
+  return w;
+}
+
+void decode_block_int8_add_fast(const uint8_t* codes, const uint8_t* scales, size_t n, int block, float sign, float* dst,
+                                float* dst2) {
+  const bool avx = have_fma();
+  parallel_chunks(n, size_t(block), [&](size_t b, size_t e, int) {
+    const size_t full = avx ? (e - b) / size_t(block) * size_t(block) : 0;
+    if (full) decode_blocks_int8_avx2(codes + b, scales + b / size_t(block), full, block, sign, dst + b, dst2 ? dst2 + b : nullptr);
+    if (b + full < e) {
+      const size_t o = b + full;
+      decode_block_int_add(codes + o, scales + o / size_t(block), e - o, block, 8, sign, dst + o, dst2 ? dst2 + o : nullptr);
+    }
+  });
+}
 
 double encode_block_fast(const float* v, float* k, size_t n, int block, const BlockGate& gate, uint32_t* words,
                          uint8_t* scales) {

@@ -18,6 +18,8 @@ CpuNode::CpuNode(int64_t n, const NodeConfig& cfg) : n_(n), cfg_(cfg) {
     int b = cfg_.tcp_block;
     if (b < 32 || b > 4096 || (b & (b - 1))) throw std::invalid_argument("tcp_block must be 0 or a power of two in 32..4096");
   }
+  if (cfg_.tcp_bits != 1 && cfg_.tcp_bits != 8) throw std::invalid_argument("tcp_bits must be 1 or 8");
+  if (cfg_.tcp_bits == 8 && cfg_.tcp_block == 0) throw std::invalid_argument("8-bit frames need a block scale mode (tcp_block)");
   values_.assign(size_t(n), 0.0f);
   for (int s = 0; s < kNumSlots; s++) edges_[s].slot = s;
 }
@@ -26,6 +28,7 @@ CpuNode::~CpuNode() { close(); }
 
 size_t CpuNode::frame_bytes() const {
   if (cfg_.tcp_block == 0) return 4 + sign_bytes(size_t(n_));
+  if (cfg_.tcp_bits == 8) return block_scales(size_t(n_), cfg_.tcp_block) + size_t(n_);  // scale bytes, one code byte per element
   return block_scales(size_t(n_), cfg_.tcp_block) + 4 * block_words(size_t(n_));
 }
 
@@ -230,12 +233,17 @@ void CpuNode::tx_loop(Edge* e) {
       } else {
         size_t ns = block_scales(n, B);
         uint8_t* scales = frame.data();
-        uint32_t* words = reinterpret_cast<uint32_t*>(frame.data() + ns);
-        // words need 4-byte alignment: ns may be odd, so encode into an aligned scratch
-        static thread_local std::vector<uint32_t> wtmp;
-        wtmp.assign(block_words(n), 0u);
-        double ss = encode_block_fast(values_.data(), e->mirror.data(), n, B, cfg_.gate, wtmp.data(), scales);
-        std::memcpy(words, wtmp.data(), 4 * wtmp.size());
+        double ss;
+        if (cfg_.tcp_bits == 8) {
+          ss = encode_block_int8_fast(values_.data(), e->mirror.data(), n, B, cfg_.gate, frame.data() + ns, scales);
+        } else {
+          uint32_t* words = reinterpret_cast<uint32_t*>(frame.data() + ns);
+          // words need 4-byte alignment: ns may be odd, so encode into an aligned scratch
+          static thread_local std::vector<uint32_t> wtmp;
+          wtmp.assign(block_words(n), 0u);
+          ss = encode_block_fast(values_.data(), e->mirror.data(), n, B, cfg_.gate, wtmp.data(), scales);
+          std::memcpy(words, wtmp.data(), 4 * wtmp.size());
+        }
         noop = true;
         int maxc = 0;
         for (size_t i = 0; i < ns; i++) {
@@ -269,6 +277,9 @@ void CpuNode::tx_loop(Edge* e) {
             float scale;
             std::memcpy(&scale, frame.data(), 4);
             decode_tensor_add_fast(frame.data() + 4, -scale, n, e->mirror.data(), nullptr);
+          } else if (cfg_.tcp_bits == 8) {
+            size_t ns = block_scales(n, B);
+            decode_block_int8_add_fast(frame.data() + ns, frame.data(), n, B, -1.0f, e->mirror.data(), nullptr);
           } else {
             size_t ns = block_scales(n, B);
             std::vector<uint32_t> flipped(block_words(n));
@@ -335,9 +346,13 @@ void CpuNode::rx_loop(Edge* e) {
         edge_failed(e, "malformed frame (scale code)", IoStatus::Error);
         break;
       }
-      wtmp.resize(block_words(n));
-      std::memcpy(wtmp.data(), frame.data() + ns, 4 * wtmp.size());
-      decode_block_add_fast(wtmp.data(), frame.data(), n, B, values_.data(), e->mirror.data());
+      if (cfg_.tcp_bits == 8) {
+        decode_block_int8_add_fast(frame.data() + ns, frame.data(), n, B, 1.0f, values_.data(), e->mirror.data());
+      } else {
+        wtmp.resize(block_words(n));
+        std::memcpy(wtmp.data(), frame.data() + ns, 4 * wtmp.size());
+        decode_block_add_fast(wtmp.data(), frame.data(), n, B, values_.data(), e->mirror.data());
+      }
       level = maxc ? exp2i(maxc - 127) : 0.0f;
     }
     e->st.last_scale_recv = level;

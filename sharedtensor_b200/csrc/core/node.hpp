@@ -26,6 +26,9 @@ namespace st {
 struct NodeConfig {
   // wire format on TCP edges: 0 = tensor scale (what the reference speaks), else block size (32..4096)
   int tcp_block = 0;
+  // block mode: bits per element of a frame, 1 (sign frames) or 8 (integer frames: one frame brings a fresh update
+  // to under one percent; between nodes of this framework, where the link has eight times the bytes to spare)
+  int tcp_bits = 1;
   int tcp_rule = 1;               // tensor mode scale: 0 = the reference's RMS rule, 1 = bisection (see codec.hpp)
   BlockGate gate;                 // block mode cut-offs
   float min_scale_abs = 0.0f;     // tensor mode: frames with a smaller scale become no-ops

@@ -14,6 +14,7 @@ def _node_config(cfg: Config):
     core = _native.core()
     nc = core.NodeConfig()
     nc.tcp_block = cfg.tcp_block
+    nc.tcp_bits = cfg.tcp_bits
     nc.gate_min_exp = cfg.min_exp
     nc.gate_rel_bits = cfg.rel_bits
     nc.min_scale_abs = cfg.min_scale_abs

@@ -43,6 +43,8 @@ class GpuBackend:
     def __init__(self, n: int, cfg: Config, device: torch.device):
         if not torch.cuda.is_available():
             raise RuntimeError("the GPU transport needs a CUDA device")
+        if cfg.tcp_bits != 1:
+            raise ValueError("tcp_bits=8 is a frame format of CPU replicas; the TCP edges of a GPU replica speak the reference's frames")
         cu = _native.cuda()
         self.n = n
         self.cfg = cfg

@@ -26,6 +26,7 @@ class Config:
     # --- quantiser ------------------------------------------------------------------------------
     scale_mode: str = "block32"      # GPU edges: block32 .. block4096
     tcp_scale_mode: str = "tensor"   # TCP edges: tensor (reference wire format) | block32 .. block4096
+    tcp_bits: int = 1                # TCP edges of CPU tensors in a block mode: 1 (sign frames) | 8 (one frame delivers an update to < 1 %)
     min_exp: int = -60               # blocks whose scale exponent is below this stay silent
     rel_bits: int = 22               # ... or this many bits below the block's own value RMS
     min_scale_abs: float = 0.0       # tensor mode cut-offs
@@ -86,6 +87,10 @@ class Config:
         if self.block == 0:
             raise ValueError("GPU edges need a block scale mode (block32..block4096)")
         self.tcp_block  # validates
+        if self.tcp_bits not in (1, 8):
+            raise ValueError("tcp_bits must be 1 or 8")
+        if self.tcp_bits == 8 and self.tcp_block == 0:
+            raise ValueError("tcp_bits=8 needs tcp_scale_mode block32..block4096 (the tensor mode is the reference's wire format)")
         if self.engine not in ("thread", "manual"):
             raise ValueError(f"engine must be thread or manual, got {self.engine!r}")
         if self.ready_mode not in ("first_frame", "converged"):

@@ -239,3 +239,36 @@ def test_fast_paths_are_bit_identical_to_the_plain_codec(n):
         core.decode_block_add(P(w1), P(c1), n, B, P(a1), P(m1))
         core.decode_block_add_fast(P(w1), P(c1), n, B, P(a2), P(m2))
         assert torch.equal(a1, a2) and torch.equal(m1, m2), B
+
+
+@pytest.mark.parametrize("n", [1, 31, 1000, 65537, 2_100_003])
+def test_fast_eight_bit_frames_are_bit_identical_to_the_plain_codec(n):
+    """8-bit integer frames as the TCP edges carry them (one code byte per element): the AVX2 + FMA / multi-threaded
+    path against the plain loops, with a NaN and exact zeros in the data; taking a frame back undoes its step."""
+    P = lambda t: t.data_ptr()  # noqa: E731
+    g = torch.Generator().manual_seed(n + 1)
+    for B in (32, 256, 4096):
+        v = torch.randn(n, generator=g) * torch.logspace(-3, 2, n)
+        k = v + torch.randn(n, generator=g) * 1e-2 * v.abs()
+        if n > 100:
+            v[3] = float("nan")
+            v[40] = 0.0
+            k[40] = 0.0
+        k1, k2 = k.clone(), k.clone()
+        ns = (n + B - 1) // B
+        c1, c2 = torch.zeros(n, dtype=torch.uint8), torch.full((n,), 7, dtype=torch.uint8)
+        s1, s2 = torch.zeros(ns, dtype=torch.uint8), torch.full((ns,), 9, dtype=torch.uint8)
+        r1 = core.encode_block_int(P(v), P(k1), n, B, -100, 22, 8, P(c1), P(s1))
+        r2 = core.encode_block_int8_fast(P(v), P(k2), n, B, -100, 22, P(c2), P(s2))
+        assert r1 == r2 and torch.equal(s1, s2), B
+        loud = s1.ne(0).repeat_interleave(B)[:n]
+        assert torch.equal(c1[loud], c2[loud]), B          # (codes of a silent block's NaN are not looked at)
+        assert torch.equal(torch.nan_to_num(k1, nan=7.0), torch.nan_to_num(k2, nan=7.0)), B
+        steps = torch.zeros(n)
+        core.block_int_steps(P(c1), P(s1), n, B, 8, P(steps))
+        a1, a2, m1, m2 = torch.zeros(n), torch.zeros(n), torch.ones(n), torch.ones(n)
+        core.decode_block_int_add(P(c1), P(s1), n, B, 8, 1.0, P(a1), P(m1))
+        core.decode_block_int8_add_fast(P(c1), P(s1), n, B, 1.0, P(a2), P(m2))
+        assert torch.equal(a1, a2) and torch.equal(m1, m2) and torch.equal(a1, steps), B
+        core.decode_block_int8_add_fast(P(c1), P(s1), n, B, -1.0, P(a2), 0)
+        assert torch.equal(a2, torch.zeros(n)), B

@@ -95,15 +95,18 @@ def test_config1_two_processes_1000_adds_each(free_port):
 
 
 @pytest.mark.parametrize("n_nodes", [3, 6])
-@pytest.mark.parametrize("tcp_scale_mode", ["tensor", "block32"])
+@pytest.mark.parametrize("tcp_scale_mode", ["tensor", "block32", "block32/8"])
 def test_sum_consistency_tree(free_port, n_nodes, tcp_scale_mode):
     torch.manual_seed(n_nodes)
     n = 1000
     init = torch.randn(n)
-    nodes = [sharedtensor.createOrFetch("127.0.0.1", free_port, init, tcp_scale_mode=tcp_scale_mode)]
+    kw = {"tcp_scale_mode": tcp_scale_mode}
+    if tcp_scale_mode.endswith("/8"):   # block scales with 8-bit integer frames
+        kw = {"tcp_scale_mode": tcp_scale_mode[:-2], "tcp_bits": 8}
+    nodes = [sharedtensor.createOrFetch("127.0.0.1", free_port, init, **kw)]
     try:
         for _ in range(n_nodes - 1):
-            nodes.append(sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), tcp_scale_mode=tcp_scale_mode))
+            nodes.append(sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), **kw))
         expect = init.clone()
         for it in range(30):
             for i, node in enumerate(nodes):
@@ -213,3 +216,43 @@ def test_membership_events_are_recorded(free_port):
         b.cfg.rejoin = False
         b.close()
         a.close()
+
+
+def test_eight_bit_frames_deliver_an_update_in_one_frame(free_port):
+    """CPU replicas over TCP with 8-bit integer frames: a fresh update is on the neighbour to under one percent after
+    a single frame (sign frames need about ten), and the frame is one code byte per element plus the scale bytes."""
+    n = 40000
+    torch.manual_seed(8)
+    init = torch.randn(n)
+    kw = {"tcp_scale_mode": "block32", "tcp_bits": 8, "rejoin": False}
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone(), **kw)
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), **kw)
+    try:
+        out = torch.zeros(n)
+        _wait_equal([a, b], init, tol_rel=1e-5, tol_inf=5e-4)
+        time.sleep(0.3)
+        before = b.stats()["edges"]["up"]
+        d = torch.randn(n)
+        a.addFromTensor(d)
+        deadline = time.time() + 10
+        while time.time() < deadline:
+            b.copyToTensor(out)
+            if ((out - init - d).norm() / d.norm()).item() < 1e-2:
+                break
+            time.sleep(0.001)
+        assert ((out - init - d).norm() / d.norm()).item() < 1e-2
+        _wait_equal([a, b], init + d, tol_rel=1e-5, tol_inf=5e-4)
+        after = b.stats()["edges"]["up"]
+        frames = after["frames_recv"] - before["frames_recv"]
+        assert 1 <= frames <= 6, frames   # three frames carry the update down to the cut-off, one says "nothing more"
+        assert (after["bytes_recv"] - before["bytes_recv"]) == frames * (n + n // 32)
+    finally:
+        b.close()
+        a.close()
+
+
+def test_eight_bit_frames_need_a_block_mode():
+    with pytest.raises(ValueError):
+        sharedtensor.Config(tcp_bits=8)
+    with pytest.raises(ValueError):
+        sharedtensor.Config(tcp_scale_mode="block32", tcp_bits=4)

@@ -223,6 +223,27 @@ def test_garbage_scale_code_in_block_mode_costs_only_that_edge(free_port):
         master.close()
 
 
+def test_garbage_scale_code_in_eight_bit_mode_costs_only_that_edge(free_port):
+    """... and with 8-bit integer frames (scale bytes, then one code byte per element)."""
+    n = 64
+    init = torch.arange(float(n))
+    master = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone(), tcp_scale_mode="block32", tcp_bits=8)
+    try:
+        c = _connect(free_port)
+        assert _recv_exact(c, 1) == b"Y"
+        c.sendall(b"\xff" * (n // 32) + b"\x81" * n)
+        deadline = time.time() + 10
+        while time.time() < deadline and master.stats()["edges"]["left"]["state"] != "free":
+            time.sleep(0.02)
+        assert master.stats()["edges"]["left"]["state"] == "free"
+        c.close()
+        out = torch.zeros(n)
+        master.copyToTensor(out)
+        assert torch.equal(out, init), "nothing of the garbage reached the values"
+    finally:
+        master.close()
+
+
 def test_simultaneous_founders_end_up_in_one_tree(free_port):
     """Six callers reach createOrFetch at the same moment with nobody serving host:port yet: exactly one becomes the
     master, the others lose the race for the address, try again and join below it with the master's values."""
