@@ -17,25 +17,28 @@ def _port():
 
 
 @settings(max_examples=6, deadline=None, suppress_health_check=list(HealthCheck))
-@given(n_nodes=st.integers(2, 7), n=st.sampled_from([1, 33, 240, 1025]), mode=st.sampled_from(["tensor", "block32", "block256"]),
+@given(n_nodes=st.integers(2, 7), n=st.sampled_from([1, 33, 240, 1025]), mode=st.sampled_from(["tensor", "block32", "block256", "block32/8", "block256/8"]),
        schedule=st.lists(st.tuples(st.integers(0, 6), st.floats(1e-4, 1.0)), min_size=3, max_size=12), seed=st.integers(0, 10_000))
 def test_every_replica_reaches_the_exact_sum(n_nodes, n, mode, schedule, seed):
     torch.manual_seed(seed)
     port = _port()
     init = torch.randn(n)
     expect = init.double().clone()
-    nodes = [sharedtensor.createOrFetch("127.0.0.1", port, init, tcp_scale_mode=mode)]
+    kw = {"tcp_scale_mode": mode}
+    if mode.endswith("/8"):   # block scales with 8-bit integer frames
+        kw = {"tcp_scale_mode": mode[:-2], "tcp_bits": 8}
+    nodes = [sharedtensor.createOrFetch("127.0.0.1", port, init, **kw)]
     try:
         joins_left = n_nodes - 1
         for who, mag in schedule:
             if joins_left and who % 2 == 0:  # joins interleave with updates: late joiners must receive history
-                nodes.append(sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), tcp_scale_mode=mode))
+                nodes.append(sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), **kw))
                 joins_left -= 1
             d = torch.randn(n) * mag
             nodes[who % len(nodes)].addFromTensor(d)
             expect += d.double()
         while joins_left:
-            nodes.append(sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), tcp_scale_mode=mode))
+            nodes.append(sharedtensor.createOrFetch("127.0.0.1", port, torch.zeros(n), **kw))
             joins_left -= 1
         out = torch.zeros(n)
         scale = max(1.0, float(expect.abs().max()))
