@@ -5,6 +5,7 @@ import os
 import signal
 import time
 
+import pytest
 import torch
 
 import sharedtensor
@@ -228,17 +229,19 @@ def test_churn_between_quiet_rounds_keeps_the_exact_sum(free_port):
             nd.close()
 
 
-def test_cut_edge_under_continuous_traffic_loses_nothing_on_loopback(free_port):
+@pytest.mark.parametrize("fmt", [{}, {"tcp_scale_mode": "block32"}, {"tcp_scale_mode": "block32", "tcp_bits": 8}],
+                         ids=["tensor", "block32", "block32-8bit"])
+def test_cut_edge_under_continuous_traffic_loses_nothing_on_loopback(free_port, fmt):
     """A child adds without pause while its up connection is cut five times.  What it had written before a cut still
     reaches the parent (the FIN follows the queued data), a frame whose write failed is taken back, the rest is
-    carried over the re-join: both replicas end up with every update."""
+    carried over the re-join: both replicas end up with every update.  In every frame format of the TCP edges."""
     import threading
 
     n = 4096
     torch.manual_seed(0)
     init = torch.randn(n)
-    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone())
-    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=20)
+    a = sharedtensor.createOrFetch("127.0.0.1", free_port, init.clone(), **fmt)
+    b = sharedtensor.createOrFetch("127.0.0.1", free_port, torch.zeros(n), rejoin_backoff_ms=20, **fmt)
     expect = init.clone()
     stop = threading.Event()
 
